@@ -1,0 +1,153 @@
+"""Symmetric heap, primitives and fused collectives on ONE GPU (world size 1): every kernel runs its
+real code path with itself as the only peer, which checks the tcgen05 mainloop, flag epochs and
+buffer layouts without needing a second device."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_heap_alloc_free_and_views(dist1):
+    from triton_distributed_b200.runtime.heap import get_heap
+    heap = get_heap()
+    assert heap.world == 1 and heap.mode in ("vmm", "ipc")
+    a = heap.create_tensor((1024, 64), torch.bfloat16)
+    b = heap.create_tensor((7,), torch.float32)
+    assert a.is_cuda and a.shape == (1024, 64) and float(a.abs().sum()) == 0.0
+    a.fill_(1.5)
+    b.fill_(2.0)
+    torch.cuda.synchronize()
+    assert float(a.float().sum()) == 1.5 * a.numel() and float(b.sum()) == 14.0
+    views = heap.create_tensors((16,), torch.int32)
+    assert len(views) == 1 and views[0].data_ptr() >= heap.base[0]
+    live = heap.live_bytes()
+    heap.free(a)
+    assert heap.live_bytes() < live
+    a2 = heap.create_tensor((1024, 64), torch.bfloat16)  # reuses the hole, zero-filled again
+    assert float(a2.abs().sum()) == 0.0
+    for t in (a2, b, views[0]):
+        heap.free(t)
+    heap.barrier_all()
+    torch.cuda.synchronize()
+    heap.check_status()
+
+
+def test_bounded_wait_reports_timeout_instead_of_hanging(dist1):
+    """A wait on a flag that nobody sets must come back with an error status."""
+    from triton_distributed_b200 import _lib
+    from triton_distributed_b200.runtime.heap import SymmTimeoutError, get_heap
+    heap = get_heap()
+    flags = heap.create_tensor((32,), torch.int32)
+    ok = torch.ones(1, dtype=torch.int32, device="cuda")
+    heap.set_timeout_ms(50)
+    try:
+        _lib.call("b200_test_wait", heap.ctx, _lib.ptr(flags), 4, 1, _lib.ptr(ok), _lib.stream_ptr())
+        torch.cuda.synchronize()
+        assert int(ok.item()) == 0
+        with pytest.raises(SymmTimeoutError):
+            heap.check_status("wait probe")
+        # the context is still usable and a satisfied wait succeeds
+        flags.fill_(1)
+        _lib.call("b200_test_wait", heap.ctx, _lib.ptr(flags), 4, 1, _lib.ptr(ok), _lib.stream_ptr())
+        torch.cuda.synchronize()
+        assert int(ok.item()) == 1
+        heap.check_status()
+    finally:
+        heap.set_timeout_ms(10000)
+        heap.free(flags)
+
+
+def test_grid_barrier_rounds(dist1):
+    from triton_distributed_b200 import _lib
+    from triton_distributed_b200.runtime.heap import get_heap
+    heap = get_heap()
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    bad = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ctas, rounds, base = 64, 20, 0
+    for _ in range(3):
+        acc = torch.zeros(rounds, dtype=torch.int32, device="cuda")
+        _lib.call("b200_test_grid_barrier", heap.ctx, _lib.ptr(counter), _lib.ptr(acc), rounds, ctas,
+                  ctypes.c_uint32(base), _lib.ptr(bad), _lib.stream_ptr())
+        base += rounds
+    torch.cuda.synchronize()
+    assert int(bad.item()) == 0
+    heap.check_status()
+
+
+@pytest.mark.parametrize("Mr,N,K", [(256, 512, 256), (1000, 776, 520), (64, 256, 128)])
+def test_ag_gemm_world1(dist1, Mr, N, K):
+    from triton_distributed_b200.kernels.nvidia import ag_gemm, create_ag_gemm_context
+    from triton_distributed_b200.runtime.heap import get_heap
+    torch.manual_seed(0)
+    a = torch.randn(Mr, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    ctx = create_ag_gemm_context(a, b, 0, 1, max_M=1024)
+    for it in range(3):  # epochs / parity buffers across calls
+        a2 = a * (it + 1)
+        c = ag_gemm(a2, b, ctx)
+        torch.cuda.synchronize()
+        get_heap().check_status("ag_gemm")
+        torch.testing.assert_close(c.float(), a2.float() @ b.float().t(), rtol=2e-2, atol=2e-2 * (it + 1))
+    assert ctx.phase == 3
+    ctx.finalize()
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (1000, 776, 520), (8, 256, 1024)])
+def test_gemm_rs_world1(dist1, M, N, K):
+    from triton_distributed_b200.kernels.nvidia import create_gemm_rs_context, gemm_rs
+    from triton_distributed_b200.runtime.heap import get_heap
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    ctx = create_gemm_rs_context(1024, N, 0, 1, 1, torch.bfloat16)
+    for it in range(3):
+        out = gemm_rs(a, b, ctx)
+        torch.cuda.synchronize()
+        get_heap().check_status("gemm_rs")
+        torch.testing.assert_close(out.float(), a.float() @ b.float().t(), rtol=2e-2, atol=2e-2)
+    ctx.finalize()
+
+
+@pytest.mark.parametrize("method", ["one_shot", "two_shot", "double_tree"])
+def test_allreduce_world1(dist1, method):
+    from triton_distributed_b200.kernels.allreduce import to_allreduce_method
+    from triton_distributed_b200.kernels.nvidia import all_reduce, all_reduce_rmsnorm, create_allreduce_ctx
+    from triton_distributed_b200.runtime.heap import get_heap
+    ctx = create_allreduce_ctx(1 << 20, 0, 1, 1)
+    for n in (8, 4096, 300000):  # the last one is chunked
+        x = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+        y = all_reduce(x, None, to_allreduce_method(method), ctx)
+        torch.cuda.synchronize()
+        get_heap().check_status("all_reduce")
+        assert torch.equal(x, y)
+    x = torch.randn(8, 5120, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn_like(x)
+    g = torch.randn(5120, device="cuda", dtype=torch.bfloat16)
+    res0 = res.clone()
+    y, h = all_reduce_rmsnorm(x, res, g, 1e-6, ctx, to_allreduce_method(method))
+    torch.cuda.synchronize()
+    get_heap().check_status("all_reduce_rmsnorm")
+    href = (x.float() + res0.float()).to(torch.bfloat16)
+    torch.testing.assert_close(h, href)
+    hf = href.float()
+    torch.testing.assert_close(y.float(), hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-6) * g.float(),
+                               rtol=2e-2, atol=2e-2)
+    ctx.finalize()
+
+
+@pytest.mark.parametrize("mode", ["pull", "push2d", "push2d_ll"])
+def test_fast_allgather_world1(dist1, mode):
+    from triton_distributed_b200.kernels.nvidia import create_fast_allgather_context, fast_allgather
+    from triton_distributed_b200.runtime.heap import get_heap
+    heap = get_heap()
+    ctx = create_fast_allgather_context(0, 0, 1, 1, max_buffer_size=1 << 20)
+    buf = heap.create_tensor((4096,), torch.float32)
+    buf.copy_(torch.arange(4096, device="cuda", dtype=torch.float32))
+    fast_allgather(buf, ctx, mode=mode)
+    torch.cuda.synchronize()
+    heap.check_status("fast_allgather")
+    assert torch.equal(buf, torch.arange(4096, device="cuda", dtype=torch.float32))
+    heap.free(buf)
+    ctx.finalize()

@@ -1,0 +1,168 @@
+"""GPU numerics of the single-GPU kernels against plain PyTorch fp32 references."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref_mm(a, b):
+    return a.float() @ b.float().t()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (1000, 776, 520), (4096, 1024, 2048), (64, 8, 128)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gemm_matches_fp32_reference(M, N, K, dtype):
+    from triton_distributed_b200 import ops
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda", dtype=dtype)
+    b = torch.randn(N, K, device="cuda", dtype=dtype) * 0.05
+    c = ops.gemm(a, b)
+    torch.cuda.synchronize()
+    ref = _ref_mm(a, b)
+    torch.testing.assert_close(c.float(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 1280, 5120), (8, 5120, 1024), (16, 384, 4096), (33, 1000, 520),
+                                   (128, 512, 1024), (256, 256, 512)])
+def test_gemm_skinny(M, N, K):
+    from triton_distributed_b200 import ops
+    torch.manual_seed(1)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    for splits in (0, 1, 3):
+        y = ops.gemm_skinny(x, w, splits=splits)
+        torch.cuda.synchronize()
+        torch.testing.assert_close(y.float(), _ref_mm(x, w), rtol=2e-2, atol=2e-2)
+    # the scratch must be left clean: a second call gives the same answer
+    y2 = ops.gemm_skinny(x, w)
+    torch.testing.assert_close(y2.float(), _ref_mm(x, w), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("M,I,K", [(8, 3200, 5120), (4, 256, 128), (40, 1000, 520)])
+def test_gemm_skinny_swiglu(M, I, K):
+    from triton_distributed_b200 import ops
+    torch.manual_seed(2)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(2 * I, K, device="cuda", dtype=torch.bfloat16) * 0.03
+    y = ops.gemm_skinny(x, w, swiglu=True)
+    gu = _ref_mm(x, w)
+    ref = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    torch.testing.assert_close(y.float(), ref, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("rows,hidden", [(8, 5120), (3, 128), (1000, 8192), (17, 16384)])
+def test_rmsnorm(rows, hidden):
+    from triton_distributed_b200 import ops
+    torch.manual_seed(3)
+    x = torch.randn(rows, hidden, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn(hidden, device="cuda", dtype=torch.bfloat16)
+    y = ops.rmsnorm(x, g, 1e-6)
+    xf = x.float()
+    ref = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * g.float()
+    torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
+    res = torch.randn_like(x)
+    res0 = res.clone()
+    y2 = ops.rmsnorm(x, g, 1e-6, residual=res)
+    h = (x.float() + res0.float()).to(torch.bfloat16)
+    torch.testing.assert_close(res, h)
+    hf = h.float()
+    ref2 = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-6) * g.float()
+    torch.testing.assert_close(y2.float(), ref2, rtol=2e-2, atol=2e-2)
+
+
+def _rope_ref(x, pos, theta=1e6):
+    # x [T, H, 128] fp32, neox style
+    D = x.shape[-1]
+    inv = 1.0 / (theta ** (torch.arange(0, D, 2, device=x.device, dtype=torch.float32) / D))
+    ang = pos.float()[:, None] * inv[None, :]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    x1, x2 = x[..., : D // 2], x[..., D // 2:]
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1)
+
+
+def test_qk_norm_rope_and_cache_write():
+    from triton_distributed_b200 import ops
+    torch.manual_seed(4)
+    T, Hq, Hkv, D = 37, 8, 2, 128
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
+    pos = torch.randint(0, 4000, (T,), device="cuda", dtype=torch.int32)
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2, device="cuda", dtype=torch.float32) / D))
+    ang = torch.arange(4096, device="cuda", dtype=torch.float32)[:, None] * inv[None, :]
+    cos_sin = torch.cat([ang.cos(), ang.sin()], -1).contiguous()
+    qg = torch.randn(D, device="cuda", dtype=torch.bfloat16)
+    kg = torch.randn(D, device="cuda", dtype=torch.bfloat16)
+    slots = torch.randperm(64, device="cuda")[:T].to(torch.int64)
+    kc = torch.zeros(64, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    q = ops.qk_norm_rope(qkv, pos, cos_sin, Hq, Hkv, kc, vc, slots, qg, kg, 1e-6)
+    x = qkv.float().view(T, Hq + 2 * Hkv, D)
+
+    def norm(v, g):
+        return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-6) * g.float()).to(torch.bfloat16).float()
+
+    q_ref = _rope_ref(norm(x[:, :Hq], qg), pos)
+    k_ref = _rope_ref(norm(x[:, Hq:Hq + Hkv], kg), pos)
+    torch.testing.assert_close(q.float(), q_ref, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(kc[slots].float(), k_ref, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(vc[slots], qkv.view(T, -1, D)[:, Hq + Hkv:])
+
+
+def test_silu_mul_and_topk():
+    from triton_distributed_b200 import ops
+    torch.manual_seed(5)
+    x = torch.randn(19, 2 * 1536, device="cuda", dtype=torch.bfloat16)
+    y = ops.silu_mul(x)
+    ref = torch.nn.functional.silu(x[:, :1536].float()) * x[:, 1536:].float()
+    torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
+    logits = torch.randn(77, 256, device="cuda", dtype=torch.float32)
+    ids, w = ops.topk_softmax(logits, 8)
+    pw, pi = torch.topk(torch.softmax(logits, -1), 8, dim=-1)
+    assert torch.equal(ids.long(), pi)
+    torch.testing.assert_close(w, pw, rtol=1e-4, atol=1e-6)
+
+
+def _paged_attn_ref(q, kc, vc, kv_lens, bt, scale, soft_cap=0.0):
+    B, Hq, D = q.shape
+    page, Hkv = kc.shape[1], kc.shape[2]
+    G = Hq // Hkv
+    out = torch.zeros(B, Hq, D, device=q.device)
+    lse = torch.full((B, Hq), -float("inf"), device=q.device)
+    for b in range(B):
+        L = int(kv_lens[b])
+        if L == 0:
+            continue
+        nb = (L + page - 1) // page
+        k = kc[bt[b, :nb].long()].reshape(-1, Hkv, D)[:L].float()
+        v = vc[bt[b, :nb].long()].reshape(-1, Hkv, D)[:L].float()
+        k = k.repeat_interleave(G, dim=1)
+        v = v.repeat_interleave(G, dim=1)
+        s = torch.einsum("hd,lhd->hl", q[b].float(), k) * scale
+        if soft_cap > 0:
+            s = soft_cap * torch.tanh(s / soft_cap)
+        lse[b] = torch.logsumexp(s, -1)
+        out[b] = torch.einsum("hl,lhd->hd", torch.softmax(s, -1), v)
+    return out, lse
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,page,max_len,splits,soft_cap", [
+    (2, 8, 1, 16, 300, 1, 0.0), (3, 64, 8, 1, 777, 4, 0.0), (1, 32, 4, 64, 4096, 8, 30.0), (4, 16, 16, 32, 130, 3, 0.0),
+    (2, 40, 2, 16, 500, 2, 0.0)])
+def test_paged_decode_attention(B, Hq, Hkv, page, max_len, splits, soft_cap):
+    from triton_distributed_b200 import ops
+    torch.manual_seed(6)
+    D = 128
+    nblk_per = (max_len + page - 1) // page
+    nblocks = B * nblk_per + 3
+    kc = torch.randn(nblocks, page, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn_like(kc)
+    perm = torch.randperm(nblocks, device="cuda")[: B * nblk_per].to(torch.int32).view(B, nblk_per)
+    kv_lens = torch.randint(1, max_len + 1, (B,), device="cuda", dtype=torch.int32)
+    kv_lens[0] = max_len
+    q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    out, lse = ops.decode_attention(q, kc, vc, kv_lens, perm, scale, soft_cap, splits, return_lse=True)
+    ref, ref_lse = _paged_attn_ref(q, kc, vc, kv_lens, perm, scale, soft_cap)
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(lse, ref_lse, rtol=1e-2, atol=1e-2)

@@ -1,0 +1,103 @@
+"""In-tree build of the native library (``lib/libb200dist.so``) for sm_100a.
+
+Every ``.cu`` / ``.cc`` under ``csrc/`` is compiled with nvcc into ``build/`` and linked into one
+shared object next to the Python package, so that a checkout is self-contained (no JIT cache).
+Compilation is incremental (source / header mtimes) and parallel.
+
+Role in the reference: CMake + setup.py building ``libtriton_distributed.so`` and the Triton
+backend (``CMakeLists.txt:15-26``, ``csrc/lib/CMakeLists.txt:47``, ``python/setup.py``).
+
+Usage: ``python -m triton_distributed_b200.build [--force] [--verbose]``
+"""
+from __future__ import annotations
+
+import argparse
+import concurrent.futures
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+BUILD = PKG.parent / "build" / "b200dist"
+LIB_DIR = PKG / "lib"
+LIB_PATH = LIB_DIR / "libb200dist.so"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr",
+    "-Xcompiler", "-fPIC",
+    "-Xcompiler", "-fvisibility=hidden",
+    "-cudart", "static",
+    "-x", "cu",
+    "-I", str(CSRC / "include"),
+]
+
+
+def _nvcc() -> str:
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found; the native library cannot be built")
+    return exe
+
+
+def sources() -> list[Path]:
+    out = sorted(list(CSRC.glob("runtime/*.cc")) + list(CSRC.glob("runtime/*.cu")) + list(CSRC.glob("kernels/*.cu")))
+    return out
+
+
+def _headers_mtime() -> float:
+    return max((h.stat().st_mtime for h in (CSRC / "include").rglob("*") if h.is_file()), default=0.0)
+
+
+def _compile(src: Path, obj: Path, verbose: bool, ptxas_v: bool) -> tuple[Path, str]:
+    cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+    if ptxas_v:
+        cmd += ["-Xptxas", "-v"]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {src.name}:\n{proc.stdout}\n{proc.stderr}")
+    return src, proc.stderr if (verbose or ptxas_v) else ""
+
+
+def build(force: bool = False, verbose: bool = False, ptxas_v: bool = False, jobs: int | None = None) -> Path:
+    """Compile what is out of date and link the shared library. Returns its path."""
+    BUILD.mkdir(parents=True, exist_ok=True)
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    hdr_time = max(_headers_mtime(), Path(__file__).stat().st_mtime)
+    todo, objs = [], []
+    for src in sources():
+        obj = BUILD / (src.parent.name + "_" + src.stem + ".o")
+        objs.append(obj)
+        if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_time):
+            todo.append((src, obj))
+    if todo:
+        with concurrent.futures.ThreadPoolExecutor(max_workers=jobs or min(8, os.cpu_count() or 4)) as ex:
+            futs = [ex.submit(_compile, s, o, verbose, ptxas_v) for s, o in todo]
+            for f in concurrent.futures.as_completed(futs):
+                src, log = f.result()
+                if verbose or ptxas_v:
+                    print(f"[build] {src.name}\n{log}", file=sys.stderr)
+    if todo or not LIB_PATH.exists():
+        cmd = [_nvcc(), "-shared", "-cudart", "static", "-gencode", "arch=compute_100a,code=sm_100a",
+               "-o", str(LIB_PATH), *map(str, objs), "-lpthread", "-ldl", "-lrt"]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
+    return LIB_PATH
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--ptxas-v", action="store_true", help="print registers / spills / shared memory per kernel")
+    args = ap.parse_args()
+    print(build(force=args.force, verbose=args.verbose, ptxas_v=args.ptxas_v))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,266 @@
+// Decode-time GEMM for few tokens (M <= 256): C[M,N] = X[M,K] * W[N,K]^T, optionally with the SwiGLU
+// gate fused (W = [gate; up], C[M, N/2] = silu(X gate^T) * (X up^T)).
+//
+// With M this small the op is a stream of the weight matrix through the SM, so the kernel is built
+// to keep HBM busy rather than the tensor cores:
+//   * swap-AB: the 128 weight rows of a tile are the M side of tcgen05.mma (M128, K16) and the tokens,
+//     padded to a multiple of 16, are the N side, so no tensor-core rows are wasted on padding and the
+//     weights are read exactly once;
+//   * split-K over gridDim.y so that N/128 tiles x splits covers all SMs; each CTA runs a deep TMA ring
+//     (up to 12 stages, ~190 KB in flight per SM);
+//   * partial sums meet in an fp32 scratch tile through red.global.add; the CTA that takes the last
+//     ticket of a tile converts (and applies SwiGLU), writes C, and re-zeroes scratch and ticket, so the
+//     scratch is clean for the next launch without a memset.
+// The tokens are the TMEM columns, so an epilogue thread owns one output feature for all tokens and a
+// warp writes 32 consecutive features of one token: coalesced without a shared-memory transpose.
+//
+// Role in the reference: the cuBLAS F.linear calls of the AllReduce forward mode
+// (python/triton_dist/layers/nvidia/tp_mlp.py:177-191, tp_attn.py:240-271) and the unfused
+// act_fn(gate) * up (tp_mlp.py:159-160).
+#include "b200/host.h"
+#include "b200/primitives.cuh"
+#include "b200/tcgen05.cuh"
+
+#include <cstring>
+
+namespace b200 {
+
+constexpr int kSkBN = 128;  // weight rows per tile
+constexpr int kSkBK = 64;
+constexpr int kSkWBytes = kSkBN * kSkBK * 2;
+constexpr int kSkMaxStages = 12;
+constexpr int kSkSmemBudget = 225 * 1024;
+
+struct SkinnyParams {
+  int M, N, K;        // N = weight rows per projection (the output features)
+  int MB;             // tokens padded to a multiple of 16
+  int stages;
+  int stage_bytes;
+  int kb_per_split;
+  int up_row0;        // dual: first row of the `up` projection inside W
+  int bf16;
+  void* C;
+  int ldc;
+  float* scratch;     // [tiles][dual ? 2 : 1][MB][128] fp32, zero on entry and on exit
+  uint32_t* tickets;  // [tiles], zero on entry and on exit
+};
+
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+
+template <bool kDual>
+__global__ void __launch_bounds__(256, 1)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const SkinnyParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full_bar[kSkMaxStages];
+  __shared__ uint64_t empty_bar[kSkMaxStages];
+  __shared__ uint64_t done_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ uint32_t abort_word;
+  __shared__ uint32_t last_flag;
+  volatile uint32_t* abort_flag = &abort_word;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y;
+  const int num_kb = (p.K + kSkBK - 1) / kSkBK;
+  const int kb0 = split * p.kb_per_split;
+  const int kb1 = min(num_kb, kb0 + p.kb_per_split);
+  const int nkb = max(0, kb1 - kb0);
+  constexpr int kW = kDual ? 2 : 1;
+  const uint32_t tmem_cols = kW * p.MB <= 32 ? 32 : kW * p.MB <= 64 ? 64 : kW * p.MB <= 128 ? 128 : kW * p.MB <= 256 ? 256 : 512;
+  const uint64_t timeout_ns = 4000000000ull;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < p.stages; ++i) {
+      mbar_init(full_bar + i, 1);
+      mbar_init(empty_bar + i, 1);
+    }
+    mbar_init(&done_bar, 1);
+    abort_word = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 2) tmem_alloc(&tmem_slot, tmem_cols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      uint32_t stage = 0, phase = 0;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, timeout_ns)) break;
+        uint8_t* s = smem + stage * p.stage_bytes;
+        mbar_expect_tx(full_bar + stage, p.stage_bytes);
+        tma_load_2d(s, &tmW, full_bar + stage, kb * kSkBK, tile * kSkBN);
+        if (kDual) tma_load_2d(s + kSkWBytes, &tmW, full_bar + stage, kb * kSkBK, p.up_row0 + tile * kSkBN);
+        tma_load_2d(s + kW * kSkWBytes, &tmX, full_bar + stage, kb * kSkBK, 0);
+        if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      const uint32_t idesc = umma_idesc_f16(kSkBN, p.MB, p.bf16 != 0);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(full_bar + stage, phase, abort_flag, timeout_ns)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t s = smem_u32(smem + stage * p.stage_bytes);
+        const uint64_t dw = umma_desc_sw128_kmajor(s);
+        const uint64_t dx = umma_desc_sw128_kmajor(s + kW * kSkWBytes);
+#pragma unroll
+        for (int k = 0; k < kSkBK / 16; ++k) {
+          const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
+          umma_f16(tmem_base, dw + 2 * k, dx + 2 * k, idesc, accum);
+          if (kDual) umma_f16(tmem_base + p.MB, umma_desc_sw128_kmajor(s + kSkWBytes) + 2 * k, dx + 2 * k, idesc, accum);
+        }
+        umma_commit(empty_bar + stage);
+        if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
+      }
+      if (ok) umma_commit(&done_bar);
+    }
+    __syncwarp();
+  } else if (warp >= 4) {
+    const int w = warp - 4;
+    const int et = threadIdx.x - 128;  // 0..127 == feature index inside the tile
+    const int n = tile * kSkBN + et;
+    bool ok = nkb > 0 ? mbar_wait(&done_bar, 0, abort_flag, timeout_ns) : true;
+    tc_fence_after_sync();
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(w * 32) << 16);
+    float* scratch = p.scratch + static_cast<size_t>(tile) * kW * p.MB * kSkBN;
+    auto store_out = [&](int m, float g, float u) {
+      if (m < p.M && n < p.N) {
+        const float v = kDual ? g / (1.f + __expf(-g)) * u : g;
+        if (p.bf16) static_cast<__nv_bfloat16*>(p.C)[static_cast<size_t>(m) * p.ldc + n] = __float2bfloat16(v);
+        else static_cast<__half*>(p.C)[static_cast<size_t>(m) * p.ldc + n] = __float2half(v);
+      }
+    };
+    if (ok && nkb > 0) {
+      for (int c0 = 0; c0 < p.MB; c0 += 16) {
+        uint32_t g[16], u[16];
+        tmem_ld_32x16(taddr + c0, g);
+        if (kDual) tmem_ld_32x16(taddr + p.MB + c0, u);
+        tmem_ld_wait();
+        if (nsplit == 1) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) store_out(c0 + j, __uint_as_float(g[j]), kDual ? __uint_as_float(u[j]) : 0.f);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (c0 + j < p.M) {
+              atomicAdd(scratch + static_cast<size_t>(c0 + j) * kSkBN + et, __uint_as_float(g[j]));
+              if (kDual) atomicAdd(scratch + static_cast<size_t>(p.MB + c0 + j) * kSkBN + et, __uint_as_float(u[j]));
+            }
+          }
+        }
+      }
+    }
+    if (nsplit > 1) {
+      // ticket: the last CTA of this tile finishes it and leaves scratch + ticket zeroed
+      __threadfence();
+      epi_bar();
+      if (et == 0) {
+        const uint32_t t = atomicAdd(p.tickets + tile, 1u);
+        last_flag = (t == static_cast<uint32_t>(nsplit - 1)) ? 1u : 0u;
+      }
+      epi_bar();
+      if (last_flag) {
+        __threadfence();
+        for (int m = 0; m < p.M; ++m) {
+          float* gs = scratch + static_cast<size_t>(m) * kSkBN + et;
+          const float g = __ldcg(gs);
+          float u = 0.f;
+          __stcg(gs, 0.f);
+          if (kDual) {
+            float* us = scratch + static_cast<size_t>(p.MB + m) * kSkBN + et;
+            u = __ldcg(us);
+            __stcg(us, 0.f);
+          }
+          store_out(m, g, u);
+        }
+        if (et == 0) p.tickets[tile] = 0;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+template <bool kDual>
+static int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const SkinnyParams& p, dim3 grid, int smem,
+                         cudaStream_t stream) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  B200_CHECK_CUDA(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    B200_CHECK_CUDA(cudaFuncSetAttribute(gemm_skinny_kernel<kDual>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSkSmemBudget + 1024));
+    configured[dev & 63] = true;
+  }
+  gemm_skinny_kernel<kDual><<<grid, 256, smem, stream>>>(tw, tx, p);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// Scratch floats / tickets needed for a call (independent of the split count).
+B200_API long long b200_gemm_skinny_scratch_floats(int M, int N, int dual) {
+  const int MB = (M + 15) / 16 * 16;
+  const long long tiles = (N + kSkBN - 1) / kSkBN;
+  return tiles * (dual ? 2 : 1) * MB * kSkBN;
+}
+
+// X [M, K] (row pitch ldx), W [Nw, K] (row pitch ldw), C [M, N] (row pitch ldc).
+// dual == 0: N = Nw. dual == 1: W = [gate (N rows); up (N rows)], C = silu(X gate^T) * (X up^T).
+// scratch / tickets: zero-initialised once by the caller; every call leaves them zeroed.
+// splits <= 0 lets the launcher choose.
+B200_API int b200_gemm_skinny(const void* X, const void* W, void* C, int M, int N, int K, int ldx, int ldw, int ldc,
+                              int dual, int dtype, float* scratch, uint32_t* tickets, int splits, void* stream) {
+  B200_REQUIRE(dtype == kBF16 || dtype == kF16, "gemm_skinny supports bf16/f16");
+  B200_REQUIRE(M >= 1 && M <= 256, "gemm_skinny handles 1..256 tokens, got %d", M);
+  B200_REQUIRE(K % 8 == 0, "K (%d) must be a multiple of 8", K);
+  SkinnyParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K;
+  p.MB = (M + 15) / 16 * 16;
+  B200_REQUIRE(!dual || p.MB <= 128, "fused SwiGLU handles at most 128 tokens");
+  const int kw = dual ? 2 : 1;
+  p.stage_bytes = kw * kSkWBytes + p.MB * 128;
+  p.stages = kSkSmemBudget / p.stage_bytes;
+  if (p.stages > kSkMaxStages) p.stages = kSkMaxStages;
+  B200_REQUIRE(p.stages >= 2, "tile does not fit in shared memory");
+  p.up_row0 = N;
+  p.bf16 = dtype == kBF16;
+  p.C = C; p.ldc = ldc; p.scratch = scratch; p.tickets = tickets;
+  const int tiles = (N + kSkBN - 1) / kSkBN;
+  const int num_kb = (K + kSkBK - 1) / kSkBK;
+  if (splits <= 0) {
+    const int sms = sm_count();
+    splits = (sms + tiles - 1) / tiles;          // cover the machine at least once
+    const int max_by_k = num_kb / 4 > 0 ? num_kb / 4 : 1;  // keep >= 4 k-blocks per CTA
+    if (splits > max_by_k) splits = max_by_k;
+  }
+  if (splits > num_kb) splits = num_kb;
+  if (splits < 1) splits = 1;
+  p.kb_per_split = (num_kb + splits - 1) / splits;
+  splits = (num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty splits
+  B200_REQUIRE(splits == 1 || (scratch && tickets), "split-K needs scratch and tickets");
+  CUtensorMap tw, tx;
+  int rc = make_tma_2d(&tw, W, dtype, static_cast<uint64_t>(kw) * N, K, ldw, kSkBN, kSkBK, true);
+  if (rc != kOk) return rc;
+  rc = make_tma_2d(&tx, X, dtype, M, K, ldx, p.MB, kSkBK, true);
+  if (rc != kOk) return rc;
+  const int smem = p.stages * p.stage_bytes + 1024;
+  dim3 grid(tiles, splits);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return dual ? launch_skinny<true>(tw, tx, p, grid, smem, s) : launch_skinny<false>(tw, tx, p, grid, smem, s);
+}

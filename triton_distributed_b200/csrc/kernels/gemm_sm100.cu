@@ -1,0 +1,559 @@
+// Persistent warp-specialised tcgen05 GEMM for sm_100a with three modes that share one mainloop:
+//
+//   PLAIN  C[M,N] = A[M,K] * B[N,K]^T                      (gemm_persistent of the reference,
+//                                                           python/triton_dist/kernels/nvidia/allgather_gemm.py:660-744)
+//   AG     C[M,N/r] = allgather(A)[M,K] * B[N/r,K]^T       (ag_gemm, allgather_gemm.py:145-251, 534-657)
+//   RS     out[M/r,N] = reduce_scatter(A[M,K/r] * B[N,K/r]^T)   (gemm_rs with fuse_scatter,
+//                                                           gemm_reduce_scatter.py:130-259, 515-590)
+//
+// One CTA per SM, 256 threads:
+//   warp 0      TMA producer: 128x64 A tile + 256x64 B tile per stage, 128-byte swizzle, 4 stages
+//   warp 1      one elected thread issues tcgen05.mma (M128 N256 K16, bf16/f16 -> f32) into TMEM;
+//               two 256-column accumulators so the epilogue of tile i overlaps the mainloop of i+1
+//   warps 2-3   AG mode: communication warps. They copy this rank's shard into the symmetric
+//               gather buffer, publish it, and pull the peers' shards over NVLink with 16-byte
+//               loads in the order in which the tile schedule needs them; arrival is tracked per
+//               128-row block and the producer warp waits (bounded) on that block's flag before
+//               its first TMA load of the block. TMA only ever reads this GPU's own memory.
+//   warps 4-7   epilogue: tcgen05.ld -> convert -> swizzled smem staging -> 128-byte row segments.
+//               RS mode stores each row into the owner rank's slot [src][row][col] through its peer
+//               mapping and bumps the owner's per-(src, block) row counter with a release.
+//   RS mode ends with a reduce phase in which all threads sum the `world` slots of this rank's
+//   rows (fp32) as the blocks complete.
+//
+// All cross-rank and cross-CTA waits are bounded; on expiry the kernel records a status, unwinds
+// every role through a CTA-wide abort flag, frees its TMEM and returns.
+#include "b200/host.h"
+#include "b200/primitives.cuh"
+#include "b200/tcgen05.cuh"
+
+#include <cstring>
+
+namespace b200 {
+
+constexpr int kBM = 128;
+constexpr int kBN = 256;
+constexpr int kBK = 64;
+constexpr int kStages = 4;
+constexpr int kABytes = kBM * kBK * 2;
+constexpr int kBBytes = kBN * kBK * 2;
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kEpiBytes = 4 * 32 * 128;  // 4 warps x 32 rows x 64 bf16
+constexpr int kGemmSmem = kStages * kStageBytes + kEpiBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kTmemCols = 512;
+constexpr int kCommThreads = 64;
+constexpr int kCommRows = 8;  // rows per communication chunk
+
+enum GemmMode : int { kPlain = 0, kAG = 1, kRS = 2 };
+
+struct GemmParams {
+  int M, N, K;
+  int tiles_m, tiles_n, group_m, m_rot;
+  int bf16;          // 1 = bf16, 0 = f16 (inputs and output)
+  void* C;           // PLAIN / AG: [M, ldc]
+  int ldc;
+  // ---- AG ----
+  const void* a_local;   // this rank's shard [Mr, K]
+  void* ag_buf[2];       // symmetric [world * Mr_cap, K], double-buffered by epoch parity
+  uint32_t* ready;       // symmetric u32[world]: ready[s] == epoch once rank s published its shard
+  uint32_t* blk_cnt;     // local u32[tiles_m cap]: rows of the block that have landed
+  uint32_t* blk_flag;    // local u32[tiles_m cap]: == epoch once the block is complete
+  uint32_t* sync;        // local u32[4]: [0] epoch, [1] done-CTA counter, [2] local-chunk counter
+  int Mr;                // rows per rank (M / world)
+  // ---- RS ----
+  void* slots[2];        // symmetric [world][Mr_cap][N], double-buffered by epoch parity
+  uint32_t* rs_cnt;      // symmetric u32[world][rs_blocks]: rows received from src for block j
+  uint32_t* rs_base;     // local u32[world][rs_blocks]: counter value before this call
+  int Mr_cap;
+  int rs_blocks;
+  void* out;             // [Mr, N]
+};
+
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int t, int& m_blk, int& n_blk) {
+  const int per_group = p.group_m * p.tiles_n;
+  const int group = t / per_group;
+  const int first_m = group * p.group_m;
+  const int gsize = min(p.group_m, p.tiles_m - first_m);
+  const int in_group = t - group * per_group;
+  const int mi = first_m + in_group % gsize;
+  n_blk = in_group / gsize;
+  m_blk = mi + p.m_rot;
+  if (m_blk >= p.tiles_m) m_blk -= p.tiles_m;
+}
+
+__device__ __forceinline__ void comm_bar() { asm volatile("bar.sync 1, 64;" ::: "memory"); }
+
+// Adds `nrows` landed rows [row0, row0 + nrows) to the arrival counters of the 128-row blocks they
+// touch; whoever completes a block publishes its flag. Called by one thread after the chunk's
+// stores were ordered before it (comm_bar) and fenced for the async proxy by their writers.
+__device__ __forceinline__ void publish_rows(const GemmParams& p, int row0, int nrows, uint32_t epoch) {
+  int r = row0;
+  const int end = row0 + nrows;
+  while (r < end) {
+    const int b = r / kBM;
+    const int bend = min(end, (b + 1) * kBM);
+    const int n = bend - r;
+    const int rows_in_block = min(kBM, p.M - b * kBM);
+    const uint32_t old = atom_add_acqrel_gpu(p.blk_cnt + b, static_cast<uint32_t>(n));
+    if (static_cast<int>(old) + n == rows_in_block) {
+      p.blk_cnt[b] = 0;
+      st_release_gpu(p.blk_flag + b, epoch);
+    }
+    r = bend;
+  }
+}
+
+// Copy `nrows` rows of `row_bytes` from src to dst with the 64 communication threads, eight
+// independent 16-byte loads in flight per thread.
+__device__ __forceinline__ void comm_copy(uint8_t* dst, const uint8_t* src, size_t nbytes, int ct) {
+  const size_t nvec = nbytes / 16;
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+  uint4* d = reinterpret_cast<uint4*>(dst);
+  size_t i = ct;
+  for (; i + 7 * kCommThreads < nvec; i += 8 * kCommThreads) {
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = ld_v4_relaxed_sys(s + i + u * kCommThreads);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) st_v4(d + i + u * kCommThreads, v[u]);
+  }
+  for (; i < nvec; i += kCommThreads) st_v4(d + i, ld_v4_relaxed_sys(s + i));
+}
+
+template <int kMode>
+__global__ void __launch_bounds__(256, 1)
+gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+                  const __grid_constant__ CUtensorMap tmB, const GemmParams p, const SymmCtx ctx) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* epi_smem = smem + kStages * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + kEpiBytes);
+  uint64_t* full_bar = bars;                 // [kStages]
+  uint64_t* empty_bar = bars + kStages;      // [kStages]
+  uint64_t* tfull_bar = bars + 2 * kStages;  // [2]
+  uint64_t* tempty_bar = tfull_bar + 2;      // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* bcast = tmem_slot + 2;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (p.K + kBK - 1) / kBK;
+  const uint64_t pipe_timeout = ctx.timeout_ns;
+
+  uint32_t epoch = 1;
+  if (kMode != kPlain) epoch = epoch_begin(p.sync);
+  const int par = epoch & 1;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(full_bar + i, 1);
+      mbar_init(empty_bar + i, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tfull_bar + i, 1);
+      mbar_init(tempty_bar + i, 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA0);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 2) tmem_alloc(tmem_slot, kTmemCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      const CUtensorMap* tmA = (kMode == kAG && par) ? &tmA1 : &tmA0;
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(p, t, m_blk, n_blk);
+        if (kMode == kAG) {
+          ok = wait_flag<WaitCmp::EQ, false>(ctx, p.blk_flag + m_blk, epoch, m_blk, __LINE__);
+          if (!ok) { *abort_flag = 1; break; }
+          fence_proxy_async();
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, pipe_timeout)) { ok = false; break; }
+          uint8_t* sa = smem + stage * kStageBytes;
+          mbar_expect_tx(full_bar + stage, kStageBytes);
+          tma_load_2d(sa, tmA, full_bar + stage, kb * kBK, m_blk * kBM);
+          tma_load_2d(sa + kABytes, &tmB, full_bar + stage, kb * kBK, n_blk * kBN);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = umma_idesc_f16(kBM, kBN, p.bf16 != 0);
+      uint32_t stage = 0, phase = 0, it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+        const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(tempty_bar + acc, acc_phase ^ 1, abort_flag, pipe_timeout)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kBN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar + stage, phase, abort_flag, pipe_timeout)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * kStageBytes);
+          const uint64_t da = umma_desc_sw128_kmajor(sa);
+          const uint64_t db = umma_desc_sw128_kmajor(sa + kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k)
+            umma_f16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit(empty_bar + stage);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(tfull_bar + acc);
+      }
+    }
+    __syncwarp();
+  } else if (warp < 4) {
+    // ------------------------------------------------------------------ communication warps (AG)
+    if (kMode == kAG) {
+      const int ct = threadIdx.x - 64;
+      const size_t row_bytes = static_cast<size_t>(p.K) * 2;
+      uint8_t* buf = static_cast<uint8_t*>(p.ag_buf[par]);
+      const int nch = (p.Mr + kCommRows - 1) / kCommRows;  // chunks per shard
+      const int total_chunks = nch * ctx.world;            // local shard first, then peers in ring order
+      for (int g = blockIdx.x; g < total_chunks; g += gridDim.x) {
+        const int step = g / nch;
+        const int c = g - step * nch;
+        int src = ctx.rank + step;
+        if (src >= ctx.world) src -= ctx.world;
+        const int r0 = c * kCommRows;
+        const int nrows = min(kCommRows, p.Mr - r0);
+        const size_t off = (static_cast<size_t>(src) * p.Mr + r0) * row_bytes;
+        if (step == 0) {
+          comm_copy(buf + off, static_cast<const uint8_t*>(p.a_local) + static_cast<size_t>(r0) * row_bytes,
+                    nrows * row_bytes, ct);
+        } else {
+          if (ct == 0) {
+            bool ok = wait_flag<WaitCmp::EQ, true>(ctx, p.ready + src, epoch, src, __LINE__);
+            *bcast = ok ? 1u : 0u;
+          }
+          comm_bar();
+          const bool ok = *bcast != 0u;
+          comm_bar();
+          if (!ok) break;
+          comm_copy(buf + off, symm_at(ctx, buf + off, src), nrows * row_bytes, ct);
+        }
+        fence_proxy_async();
+        comm_bar();
+        if (ct == 0) {
+          publish_rows(p, src * p.Mr + r0, nrows, epoch);
+          if (step == 0 && ctx.world > 1) {
+            // the CTA that lands the last local chunk tells every peer that this shard can be pulled
+            const uint32_t old = atom_add_acqrel_gpu(p.sync + 2, 1u);
+            if (old == static_cast<uint32_t>(nch - 1)) {
+              p.sync[2] = 0;
+              fence_acq_rel_sys();
+              for (int k = 1; k < ctx.world; ++k) {
+                int peer = ctx.rank + k;
+                if (peer >= ctx.world) peer -= ctx.world;
+                st_release_sys(symm_at(ctx, p.ready + ctx.rank, peer), epoch);
+              }
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int w = warp - 4;  // == warp % 4: the TMEM lane quarter this warp may read
+    uint8_t* stg = epi_smem + w * (32 * 128);
+    uint32_t it = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+      int m_blk, n_blk;
+      tile_coords(p, t, m_blk, n_blk);
+      const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(tfull_bar + acc, acc_phase, abort_flag, pipe_timeout)) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(w * 32) << 16) + acc * kBN;
+      const int row_base = m_blk * kBM + w * 32;
+#pragma unroll 1
+      for (int c = 0; c < kBN / 64; ++c) {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(taddr + c * 64, r0);
+        tmem_ld_32x32(taddr + c * 64 + 32, r1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t* r = j < 4 ? r0 + j * 8 : r1 + (j - 4) * 8;
+          uint4 v;
+          if (p.bf16) {
+            v.x = pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1]));
+            v.y = pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3]));
+            v.z = pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5]));
+            v.w = pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7]));
+          } else {
+            v.x = pack_f16x2(__uint_as_float(r[0]), __uint_as_float(r[1]));
+            v.y = pack_f16x2(__uint_as_float(r[2]), __uint_as_float(r[3]));
+            v.z = pack_f16x2(__uint_as_float(r[4]), __uint_as_float(r[5]));
+            v.w = pack_f16x2(__uint_as_float(r[6]), __uint_as_float(r[7]));
+          }
+          *reinterpret_cast<uint4*>(stg + lane * 128 + ((j ^ (lane & 7)) * 16)) = v;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int rr = i * 4 + (lane >> 3);
+          const int ch = lane & 7;
+          const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((ch ^ (rr & 7)) * 16));
+          const int grow = row_base + rr;
+          const int gcol = n_blk * kBN + c * 64 + ch * 8;
+          if (grow < p.M && gcol < p.N) {
+            if (kMode == kRS) {
+              const int owner = grow / p.Mr;
+              const int lrow = grow - owner * p.Mr;
+              uint8_t* slot = static_cast<uint8_t*>(p.slots[par]) +
+                              ((static_cast<size_t>(ctx.rank) * p.Mr_cap + lrow) * p.N + gcol) * 2;
+              st_v4(symm_at(ctx, slot, owner), v);
+            } else {
+              st_v4(static_cast<uint8_t*>(p.C) + (static_cast<size_t>(grow) * p.ldc + gcol) * 2, v);
+            }
+          }
+        }
+        __syncwarp();
+      }
+      // accumulator fully read: hand it back to the MMA warp
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar + acc);
+      if (kMode == kRS) {
+        // tell each owner how many of its rows this warp just delivered for this column block
+        const int r_lo = row_base, r_hi = min(row_base + 32, p.M);
+        if (r_lo < r_hi) {
+          const int o_lo = r_lo / p.Mr, o_hi = (r_hi - 1) / p.Mr;
+          const int o = o_lo + lane;
+          fence_acq_rel_sys();
+          if (o <= o_hi) {
+            const int s0 = max(r_lo, o * p.Mr), s1 = min(r_hi, (o + 1) * p.Mr);
+            const int j = m_blk - (o * p.Mr) / kBM;
+            uint32_t* cnt = p.rs_cnt + ctx.rank * p.rs_blocks + j;
+            red_add_release_sys(symm_at(ctx, cnt, o), static_cast<uint32_t>(s1 - s0));
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- RS reduce phase
+  __syncthreads();
+  bool failed = *abort_flag != 0u;
+  if (kMode == kRS && !failed) {
+    const int seg0 = ctx.rank * p.Mr;
+    const int first_blk = seg0 / kBM;
+    const int vec_per_row = p.N / 8;
+    const uint8_t* slots = static_cast<const uint8_t*>(p.slots[par]);
+    int ready_blk = -1;
+    const int ngroups = (p.Mr + 7) / 8;
+    for (int g = blockIdx.x; g < ngroups && !failed; g += gridDim.x) {
+      const int lr0 = g * 8, lr1 = min(p.Mr, lr0 + 8);
+      // rows lr0..lr1 may straddle two 128-row blocks: wait for the later one (blocks complete in order
+      // of j only approximately, so both are checked)
+      const int jb0 = (seg0 + lr0) / kBM - first_blk, jb1 = (seg0 + lr1 - 1) / kBM - first_blk;
+      for (int j = jb0; j <= jb1; ++j) {
+        if (j <= ready_blk) continue;
+        bool ok = true;
+        if (threadIdx.x < ctx.world) {
+          const int blk = first_blk + j;
+          const int s0 = max(seg0, blk * kBM), s1 = min(seg0 + p.Mr, (blk + 1) * kBM);
+          const uint32_t target = p.rs_base[threadIdx.x * p.rs_blocks + j] + static_cast<uint32_t>((s1 - s0) * p.tiles_n);
+          ok = wait_flag<WaitCmp::GE, true>(ctx, p.rs_cnt + threadIdx.x * p.rs_blocks + j, target, threadIdx.x, __LINE__);
+        }
+        if (!__syncthreads_and(ok)) { failed = true; break; }
+        ready_blk = j;
+      }
+      if (failed) break;
+      const int nvec = (lr1 - lr0) * vec_per_row;
+      for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        const int lrow = lr0 + v / vec_per_row;
+        const int col = (v - (v / vec_per_row) * vec_per_row) * 8;
+        float accv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int s = 0; s < ctx.world; ++s) {
+          const uint4 x = ld_v4_relaxed_sys(slots + ((static_cast<size_t>(s) * p.Mr_cap + lrow) * p.N + col) * 2);
+          const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = p.bf16 ? unpack_bf16x2(xs[q]) : unpack_f16x2(xs[q]);
+            accv[2 * q] += f.x;
+            accv[2 * q + 1] += f.y;
+          }
+        }
+        uint4 o;
+        if (p.bf16) {
+          o.x = pack_bf16x2(accv[0], accv[1]); o.y = pack_bf16x2(accv[2], accv[3]);
+          o.z = pack_bf16x2(accv[4], accv[5]); o.w = pack_bf16x2(accv[6], accv[7]);
+        } else {
+          o.x = pack_f16x2(accv[0], accv[1]); o.y = pack_f16x2(accv[2], accv[3]);
+          o.z = pack_f16x2(accv[4], accv[5]); o.w = pack_f16x2(accv[6], accv[7]);
+        }
+        st_v4(static_cast<uint8_t*>(p.out) + (static_cast<size_t>(lrow) * p.N + col) * 2, o);
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) tmem_dealloc(tmem_base, kTmemCols);
+  if (threadIdx.x == 0) {
+    if (*abort_flag != 0u) report_status(ctx, kStatusPipeTimeout, blockIdx.x, 0, 0, __LINE__);
+    if (kMode != kPlain) {
+      __threadfence();
+      if (atomicAdd(p.sync + 1, 1u) == gridDim.x - 1) {
+        p.sync[1] = 0;
+        if (kMode == kRS) {
+          // every rank delivered its rows of this call: advance the counter bases
+          const int seg0 = ctx.rank * p.Mr, first_blk = seg0 / kBM, last_blk = (seg0 + p.Mr - 1) / kBM;
+          for (int j = 0; j <= last_blk - first_blk; ++j) {
+            const int blk = first_blk + j;
+            const int s0 = max(seg0, blk * kBM), s1 = min(seg0 + p.Mr, (blk + 1) * kBM);
+            for (int s = 0; s < ctx.world; ++s)
+              p.rs_base[s * p.rs_blocks + j] += static_cast<uint32_t>((s1 - s0) * p.tiles_n);
+          }
+        }
+        __threadfence();
+        p.sync[0] = epoch;
+      }
+    }
+  }
+}
+
+template <int kMode>
+static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b, const GemmParams& p,
+                       const SymmCtx& ctx, int grid, cudaStream_t stream) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  B200_CHECK_CUDA(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    B200_CHECK_CUDA(cudaFuncSetAttribute(gemm_sm100_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
+    configured[dev & 63] = true;
+  }
+  gemm_sm100_kernel<kMode><<<grid, 256, kGemmSmem, stream>>>(a0, a1, b, p, ctx);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+static int fill_common(GemmParams& p, int M, int N, int K, int dtype, int group_m) {
+  B200_REQUIRE(dtype == kBF16 || dtype == kF16, "gemm supports bf16 and f16, got dtype %d", dtype);
+  B200_REQUIRE(M > 0 && N > 0 && K > 0, "empty problem %dx%dx%d", M, N, K);
+  B200_REQUIRE(K % 8 == 0 && N % 8 == 0, "K (%d) and N (%d) must be multiples of 8", K, N);
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = (M + kBM - 1) / kBM;
+  p.tiles_n = (N + kBN - 1) / kBN;
+  p.group_m = group_m > 0 ? group_m : 8;
+  p.m_rot = 0;
+  p.bf16 = dtype == kBF16;
+  return kOk;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// C[M,N] = A[M,K] * B[N,K]^T, all row-major with leading dimensions lda/ldb/ldc (elements).
+B200_API int b200_gemm(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int dtype,
+                       int max_ctas, void* stream) {
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  int rc = fill_common(p, M, N, K, dtype, 16);
+  if (rc != kOk) return rc;
+  p.C = C;
+  p.ldc = ldc;
+  CUtensorMap ta, tb;
+  rc = make_tma_2d(&ta, A, dtype, M, K, lda, kBM, kBK, true);
+  if (rc != kOk) return rc;
+  rc = make_tma_2d(&tb, B, dtype, N, K, ldb, kBN, kBK, true);
+  if (rc != kOk) return rc;
+  SymmCtx ctx;
+  memset(&ctx, 0, sizeof(ctx));
+  ctx.world = 1;
+  ctx.timeout_ns = 4000000000ull;
+  int grid = min(p.tiles_m * p.tiles_n, sm_count());
+  if (max_ctas > 0) grid = min(grid, max_ctas);
+  return launch_gemm<kPlain>(ta, ta, tb, p, ctx, grid, static_cast<cudaStream_t>(stream));
+}
+
+// AG-GEMM. a_local [Mr, K] is this rank's shard; ag_buf0/1 are the two symmetric gather buffers
+// [world * Mr, K] (rows of rank s at s * Mr); B is [N, K]; C is [world * Mr, N].
+// ready: symmetric u32[world]; blk_cnt/blk_flag: local u32[>= tiles_m]; sync: local u32[4]; all zero-initialised once.
+B200_API int b200_ag_gemm(const void* symm_ctx, const void* a_local, void* ag_buf0, void* ag_buf1, const void* B, void* C,
+                          int Mr, int N, int K, int ldb, int ldc, int dtype, uint32_t* ready, uint32_t* blk_cnt,
+                          uint32_t* blk_flag, uint32_t* sync, int group_m, int max_ctas, void* stream) {
+  SymmCtx ctx;
+  memcpy(&ctx, symm_ctx, sizeof(ctx));
+  const int M = Mr * ctx.world;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  int rc = fill_common(p, M, N, K, dtype, group_m);
+  if (rc != kOk) return rc;
+  p.C = C;
+  p.ldc = ldc;
+  p.a_local = a_local;
+  p.ag_buf[0] = ag_buf0;
+  p.ag_buf[1] = ag_buf1;
+  p.ready = ready;
+  p.blk_cnt = blk_cnt;
+  p.blk_flag = blk_flag;
+  p.sync = sync;
+  p.Mr = Mr;
+  p.m_rot = (ctx.rank * Mr) / kBM;
+  B200_REQUIRE((reinterpret_cast<uint64_t>(a_local) & 15u) == 0, "a_local must be 16-byte aligned");
+  CUtensorMap ta0, ta1, tb;
+  rc = make_tma_2d(&ta0, ag_buf0, dtype, M, K, K, kBM, kBK, true);
+  if (rc != kOk) return rc;
+  rc = make_tma_2d(&ta1, ag_buf1, dtype, M, K, K, kBM, kBK, true);
+  if (rc != kOk) return rc;
+  rc = make_tma_2d(&tb, B, dtype, N, K, ldb, kBN, kBK, true);
+  if (rc != kOk) return rc;
+  int grid = sm_count();
+  if (max_ctas > 0) grid = min(grid, max_ctas);
+  return launch_gemm<kAG>(ta0, ta1, tb, p, ctx, grid, static_cast<cudaStream_t>(stream));
+}
+
+// GEMM-RS. A [M, K] (K is this rank's K shard), B [N, K], out [M / world, N].
+// slots0/1: symmetric [world][Mr_cap][N]; rs_cnt: symmetric u32[world][rs_blocks]; rs_base: local
+// u32[world][rs_blocks]; sync: local u32[4]; all zero-initialised once.
+B200_API int b200_gemm_rs(const void* symm_ctx, const void* A, const void* B, void* out, int M, int N, int K, int lda,
+                          int ldb, int dtype, void* slots0, void* slots1, uint32_t* rs_cnt, uint32_t* rs_base,
+                          uint32_t* sync, int Mr_cap, int rs_blocks, int group_m, int max_ctas, void* stream) {
+  SymmCtx ctx;
+  memcpy(&ctx, symm_ctx, sizeof(ctx));
+  B200_REQUIRE(M % ctx.world == 0, "M (%d) must be divisible by the world size (%d)", M, ctx.world);
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  int rc = fill_common(p, M, N, K, dtype, group_m);
+  if (rc != kOk) return rc;
+  p.Mr = M / ctx.world;
+  B200_REQUIRE(p.Mr <= Mr_cap, "M / world (%d) exceeds the context capacity (%d)", p.Mr, Mr_cap);
+  B200_REQUIRE((p.Mr + kBM - 1) / kBM + 1 <= rs_blocks, "rs_blocks (%d) too small for %d rows per rank", rs_blocks, p.Mr);
+  p.slots[0] = slots0;
+  p.slots[1] = slots1;
+  p.rs_cnt = rs_cnt;
+  p.rs_base = rs_base;
+  p.sync = sync;
+  p.Mr_cap = Mr_cap;
+  p.rs_blocks = rs_blocks;
+  p.out = out;
+  p.m_rot = (((ctx.rank + 1) % ctx.world) * p.Mr) / kBM;
+  CUtensorMap ta, tb;
+  rc = make_tma_2d(&ta, A, dtype, M, K, lda, kBM, kBK, true);
+  if (rc != kOk) return rc;
+  rc = make_tma_2d(&tb, B, dtype, N, K, ldb, kBN, kBK, true);
+  if (rc != kOk) return rc;
+  int grid = sm_count();
+  if (max_ctas > 0) grid = min(grid, max_ctas);
+  return launch_gemm<kRS>(ta, ta, tb, p, ctx, grid, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,11 @@
+"""NVIDIA kernel library (exports follow ``python/triton_dist/kernels/nvidia/__init__.py:25-85``)."""
+from .allgather_gemm import ag_gemm, create_ag_gemm_context, gemm_non_persistent, gemm_persistent
+from .allreduce import all_reduce, all_reduce_rmsnorm, create_allreduce_ctx, get_auto_allreduce_method
+from .common_ops import BarrierAllContext, barrier_all_on_stream, set_signal, wait_eq
+from .flash_decode import (get_triton_combine_kv_algo_info, gqa_fwd_batch_decode, gqa_fwd_batch_decode_aot,
+                           gqa_fwd_batch_decode_intra_rank, gqa_fwd_batch_decode_intra_rank_aot,
+                           gqa_fwd_batch_decode_persistent, gqa_fwd_batch_decode_persistent_aot,
+                           kernel_gqa_fwd_batch_decode_split_kv_persistent,
+                           kernel_inter_rank_gqa_fwd_batch_decode_combine_kv)
+from .gemm_reduce_scatter import create_gemm_rs_context, gemm_rs
+from .low_latency_allgather import create_fast_allgather_context, fast_allgather

@@ -1,0 +1,171 @@
+"""AllReduce over the symmetric heap, optionally fused with residual-add + RMSNorm.
+
+API parity with ``python/triton_dist/kernels/nvidia/allreduce.py`` (``create_allreduce_ctx`` :114,
+``all_reduce`` :1054, ``get_auto_allreduce_method`` :1039). Method mapping on one NVSwitch node:
+
+  =====================  =====================================================================
+  reference method       kernel used here (``csrc/kernels/allreduce.cu``)
+  =====================  =====================================================================
+  OneShot, OneShot_TMA   ONE_SHOT push (plain 16-byte P2P stores; TMA adds nothing for a push)
+  TwoShot                TWO_SHOT pull-reduce + push-broadcast
+  OneShot_Multimem       multimem.ld_reduce over the whole buffer
+  TwoShot_Multimem(_ST)  multimem.ld_reduce of the own slice + multimem.st broadcast
+  DoubleTree             ONE_SHOT for <= 64 KiB else TWO_SHOT: behind an NVSwitch every peer is one
+                         hop away, so a tree only adds hops; the name is kept for API parity
+  =====================  =====================================================================
+
+Unlike the reference there is no staging memcpy outside the kernel and no host-side call counter:
+the kernel stages, synchronises CTA-by-CTA with its peers, reduces and (optionally) normalises, and
+its epoch lives in device memory, so every method — chunked or not — can be captured in a CUDA graph.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+from ... import _lib, ops
+from ..._lib import c_float, dtype_code, ptr, stream_ptr
+from ...runtime.heap import SymmHeap, get_heap
+from ..allreduce import AllReduceMethod
+
+_NATIVE = {
+    AllReduceMethod.OneShot: 0, AllReduceMethod.OneShot_TMA: 0,
+    AllReduceMethod.TwoShot: 1,
+    AllReduceMethod.OneShot_Multimem: 2,
+    AllReduceMethod.TwoShot_Multimem: 3, AllReduceMethod.TwoShot_Multimem_ST: 3,
+}
+
+
+@dataclasses.dataclass
+class AllReduceContext:
+    workspace_nbytes: int
+    rank: int
+    world_size: int
+    local_world_size: int
+    heap: SymmHeap
+    workspaces: list[torch.Tensor]  # two parity buffers (uint8)
+    flags: torch.Tensor             # symmetric u32 CTA-level barrier epochs
+    sync: torch.Tensor              # local [epoch, done counter]
+    max_ctas: int
+
+    def finalize(self) -> None:
+        torch.cuda.synchronize()
+        for t in self.workspaces + [self.flags]:
+            self.heap.free(t)
+        self.workspaces = []
+
+
+def create_allreduce_ctx(workspace_nbytes: int, rank: int, world_size: int, local_world_size: int) -> AllReduceContext:
+    """`workspace_nbytes` bounds the bytes one call can move per parity buffer; larger inputs are chunked."""
+    heap = get_heap()
+    if world_size != heap.world:
+        raise ValueError("all_reduce spans the ranks of the symmetric heap (single node)")
+    lib = _lib.load()
+    max_ctas = lib.b200_allreduce_max_ctas()
+    ws = [heap.create_tensor((workspace_nbytes,), torch.uint8, align=1024) for _ in range(2)]
+    flags = heap.create_tensor((2 * max_ctas * 8,), torch.int32)
+    ctx = AllReduceContext(workspace_nbytes, rank, world_size, local_world_size, heap, ws, flags,
+                           torch.zeros(4, dtype=torch.int32, device="cuda"), max_ctas)
+    heap.barrier_all()
+    torch.cuda.synchronize()
+    return ctx
+
+
+def get_auto_allreduce_method(nbytes: int, has_multicast: bool | None = None) -> AllReduceMethod:
+    """Small messages are latency-bound (one-shot), large ones bandwidth-bound (two-shot); NVLS when bound."""
+    if has_multicast is None:
+        has_multicast = get_heap().has_multicast
+    if has_multicast:
+        return AllReduceMethod.TwoShot_Multimem if nbytes > 64 * 1024 else AllReduceMethod.OneShot_Multimem
+    return AllReduceMethod.TwoShot if nbytes > 256 * 1024 else AllReduceMethod.OneShot
+
+
+def _resolve(method: AllReduceMethod | None, nbytes: int, ctx: AllReduceContext) -> int:
+    if method is None or method == AllReduceMethod.Unknown:
+        method = get_auto_allreduce_method(nbytes, ctx.heap.has_multicast)
+    if method == AllReduceMethod.DoubleTree:
+        method = AllReduceMethod.OneShot if nbytes <= 64 * 1024 else AllReduceMethod.TwoShot
+    if method in (AllReduceMethod.OneShot_Multimem, AllReduceMethod.TwoShot_Multimem,
+                  AllReduceMethod.TwoShot_Multimem_ST) and not ctx.heap.has_multicast:
+        raise RuntimeError(f"{method.name} needs an NVLS multicast mapping, which this heap does not have")
+    return _NATIVE[method]
+
+
+def _ws_factor(native: int, world: int, fused: bool) -> int:
+    return {0: world, 2: 1}.get(native, 3 if fused else 2)
+
+
+def _num_ctas(nbytes: int, ctx: AllReduceContext, max_sm: int) -> int:
+    n = max(1, min(ctx.max_ctas, nbytes // (32 * 1024)))
+    if max_sm > 0:
+        n = min(n, max_sm)
+    return int(n)
+
+
+def all_reduce(x: torch.Tensor, output: torch.Tensor | None = None, method: AllReduceMethod | None = None,
+               ctx: AllReduceContext | None = None, max_sm: int = -1, straggler_option=None) -> torch.Tensor:
+    """Sum `x` over all ranks into `output` (allocated when None)."""
+    if ctx is None:
+        raise ValueError("all_reduce needs a context from create_allreduce_ctx")
+    if not x.is_contiguous():
+        x = x.contiguous()
+    if output is None:
+        output = torch.empty_like(x)
+    if straggler_option is not None and straggler_option[0] == ctx.rank:
+        torch.cuda._sleep(int(straggler_option[1]))
+    es = x.element_size()
+    native = _resolve(method, x.numel() * es, ctx)
+    factor = _ws_factor(native, ctx.world_size, False)
+    unit = (16 // es) * ctx.world_size
+    max_elems = (ctx.workspace_nbytes // (factor * es)) // unit * unit
+    if max_elems <= 0:
+        raise ValueError("allreduce workspace is too small for a single vector per rank")
+    n = x.numel()
+    xf, of = x.view(-1), output.view(-1)
+    done = 0
+    while done < n:
+        cur = min(max_elems, n - done)
+        cur_native = native
+        if cur % unit != 0:  # ragged tail: the one-shot push has no divisibility requirement beyond 16 bytes
+            if cur % (16 // es) != 0:
+                raise ValueError("all_reduce needs a multiple of 16 bytes")
+            cur_native = 0
+            cap = (ctx.workspace_nbytes // (ctx.world_size * es)) // (16 // es) * (16 // es)
+            cur = min(cur, cap)
+        _lib.call("b200_allreduce", ctx.heap.ctx, ptr(xf[done:]), ptr(of[done:]), _lib.c_u64(cur), dtype_code(x.dtype),
+                  cur_native, ptr(ctx.workspaces[0]), ptr(ctx.workspaces[1]), ptr(ctx.flags), ptr(ctx.sync), 0, None, None,
+                  None, None, c_float(0.0), _num_ctas(cur * es, ctx, max_sm), stream_ptr())
+        ops._count()
+        done += cur
+    return output
+
+
+def all_reduce_rmsnorm(x: torch.Tensor, residual: torch.Tensor | None, gamma: torch.Tensor, eps: float,
+                       ctx: AllReduceContext, method: AllReduceMethod | None = None,
+                       normed_out: torch.Tensor | None = None, residual_out: torch.Tensor | None = None,
+                       max_sm: int = -1):
+    """Fused ``h = all_reduce(x) + residual; y = rmsnorm(h) * gamma``. x: [rows, hidden].
+
+    Returns (y, h). `residual_out` defaults to `residual` (in place) when a residual is given.
+    """
+    rows, hidden = x.shape
+    es = x.element_size()
+    native = _resolve(method, x.numel() * es, ctx)
+    if native in (1, 3) and rows % ctx.world_size != 0:
+        native = 0 if native == 1 else 2  # row ownership needs rows divisible by the world size
+    factor = _ws_factor(native, ctx.world_size, True)
+    if x.numel() * es * factor > ctx.workspace_nbytes:
+        raise ValueError("fused all_reduce_rmsnorm does not chunk: enlarge the context workspace")
+    if normed_out is None:
+        normed_out = torch.empty_like(x)
+    if residual_out is None:
+        residual_out = residual if residual is not None else torch.empty_like(x)
+    n_ctas = min(ctx.max_ctas, rows if native in (0, 2) else max(1, rows // ctx.world_size))
+    if max_sm > 0:
+        n_ctas = min(n_ctas, max_sm)
+    _lib.call("b200_allreduce", ctx.heap.ctx, ptr(x), None, _lib.c_u64(x.numel()), dtype_code(x.dtype), native,
+              ptr(ctx.workspaces[0]), ptr(ctx.workspaces[1]), ptr(ctx.flags), ptr(ctx.sync), hidden, ptr(residual),
+              ptr(residual_out), ptr(gamma), ptr(normed_out), c_float(eps), max(1, n_ctas), stream_ptr())
+    ops._count()
+    return normed_out, residual_out

@@ -1,0 +1,88 @@
+"""GEMM-RS: ``out[M/r, N] = reduce_scatter(A[M, K/r] @ B[N, K/r].T)`` in one fused sm_100a kernel.
+
+API parity with ``python/triton_dist/kernels/nvidia/gemm_reduce_scatter.py`` (``create_gemm_rs_context``
+:79, ``gemm_rs`` :576). The reference's producer GEMM writes into a symmetric buffer and a second
+stream scatters and ring-reduces; here the tcgen05 epilogue stores every output row straight into
+the owner rank's slot over NVLink, bumps the owner's arrival counters with a release, and the same
+kernel finishes with the owner-side fp32 reduction of its rows (``csrc/kernels/gemm_sm100.cu``).
+The sum order is fixed (slot 0..r-1), so results are reproducible run to run.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+from ... import _lib, ops
+from ..._lib import dtype_code, ptr, stream_ptr
+from ...runtime.heap import SymmHeap, get_heap
+
+
+@dataclasses.dataclass
+class GEMMReduceScatterTensorParallelContext:
+    rank: int
+    world_size: int
+    local_world_size: int
+    max_M: int
+    N: int
+    output_dtype: torch.dtype
+    heap: SymmHeap
+    slots: list[torch.Tensor]     # two parity buffers [world, max_M / world, N]
+    rs_cnt: torch.Tensor          # symmetric u32 [world, rs_blocks] arrival counters (remote-incremented)
+    rs_base: torch.Tensor         # local counter bases
+    sync: torch.Tensor
+    rs_blocks: int
+    BLOCK_M: int = 128
+    BLOCK_N: int = 256
+    BLOCK_K: int = 64
+    stages: int = 4
+    group_m: int = 8
+    max_ctas: int = 0
+
+    def finalize(self) -> None:
+        torch.cuda.synchronize()
+        for t in self.slots + [self.rs_cnt]:
+            self.heap.free(t)
+        self.slots = []
+
+
+def create_gemm_rs_context(max_M: int, N: int, rank: int, world_size: int, local_world_size: int,
+                           output_dtype: torch.dtype, rs_stream=None, BLOCK_M: int = 128, BLOCK_N: int = 256,
+                           BLOCK_K: int = 64, GROUP_M: int = 8, stages: int = 4) -> GEMMReduceScatterTensorParallelContext:
+    heap = get_heap()
+    if world_size != heap.world:
+        raise ValueError("GEMM-RS spans the ranks of the symmetric heap (single node)")
+    if max_M % world_size != 0:
+        raise ValueError("max_M must be divisible by the world size")
+    mr_cap = max_M // world_size
+    rs_blocks = (mr_cap + 127) // 128 + 2
+    slots = [heap.create_tensor((world_size, mr_cap, N), output_dtype, align=1024) for _ in range(2)]
+    rs_cnt = heap.create_tensor((world_size * rs_blocks,), torch.int32)
+    ctx = GEMMReduceScatterTensorParallelContext(
+        rank=rank, world_size=world_size, local_world_size=local_world_size, max_M=max_M, N=N, output_dtype=output_dtype,
+        heap=heap, slots=slots, rs_cnt=rs_cnt,
+        rs_base=torch.zeros(world_size * rs_blocks, dtype=torch.int32, device="cuda"),
+        sync=torch.zeros(4, dtype=torch.int32, device="cuda"), rs_blocks=rs_blocks, group_m=GROUP_M)
+    heap.barrier_all()
+    torch.cuda.synchronize()
+    return ctx
+
+
+def gemm_rs(a: torch.Tensor, b: torch.Tensor, ctx: GEMMReduceScatterTensorParallelContext, persistent: bool = True,
+            fuse_scatter: bool = True, out: torch.Tensor | None = None) -> torch.Tensor:
+    """a: [M, K/r]; b: [N, K/r]. Returns this rank's rows [M/r, N] of the summed product."""
+    M, K = a.shape
+    N = b.shape[0]
+    if N != ctx.N or M > ctx.max_M:
+        raise ValueError(f"problem [{M},{N}] does not fit the context ([{ctx.max_M},{ctx.N}])")
+    if M % ctx.world_size != 0:
+        raise ValueError("M must be divisible by the world size")
+    if a.stride(1) != 1 or b.stride(1) != 1:
+        raise ValueError("a and b must be row-major")
+    if out is None:
+        out = torch.empty((M // ctx.world_size, N), dtype=ctx.output_dtype, device=a.device)
+    _lib.call("b200_gemm_rs", ctx.heap.ctx, ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0),
+              dtype_code(a.dtype), ptr(ctx.slots[0]), ptr(ctx.slots[1]), ptr(ctx.rs_cnt), ptr(ctx.rs_base), ptr(ctx.sync),
+              ctx.max_M // ctx.world_size, ctx.rs_blocks, ctx.group_m, ctx.max_ctas, stream_ptr())
+    ops._count()
+    return out

@@ -1,0 +1,232 @@
+"""Single-GPU hot ops backed by the sm_100a kernels in ``csrc/kernels``.
+
+Every function here launches native code on the current CUDA stream and fails loudly when the
+native library or a GPU is missing: there is no silent PyTorch fallback (the CPU reference
+semantics live in :mod:`triton_distributed_b200.ref`).
+
+Replaces in the reference: cuBLAS ``F.linear``, ``flashinfer.norm.rmsnorm``,
+``flashinfer.apply_rope_with_cos_sin_cache_inplace``, ``act_fn(gate) * up`` and the softmax/topk router
+(``layers/nvidia/tp_mlp.py:159-186``, ``tp_attn.py:60-75,159-195``, ``kernels/nvidia/moe_reduce_rs.py:172-189``).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import c_float, c_int, dtype_code, ptr, stream_ptr
+
+# number of native kernel launches issued through this module (bench.py reports it)
+launch_count = 0
+
+
+def _count(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
+
+def _check_2d(t: torch.Tensor, name: str) -> None:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be a 2-D tensor with unit inner stride, got shape {tuple(t.shape)} stride {t.stride()}")
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, max_ctas: int = 0) -> torch.Tensor:
+    """``a[M,K] @ b[N,K].T`` on the persistent tcgen05 kernel (128x256x64 tiles, fp32 accumulation)."""
+    _lib.require_cuda()
+    _check_2d(a, "a"), _check_2d(b, "b")
+    M, K = a.shape
+    N = b.shape[0]
+    if b.shape[1] != K or a.dtype != b.dtype:
+        raise ValueError("gemm: shape/dtype mismatch")
+    if out is None:
+        out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    _lib.call("b200_gemm", ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+              dtype_code(a.dtype), max_ctas, stream_ptr())
+    _count()
+    return out
+
+
+class _SkinnyScratch:
+    """Per-device split-K scratch shared by all skinny GEMM calls of a stream (each call re-zeroes it)."""
+
+    def __init__(self):
+        self.bufs: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+
+    def get(self, device: torch.device, floats: int, tiles: int):
+        key = device.index if device.index is not None else torch.cuda.current_device()
+        cur = self.bufs.get(key)
+        if cur is None or cur[0].numel() < floats or cur[1].numel() < tiles:
+            if cur is not None:
+                torch.cuda.synchronize()
+            nf = max(floats, 4 << 20, 0 if cur is None else cur[0].numel())
+            nt = max(tiles, 4096, 0 if cur is None else cur[1].numel())
+            cur = (torch.zeros(nf, dtype=torch.float32, device=device), torch.zeros(nt, dtype=torch.int32, device=device))
+            self.bufs[key] = cur
+        return cur
+
+
+_skinny_scratch = _SkinnyScratch()
+
+
+def reserve_skinny_scratch(device, floats: int, tiles: int) -> None:
+    """Pre-size the split-K scratch (call before CUDA-graph capture so no allocation happens inside)."""
+    _skinny_scratch.get(torch.device(device), floats, tiles)
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, swiglu: bool = False,
+                splits: int = 0) -> torch.Tensor:
+    """Decode GEMM for ``M <= 256`` tokens: ``x[M,K] @ w[N,K].T`` with the weights streamed once.
+
+    With ``swiglu=True``, ``w`` is ``[gate; up]`` (2*I rows) and the result is ``silu(x gate^T) * (x up^T)`` [M, I].
+    """
+    _lib.require_cuda()
+    _check_2d(x, "x"), _check_2d(w, "w")
+    M, K = x.shape
+    n_rows = w.shape[0]
+    N = n_rows // 2 if swiglu else n_rows
+    if out is None:
+        out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    lib = _lib.load()
+    lib.b200_gemm_skinny_scratch_floats.restype = ctypes.c_longlong
+    floats = lib.b200_gemm_skinny_scratch_floats(M, N, 1 if swiglu else 0)
+    tiles = (N + 127) // 128
+    scratch, tickets = _skinny_scratch.get(x.device, floats, tiles)
+    _lib.call("b200_gemm_skinny", ptr(x), ptr(w), ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
+              1 if swiglu else 0, dtype_code(x.dtype), ptr(scratch), ptr(tickets), splits, stream_ptr())
+    _count()
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ w.T`` for any leading shape, routed to the skinny kernel for <= 256 rows, else the tiled one."""
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    o2 = out.reshape(-1, w.shape[0]) if out is not None else None
+    y = gemm_skinny(x2, w, o2) if x2.shape[0] <= 256 else gemm(x2, w, o2)
+    return y.reshape(*lead, w.shape[0])
+
+
+def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float, residual: torch.Tensor | None = None,
+            out: torch.Tensor | None = None) -> torch.Tensor:
+    """RMSNorm over the last dim. With `residual`, computes ``residual += x`` in place first and normalises the sum."""
+    _lib.require_cuda()
+    hidden = x.shape[-1]
+    x2 = x.reshape(-1, hidden)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    if out is None:
+        out = torch.empty_like(x2)
+    o2 = out.reshape(-1, hidden)
+    r2 = residual.reshape(-1, hidden) if residual is not None else None
+    _lib.call("b200_rmsnorm", ptr(x2), ptr(r2), ptr(r2), ptr(gamma), ptr(o2), x2.shape[0], hidden, c_float(eps),
+              dtype_code(x.dtype), stream_ptr())
+    _count()
+    return o2.reshape(x.shape)
+
+
+def qk_norm_rope(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor, num_q_heads: int,
+                 num_kv_heads: int, k_cache: torch.Tensor, v_cache: torch.Tensor, slots: torch.Tensor | None,
+                 q_gamma: torch.Tensor | None, k_gamma: torch.Tensor | None, eps: float = 1e-6,
+                 q_out: torch.Tensor | None = None) -> torch.Tensor:
+    """Per-head RMSNorm of q/k, neox RoPE, and the write of k/v into the KV cache at `slots`, in one kernel.
+
+    qkv: [T, (Hq + 2 Hkv) * 128]; positions: int32 [T]; cos_sin: fp32 [max_pos, 128] (cos | sin);
+    caches: [num_slots, Hkv, 128] (any view whose first dim is the slot); slots: int64 [T] (None = identity).
+    Returns q [T, Hq, 128].
+    """
+    _lib.require_cuda()
+    T = qkv.shape[0]
+    D = 128
+    if qkv.shape[1] != (num_q_heads + 2 * num_kv_heads) * D or not qkv.is_contiguous():
+        raise ValueError("qkv must be contiguous [T, (Hq + 2*Hkv) * 128]")
+    if positions.dtype != torch.int32 or cos_sin.dtype != torch.float32:
+        raise ValueError("positions must be int32 and cos_sin float32")
+    if q_out is None:
+        q_out = torch.empty((T, num_q_heads, D), dtype=qkv.dtype, device=qkv.device)
+    _lib.call("b200_qk_norm_rope", ptr(qkv), ptr(positions), ptr(slots), ptr(q_gamma), ptr(k_gamma), ptr(cos_sin),
+              ptr(q_out), ptr(k_cache), ptr(v_cache), T, num_q_heads, num_kv_heads, D, c_float(eps),
+              dtype_code(qkv.dtype), stream_ptr())
+    _count()
+    return q_out
+
+
+def silu_mul(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``silu(x[..., :I]) * x[..., I:]`` for the fused [gate | up] projection."""
+    _lib.require_cuda()
+    inter = x.shape[-1] // 2
+    x2 = x.reshape(-1, x.shape[-1])
+    _check_2d(x2, "x")
+    if out is None:
+        out = torch.empty((x2.shape[0], inter), dtype=x.dtype, device=x.device)
+    _lib.call("b200_silu_mul", ptr(x2), ptr(out), x2.shape[0], inter, x2.stride(0), dtype_code(x.dtype), stream_ptr())
+    _count()
+    return out.reshape(*x.shape[:-1], inter)
+
+
+def topk_softmax(logits: torch.Tensor, k: int, renormalize: bool = False):
+    """Router: softmax over experts then top-k. Returns (ids int32 [T,k], weights fp32 [T,k])."""
+    _lib.require_cuda()
+    T, E = logits.shape
+    logits = logits.contiguous()
+    ids = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+    _lib.call("b200_topk_softmax", ptr(logits), dtype_code(logits.dtype), T, E, k, ptr(ids), ptr(w),
+              1 if renormalize else 0, stream_ptr())
+    _count()
+    return ids, w
+
+
+def choose_kv_splits(batch: int, num_kv_heads: int, group: int, max_kv_len: int, sm_count: int = 148) -> int:
+    """Split count so that batch x kv-heads x splits fills the machine about twice, with >= 256 tokens per split."""
+    ctas = batch * num_kv_heads * ((group + 15) // 16)
+    want = max(1, (2 * sm_count + ctas - 1) // ctas)
+    by_len = max(1, max_kv_len // 256)
+    return int(max(1, min(want, by_len, 128)))
+
+
+def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_lens: torch.Tensor,
+                     block_table: torch.Tensor, scale: float, soft_cap: float = 0.0, num_splits: int = 1,
+                     out: torch.Tensor | None = None, return_lse: bool = False, workspace: dict | None = None):
+    """Paged GQA decode attention. q [B,Hq,128]; caches [num_blocks, page, Hkv, 128]; kv_lens int32 [B];
+    block_table int32 [B, max_blocks]. Returns out [B,Hq,128] (and natural-log LSE fp32 [B,Hq])."""
+    _lib.require_cuda()
+    B, Hq, D = q.shape
+    page, Hkv = k_cache.shape[1], k_cache.shape[2]
+    if not (q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous() and block_table.stride(1) == 1):
+        raise ValueError("decode_attention needs contiguous q / caches and a row-major block table")
+    if out is None:
+        out = torch.empty_like(q)
+    lse = torch.empty((B, Hq), dtype=torch.float32, device=q.device) if return_lse else None
+    if num_splits > 1:
+        if workspace is not None and "o_part" in workspace and workspace["o_part"].numel() >= B * Hq * num_splits * D:
+            o_part, lse_part = workspace["o_part"], workspace["lse_part"]
+        else:
+            o_part = torch.empty(B * Hq * num_splits * D, dtype=torch.float32, device=q.device)
+            lse_part = torch.empty(B * Hq * num_splits, dtype=torch.float32, device=q.device)
+            if workspace is not None:
+                workspace["o_part"], workspace["lse_part"] = o_part, lse_part
+    else:
+        o_part = lse_part = None
+    _lib.call("b200_decode_attn_split", ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.stride(0),
+              ptr(kv_lens), B, Hq, Hkv, D, page, c_float(scale), c_float(soft_cap), num_splits, ptr(o_part),
+              ptr(lse_part), ptr(out), ptr(lse), dtype_code(q.dtype), stream_ptr())
+    _count()
+    if num_splits > 1:
+        _lib.call("b200_decode_combine", ptr(o_part), ptr(lse_part), ctypes.c_longlong(num_splits * D),
+                  ctypes.c_longlong(D), ctypes.c_longlong(num_splits), ctypes.c_longlong(1), B * Hq, num_splits,
+                  ptr(out), None, ptr(lse), dtype_code(q.dtype), stream_ptr())
+        _count()
+    return (out, lse) if return_lse else out
+
+
+def combine_partials(o_part: torch.Tensor, lse_part: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """Merge attention partials over dim 0: o_part fp32 [R, BH, 128], lse_part fp32 [R, BH] -> [BH, 128]."""
+    _lib.require_cuda()
+    R, BH, D = o_part.shape
+    out = torch.empty((BH, D), dtype=out_dtype, device=o_part.device)
+    _lib.call("b200_decode_combine", ptr(o_part), ptr(lse_part), ctypes.c_longlong(o_part.stride(1)),
+              ctypes.c_longlong(o_part.stride(0)), ctypes.c_longlong(lse_part.stride(1)),
+              ctypes.c_longlong(lse_part.stride(0)), BH, R, ptr(out), None, None, dtype_code(out_dtype), stream_ptr())
+    _count()
+    return out
