@@ -1,0 +1,277 @@
+"""Multi-rank GPU checks, run as ``torchrun --nproc-per-node N tests/dist_cases.py [case ...]``.
+
+Every case compares a fused kernel with the ``torch.distributed`` (NCCL) + ``torch.matmul`` composition
+that the reference uses as its golden (``test/nvidia/test_ag_gemm.py:71-137``, ``test_gemm_rs.py:38-51``,
+``test_allreduce.py:95-136``, ``test_fast_allgather.py``). A case passes only if it passes on every rank
+and no kernel recorded an expired wait. Exit code = number of failed cases.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import traceback
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from triton_distributed_b200 import _lib  # noqa: E402
+from triton_distributed_b200 import utils as U  # noqa: E402
+from triton_distributed_b200.kernels.allreduce import to_allreduce_method  # noqa: E402
+from triton_distributed_b200.kernels.nvidia import (ag_gemm, all_reduce, all_reduce_rmsnorm, create_ag_gemm_context,  # noqa: E402
+                                                    create_allreduce_ctx, create_fast_allgather_context,
+                                                    create_gemm_rs_context, fast_allgather, gemm_rs)
+from triton_distributed_b200.runtime.heap import get_heap  # noqa: E402
+
+CASES = {}
+
+
+def case(fn):
+    CASES[fn.__name__] = fn
+    return fn
+
+
+def _rank_world():
+    return dist.get_rank(), dist.get_world_size()
+
+
+@case
+def heap_peer_views():
+    rank, world = _rank_world()
+    heap = get_heap()
+    views = heap.create_tensors((world, 256), torch.float32)
+    # every rank writes its row into every peer's copy through the peer mapping (copy engine / elementwise kernels)
+    for k in range(world):
+        views[k][rank].fill_(float(rank + 1))
+    torch.cuda.synchronize()
+    heap.barrier_all()
+    torch.cuda.synchronize()
+    want = torch.arange(1, world + 1, device="cuda", dtype=torch.float32)[:, None].expand(world, 256)
+    assert torch.equal(views[rank], want), "peer writes did not land"
+    if heap.has_multicast:
+        mc = heap.multicast_tensor(views[rank])
+        assert mc.data_ptr() != views[rank].data_ptr()
+    heap.barrier_all()
+    torch.cuda.synchronize()
+    heap.free(views[rank])
+
+
+@case
+def primitives_put_get_notify():
+    rank, world = _rank_world()
+    heap = get_heap()
+    n = 4096
+    src = heap.create_tensor((n,), torch.int32)
+    dst = heap.create_tensor((n,), torch.int32)
+    sig = heap.create_tensor((32,), torch.int32)
+    flags = heap.create_tensor((32,), torch.int32)
+    ok = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for it in range(1, 4):
+        src.copy_(torch.arange(n, device="cuda", dtype=torch.int32) + rank * 100000 + it)
+        heap.barrier_all()
+        _lib.call("b200_test_ring_put", heap.ctx, _lib.ptr(src), _lib.ptr(dst), _lib.ptr(sig), n, it, _lib.ptr(ok), _lib.stream_ptr())
+        torch.cuda.synchronize()
+        prev = (rank - 1) % world
+        assert int(ok.item()) == 1
+        assert torch.equal(dst, torch.arange(n, device="cuda", dtype=torch.int32) + prev * 100000 + it), "ring put"
+        heap.barrier_all()
+    dst.zero_()
+    heap.barrier_all()
+    _lib.call("b200_test_ring_get", heap.ctx, _lib.ptr(src), _lib.ptr(dst), n, _lib.ptr(flags), 1, _lib.ptr(ok), _lib.stream_ptr())
+    torch.cuda.synchronize()
+    prev = (rank - 1) % world
+    assert int(ok.item()) == 1 and torch.equal(dst, torch.arange(n, device="cuda", dtype=torch.int32) + prev * 100000 + 3), "ring get"
+    counter = heap.create_tensor((8,), torch.int32)
+    heap.barrier_all()
+    _lib.call("b200_test_notify_add", heap.ctx, _lib.ptr(counter), 0, world, _lib.ptr(ok), _lib.stream_ptr())
+    torch.cuda.synchronize()
+    assert int(ok.item()) == 1
+    heap.barrier_all()
+    torch.cuda.synchronize()
+    if rank == 0:
+        assert int(counter[0].item()) == world, "notify add"
+    if heap.has_multicast:
+        buf = heap.create_tensor((1024,), torch.float32)
+        buf.fill_(float(rank + 1))
+        out = torch.zeros(1024, device="cuda")
+        mflags = heap.create_tensor((32,), torch.int32)
+        heap.barrier_all()
+        _lib.call("b200_test_multimem", heap.ctx, _lib.ptr(buf), 256, _lib.ptr(mflags), 1, _lib.ptr(out), _lib.ptr(ok), _lib.stream_ptr())
+        torch.cuda.synchronize()
+        assert int(ok.item()) == 1 and torch.all(out == world * (world + 1) / 2), "multimem ld_reduce"
+        heap.barrier_all()
+        torch.cuda.synchronize()
+        heap.free(mflags), heap.free(buf)
+    for t in (counter, flags, sig, dst, src):
+        heap.free(t)
+
+
+@case
+def fast_allgather_modes():
+    rank, world = _rank_world()
+    heap = get_heap()
+    ctx = create_fast_allgather_context(rank, 0, world, 1, max_buffer_size=4 << 20)
+    modes = ["pull", "push2d", "push2d_ll"] + (["push2d_ll_multimem"] if heap.has_multicast else [])
+    for per_rank in (64, 4096, 65536):
+        buf = heap.create_tensor((world, per_rank), torch.float32)
+        for it, mode in enumerate(modes * 2):
+            buf.zero_()
+            buf[rank] = torch.arange(per_rank, device="cuda", dtype=torch.float32) + 1000 * rank + it
+            heap.barrier_all()
+            fast_allgather(buf, ctx, mode=mode)
+            torch.cuda.synchronize()
+            want = torch.arange(per_rank, device="cuda", dtype=torch.float32)[None, :] + 1000 * torch.arange(
+                world, device="cuda", dtype=torch.float32)[:, None] + it
+            assert torch.equal(buf, want), f"fast_allgather {mode} {per_rank}"
+            heap.barrier_all()
+        torch.cuda.synchronize()
+        heap.free(buf)
+    ctx.finalize()
+
+
+@case
+def allreduce_methods():
+    rank, world = _rank_world()
+    heap = get_heap()
+    ctx = create_allreduce_ctx(8 << 20, rank, world, world)
+    methods = ["one_shot", "two_shot", "double_tree"] + (["one_shot_multimem", "two_shot_multimem"] if heap.has_multicast else [])
+    tol = {torch.bfloat16: 3e-2, torch.float16: 1e-2, torch.float32: 1e-3}
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        for n in (8 * world, 4096 * world, 1 << 20, (3 << 20) + 16 * world):
+            for m in methods:
+                torch.manual_seed(rank + n)
+                x = torch.randn(n, device="cuda", dtype=dtype)
+                ref = x.clone().float()
+                dist.all_reduce(ref)
+                for _ in range(2):
+                    y = all_reduce(x, None, to_allreduce_method(m), ctx)
+                torch.cuda.synchronize()
+                torch.testing.assert_close(y.float(), ref, rtol=tol[dtype], atol=tol[dtype] * 4, msg=lambda s: f"{m} {dtype} n={n}: {s}")
+    y = all_reduce(torch.ones(1024, device="cuda", dtype=torch.float32), None, None, ctx)  # auto method
+    assert torch.all(y == world)
+    ctx.finalize()
+
+
+@case
+def allreduce_fused_rmsnorm():
+    rank, world = _rank_world()
+    heap = get_heap()
+    ctx = create_allreduce_ctx(32 << 20, rank, world, world)
+    methods = ["one_shot", "two_shot"] + (["one_shot_multimem", "two_shot_multimem"] if heap.has_multicast else [])
+    for rows, hidden in ((8, 5120), (8 * world, 8192), (3, 1024), (64 * world, 8192)):
+        for m in methods:
+            torch.manual_seed(rank * 7 + rows)
+            x = torch.randn(rows, hidden, device="cuda", dtype=torch.bfloat16)
+            torch.manual_seed(rows)
+            res = torch.randn(rows, hidden, device="cuda", dtype=torch.bfloat16)
+            g = torch.randn(hidden, device="cuda", dtype=torch.bfloat16)
+            s = x.clone().float()
+            dist.all_reduce(s)
+            h_ref = (s.to(torch.bfloat16).float() + res.float())  # tolerance covers the reference's extra rounding
+            res_in = res.clone()
+            y, h = all_reduce_rmsnorm(x, res_in, g, 1e-6, ctx, to_allreduce_method(m))
+            torch.cuda.synchronize()
+            torch.testing.assert_close(h.float(), h_ref, rtol=3e-2, atol=6e-2, msg=lambda s_: f"residual {m} {rows}x{hidden}: {s_}")
+            hf = h.float()
+            y_ref = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-6) * g.float()
+            torch.testing.assert_close(y.float(), y_ref, rtol=2e-2, atol=2e-2, msg=lambda s_: f"normed {m} {rows}x{hidden}: {s_}")
+            # all ranks must hold identical results
+            hh = [torch.empty_like(h) for _ in range(world)]
+            dist.all_gather(hh, h.contiguous())
+            assert all(torch.equal(hh[0], t) for t in hh), f"ranks disagree on the residual ({m})"
+    ctx.finalize()
+
+
+def _ag_gemm_case(Mr, N, K, dtype, iters=3, straggler=False):
+    rank, world = _rank_world()
+    torch.manual_seed(1234 + rank)
+    b = (torch.randn(N, K, device="cuda", dtype=dtype) * 0.05)
+    ctx = create_ag_gemm_context(torch.empty(Mr, K, device="cuda", dtype=dtype), b, rank, world, max_M=Mr * world)
+    for it in range(iters):
+        a = torch.randn(Mr, K, device="cuda", dtype=dtype)
+        full = torch.empty(Mr * world, K, device="cuda", dtype=dtype)
+        dist.all_gather_into_tensor(full, a)
+        ref = full.float() @ b.float().t()
+        opt = (it % world, 2_000_000_000) if straggler else None
+        c = ag_gemm(a, b, ctx, straggler_option=opt)
+        torch.cuda.synchronize()
+        torch.testing.assert_close(c.float(), ref, rtol=2e-2, atol=2e-2, msg=lambda s: f"ag_gemm Mr={Mr} N={N} K={K} it={it}: {s}")
+    ctx.finalize()
+
+
+@case
+def ag_gemm_shapes():
+    _ag_gemm_case(128, 256, 256, torch.bfloat16)
+    _ag_gemm_case(512, 1024, 2048, torch.bfloat16)
+    _ag_gemm_case(999, 776, 520, torch.bfloat16)   # ragged: blocks straddle ranks
+    _ag_gemm_case(64, 512, 1024, torch.float16)
+    _ag_gemm_case(1024, 7168, 8192, torch.bfloat16, iters=2)
+
+
+@case
+def ag_gemm_straggler():
+    _ag_gemm_case(512, 1024, 1024, torch.bfloat16, iters=4, straggler=True)
+
+
+def _gemm_rs_case(M, N, K, dtype, iters=3):
+    rank, world = _rank_world()
+    torch.manual_seed(4321 + rank)
+    ctx = create_gemm_rs_context(M, N, rank, world, world, dtype)
+    b = torch.randn(N, K, device="cuda", dtype=dtype) * 0.05
+    for it in range(iters):
+        a = torch.randn(M, K, device="cuda", dtype=dtype) * 0.5 * (rank + 1)
+        full = (a.float() @ b.float().t())
+        ref = torch.empty(M // world, N, device="cuda", dtype=torch.float32)
+        dist.reduce_scatter_tensor(ref, full)
+        out = gemm_rs(a, b, ctx)
+        torch.cuda.synchronize()
+        torch.testing.assert_close(out.float(), ref, rtol=6e-2, atol=6e-2 * world, msg=lambda s: f"gemm_rs M={M} N={N} K={K} it={it}: {s}")
+    ctx.finalize()
+
+
+@case
+def gemm_rs_shapes():
+    world = dist.get_world_size()
+    _gemm_rs_case(128 * world, 256, 256, torch.bfloat16)
+    _gemm_rs_case(512 * world, 1024, 512, torch.bfloat16)
+    _gemm_rs_case(100 * world, 776, 520, torch.bfloat16)  # ragged: tiles straddle owners
+    _gemm_rs_case(world, 512, 1024, torch.bfloat16)       # one row per rank (decode-like)
+    _gemm_rs_case(64 * world, 512, 256, torch.float16)
+    _gemm_rs_case(8192, 8192, 3584, torch.bfloat16, iters=2)
+
+
+def main() -> int:
+    U.initialize_distributed(seed=0, heap_bytes=int(os.environ.get("B200DIST_TEST_HEAP", 3 << 30)))
+    rank, world = _rank_world()
+    heap = get_heap()
+    names = sys.argv[1:] or list(CASES)
+    if rank == 0:
+        print(f"[dist_cases] world={world} heap mode={heap.mode} multicast={heap.has_multicast}", flush=True)
+    failed = 0
+    for name in names:
+        ok, err = True, ""
+        try:
+            CASES[name]()
+            torch.cuda.synchronize()
+            heap.check_status(name)
+        except Exception:  # noqa: BLE001
+            ok, err = False, traceback.format_exc()
+        verdicts = [None] * world
+        dist.all_gather_object(verdicts, (ok, err))
+        all_ok = all(v[0] for v in verdicts)
+        if rank == 0:
+            print(f"CASE {name} {'PASS' if all_ok else 'FAIL'}", flush=True)
+            if not all_ok:
+                for r, v in enumerate(verdicts):
+                    if not v[0]:
+                        print(f"--- rank {r} ---\n{v[1]}", flush=True)
+        failed += 0 if all_ok else 1
+        if not all_ok:
+            break  # state after a failed collective case is not trustworthy
+    U.finalize_distributed()
+    return failed
+
+
+if __name__ == "__main__":
+    sys.exit(main())
