@@ -155,17 +155,29 @@ def all_reduce_rmsnorm(x: torch.Tensor, residual: torch.Tensor | None, gamma: to
     if native in (1, 3) and rows % ctx.world_size != 0:
         native = 0 if native == 1 else 2  # row ownership needs rows divisible by the world size
     factor = _ws_factor(native, ctx.world_size, True)
-    if x.numel() * es * factor > ctx.workspace_nbytes:
-        raise ValueError("fused all_reduce_rmsnorm does not chunk: enlarge the context workspace")
+    cap = ctx.workspace_nbytes // (factor * hidden * es)
+    if native in (1, 3):
+        cap = cap // ctx.world_size * ctx.world_size
+    if cap <= 0:
+        raise ValueError("allreduce workspace is too small for one row per rank")
     if normed_out is None:
         normed_out = torch.empty_like(x)
     if residual_out is None:
         residual_out = residual if residual is not None else torch.empty_like(x)
-    n_ctas = min(ctx.max_ctas, rows if native in (0, 2) else max(1, rows // ctx.world_size))
-    if max_sm > 0:
-        n_ctas = min(n_ctas, max_sm)
-    _lib.call("b200_allreduce", ctx.heap.ctx, ptr(x), None, _lib.c_u64(x.numel()), dtype_code(x.dtype), native,
-              ptr(ctx.workspaces[0]), ptr(ctx.workspaces[1]), ptr(ctx.flags), ptr(ctx.sync), hidden, ptr(residual),
-              ptr(residual_out), ptr(gamma), ptr(normed_out), c_float(eps), max(1, n_ctas), stream_ptr())
-    ops._count()
+    for r0 in range(0, rows, cap):  # row chunks are independent calls
+        r1 = min(rows, r0 + cap)
+        nr = r1 - r0
+        cur = native
+        if cur in (1, 3) and nr % ctx.world_size != 0:
+            cur = 0 if cur == 1 else 2
+            if nr * hidden * es * _ws_factor(cur, ctx.world_size, True) > ctx.workspace_nbytes:
+                raise ValueError("ragged tail does not fit the allreduce workspace")
+        n_ctas = min(ctx.max_ctas, nr if cur in (0, 2) else max(1, nr // ctx.world_size))
+        if max_sm > 0:
+            n_ctas = min(n_ctas, max_sm)
+        _lib.call("b200_allreduce", ctx.heap.ctx, ptr(x[r0:r1]), None, _lib.c_u64(nr * hidden), dtype_code(x.dtype), cur,
+                  ptr(ctx.workspaces[0]), ptr(ctx.workspaces[1]), ptr(ctx.flags), ptr(ctx.sync), hidden,
+                  ptr(residual[r0:r1]) if residual is not None else None, ptr(residual_out[r0:r1]), ptr(gamma),
+                  ptr(normed_out[r0:r1]), c_float(eps), max(1, n_ctas), stream_ptr())
+        ops._count()
     return normed_out, residual_out

@@ -1,0 +1,5 @@
+"""Layers (exports follow ``python/triton_dist/layers/nvidia/__init__.py:25-29``)."""
+from .tp_attn import TP_Attn, _set_cos_sin_cache, layer_norm
+from .tp_mlp import TP_MLP, shard_local
+
+__all__ = ["TP_MLP", "TP_Attn", "layer_norm", "_set_cos_sin_cache", "shard_local"]

@@ -1,0 +1,229 @@
+"""Qwen3 dense decoder with tensor parallelism and three forward modes.
+
+API parity with ``python/triton_dist/models/qwen.py:54-229``: ``Qwen3(model_config, group)``,
+``set_fwd(mode)``, ``init_triton_dist_ctx(max_M)``, ``init_triton_dist_AR_ctx(max_M, ar_method)``,
+``inference(input_ids, position_ids, kv_cache, wo_lm_head)`` and ``finalize()``.
+
+Modes:
+  ``torch``           cuBLAS GEMMs, torch norms/rope/attention, NCCL all-reduce: golden and baseline.
+  ``triton_dist``     AG-GEMM + GEMM-RS; hidden states stay batch-sharded between layers.
+  ``triton_dist_AR``  native GEMMs on replicated activations; each all-reduce is fused with the residual
+                      add and the following RMSNorm, so a layer is 8 launches at decode.
+
+Weights come from HF safetensors shards or random initialisation (``models/weights.py``); each rank reads
+only its slices. The vocabulary is sharded over ranks for ``lm_head`` (logits are all-gathered).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from .. import ops
+from ..kernels.allreduce import AllReduceMethod
+from ..kernels.nvidia import (all_reduce_rmsnorm, create_ag_gemm_context, create_allreduce_ctx,
+                              create_gemm_rs_context)
+from ..layers.nvidia import TP_MLP, TP_Attn, _set_cos_sin_cache, layer_norm
+from .config import ArchConfig, ModelConfig
+from .kv_cache import KV_Cache
+from .utils import logger
+from .weights import RandomSource, SafetensorsSource, WeightSource
+
+
+class Qwen3Layer:
+
+    def __init__(self, layer_idx: int, rank: int, world_size: int, group):
+        self.layer_idx = layer_idx
+        self.attn = TP_Attn(rank, world_size, group)
+        self.mlp = TP_MLP(rank, world_size, group)
+        self.input_norm_w = self.post_norm_w = None
+        self.eps = 1e-6
+
+    def load(self, src: WeightSource, arch: ArchConfig, rank: int, world: int) -> None:
+        p = f"model.layers.{self.layer_idx}."
+        D = arch.head_dim
+        qs = slice(rank * arch.num_attention_heads * D // world, (rank + 1) * arch.num_attention_heads * D // world)
+        kv_per = max(1, arch.num_key_value_heads // world)
+        kv_idx = rank * arch.num_key_value_heads // world if arch.num_key_value_heads >= world else rank * arch.num_key_value_heads // world
+        ks = slice(kv_idx * D, (kv_idx + kv_per) * D)
+        Is = slice(rank * arch.intermediate_size // world, (rank + 1) * arch.intermediate_size // world)
+        self.attn._init_parameters(
+            q=src.get(p + "self_attn.q_proj.weight", rows=qs), k=src.get(p + "self_attn.k_proj.weight", rows=ks),
+            v=src.get(p + "self_attn.v_proj.weight", rows=ks), o=src.get(p + "self_attn.o_proj.weight", cols=qs),
+            q_norm=src.get(p + "self_attn.q_norm.weight") if src.has(p + "self_attn.q_norm.weight") else None,
+            k_norm=src.get(p + "self_attn.k_norm.weight") if src.has(p + "self_attn.k_norm.weight") else None,
+            num_heads=arch.num_attention_heads, num_kv_heads=arch.num_key_value_heads, eps=arch.rms_norm_eps)
+        self.mlp._init_parameters(gate=src.get(p + "mlp.gate_proj.weight", rows=Is), up=src.get(p + "mlp.up_proj.weight", rows=Is),
+                                  down=src.get(p + "mlp.down_proj.weight", cols=Is))
+        self.input_norm_w = src.get(p + "input_layernorm.weight")
+        self.post_norm_w = src.get(p + "post_attention_layernorm.weight")
+        self.eps = arch.rms_norm_eps
+
+    def set_fwd(self, mode: str) -> None:
+        self.mode = mode
+
+    @torch.no_grad()
+    def fwd(self, hidden, position_ids, cos_sin_cache, kv_cache, step=None):
+        """Unfused layer forward for the ``torch`` and ``triton_dist`` modes (pre-norm residual block)."""
+        residual = hidden
+        x = layer_norm(hidden, self.eps, self.input_norm_w)
+        if self.mode == "torch":
+            x = self.attn.torch_fwd(x, position_ids, cos_sin_cache, kv_cache, self.layer_idx)
+        else:
+            x = self.attn.dist_triton_fwd(x, position_ids, cos_sin_cache, kv_cache, self.layer_idx, step=step)
+        hidden = residual + x
+        residual = hidden
+        x = layer_norm(hidden, self.eps, self.post_norm_w)
+        x = self.mlp.torch_fwd(x) if self.mode == "torch" else self.mlp.dist_triton_fwd(x)
+        return residual + x
+
+
+class Qwen3:
+
+    def __init__(self, model_config: ModelConfig, group=None, source: WeightSource | None = None):
+        self.model_config = model_config
+        self.group = group
+        self.rank, self.world_size = model_config.rank, model_config.world_size
+        self.dtype = model_config.dtype
+        self.arch = model_config.arch()
+        a = self.arch
+        if a.num_attention_heads % self.world_size or a.intermediate_size % self.world_size:
+            raise ValueError("heads and intermediate size must be divisible by the world size")
+        self.device = "cuda" if torch.cuda.is_available() else "cpu"
+        self.mode = "torch"
+        self.ar_ctx = self.ag_ctx_qkv = self.ag_ctx_mlp = self.rs_ctx = None
+        self.ar_method = None
+        self.max_length = model_config.max_length
+        self.init_parameters(source)
+
+    # ------------------------------------------------------------------ weights
+    def init_parameters(self, source: WeightSource | None = None) -> None:
+        cfg, a = self.model_config, self.arch
+        if source is None:
+            if cfg.checkpoint_dir:
+                source = SafetensorsSource(cfg.checkpoint_dir, self.device, self.dtype)
+            else:
+                big = a.hidden_size * a.intermediate_size * a.num_hidden_layers > 2e9
+                source = RandomSource(a, self.dtype, cfg.seed, self.device, consistent=not big)
+        r, w = self.rank, self.world_size
+        self.embed_tokens = source.get("model.embed_tokens.weight")
+        self.vocab_pad = (a.vocab_size + w - 1) // w * w
+        vs = slice(r * self.vocab_pad // w, min(a.vocab_size, (r + 1) * self.vocab_pad // w))
+        head_name = "lm_head.weight" if source.has("lm_head.weight") else "model.embed_tokens.weight"
+        lm = source.get(head_name, rows=vs)
+        rows_local = self.vocab_pad // w
+        if lm.shape[0] < rows_local:  # pad the last rank's shard so that every rank computes the same shape
+            lm = torch.cat([lm, torch.zeros(rows_local - lm.shape[0], lm.shape[1], dtype=lm.dtype, device=lm.device)])
+        self.lm_head = lm.contiguous()
+        self.norm_w = source.get("model.norm.weight")
+        self.layers = []
+        for i in range(a.num_hidden_layers):
+            layer = Qwen3Layer(i, r, w, self.group)
+            layer.load(source, a, r, w)
+            layer.set_fwd(self.mode)
+            self.layers.append(layer)
+        inv_freq = 1.0 / (a.rope_theta ** (torch.arange(0, a.head_dim, 2, dtype=torch.float32, device=self.device) / a.head_dim))
+        self.cos_sin_cache = _set_cos_sin_cache(inv_freq, self.max_length)
+        self.num_layers = a.num_hidden_layers
+        self.eps = a.rms_norm_eps
+
+    def set_fwd(self, mode: str = "torch") -> None:
+        if mode not in ("torch", "triton_dist", "triton_dist_AR"):
+            raise ValueError(f"unknown forward mode {mode!r}")
+        self.mode = mode
+        for layer in self.layers:
+            layer.set_fwd(mode)
+
+    # ------------------------------------------------------------------ contexts (shared by all layers)
+    def init_triton_dist_ctx(self, max_M: int) -> None:
+        H = self.arch.hidden_size
+        l0 = self.layers[0]
+        dummy = torch.empty(max_M // self.world_size, H, dtype=self.dtype, device="cuda")
+        if self.ag_ctx_qkv is None:
+            # one gather context serves both projections (same K); one scatter context serves o_proj and down
+            self.ag_ctx_qkv = create_ag_gemm_context(dummy, l0.attn.wqkv, self.rank, self.world_size, max_M)
+            self.rs_ctx = create_gemm_rs_context(max_M, H, self.rank, self.world_size, self.world_size, self.dtype)
+        for layer in self.layers:
+            layer.attn._init_ctx(max_M, ag_ctx=self.ag_ctx_qkv, rs_ctx=self.rs_ctx)
+            layer.mlp._init_ctx(max_M, ag_ctx=self.ag_ctx_qkv, rs_ctx=self.rs_ctx)
+
+    def init_triton_dist_AR_ctx(self, max_M: int, ar_method: AllReduceMethod | None = None) -> None:
+        self.ar_method = ar_method
+        if self.world_size > 1 and self.ar_ctx is None:
+            # fixed-size workspace: larger inputs are processed in row chunks
+            self.ar_ctx = create_allreduce_ctx(64 << 20, self.rank, self.world_size, self.world_size)
+        for layer in self.layers:
+            for sub in (layer.attn, layer.mlp):
+                sub.ar_ctx, sub.ar_method = self.ar_ctx, ar_method
+        # pre-size the split-K scratch so that nothing allocates inside a CUDA graph capture
+        a = self.arch
+        widest = max(self.lm_head.shape[0], a.intermediate_size // self.world_size, a.hidden_size)
+        ops.reserve_skinny_scratch(torch.device("cuda", torch.cuda.current_device()),
+                                   2 * ((min(max_M, 256) + 15) // 16 * 16) * ((widest + 127) // 128) * 128,
+                                   (widest + 127) // 128)
+
+    def finalize(self) -> None:
+        for c in (self.ar_ctx, self.ag_ctx_qkv, self.rs_ctx):
+            if c:
+                c.finalize()
+        self.ar_ctx = self.ag_ctx_qkv = self.rs_ctx = None
+
+    # ------------------------------------------------------------------ forward
+    def _reduce_norm(self, partial, residual, gamma):
+        """h = all_reduce(partial) + residual (in place); returns rmsnorm(h) * gamma."""
+        if self.world_size > 1:
+            y, _ = all_reduce_rmsnorm(partial, residual, gamma, self.eps, self.ar_ctx, self.ar_method)
+            return y
+        return ops.rmsnorm(partial, gamma, self.eps, residual=residual)
+
+    @torch.no_grad()
+    def _inference_AR(self, input_ids, position_ids, kv_cache):
+        bsz, seqlen = input_ids.shape
+        T = bsz * seqlen
+        residual = F.embedding(input_ids.reshape(-1), self.embed_tokens)  # [T, H], becomes the residual stream
+        step = {"pos": position_ids.reshape(-1).to(torch.int32), "slots": kv_cache.slots(position_ids),
+                "kv_lens": (position_ids[:, -1] + 1).to(torch.int32)}
+        x = ops.rmsnorm(residual, self.layers[0].input_norm_w, self.eps)
+        for i, layer in enumerate(self.layers):
+            part = layer.attn.partial_fwd(x, position_ids, self.cos_sin_cache, kv_cache, i, bsz, seqlen, step)
+            x = self._reduce_norm(part, residual, layer.post_norm_w)
+            part = layer.mlp.partial_fwd(x)
+            nxt = self.layers[i + 1].input_norm_w if i + 1 < self.num_layers else self.norm_w
+            x = self._reduce_norm(part, residual, nxt)
+        return x.view(bsz, seqlen, -1)  # already final-normed
+
+    @torch.no_grad()
+    def inference(self, input_ids: torch.Tensor, position_ids: torch.Tensor, kv_cache: KV_Cache,
+                  wo_lm_head: bool = False) -> torch.Tensor:
+        """input_ids / position_ids [B, S] (full batch on every rank). Returns fp32 logits [B, 1, V] of the last
+        position (or the normed hidden states with ``wo_lm_head``). ``triton_dist`` mode needs B % world == 0."""
+        bsz, seqlen = input_ids.shape
+        if self.mode == "triton_dist_AR":
+            hidden = self._inference_AR(input_ids, position_ids, kv_cache)
+        else:
+            hidden = F.embedding(input_ids, self.embed_tokens)
+            step = None
+            if self.mode == "triton_dist":
+                bl = bsz // self.world_size
+                hidden = hidden[self.rank * bl:(self.rank + 1) * bl].contiguous()
+                step = {"pos": position_ids.reshape(-1).to(torch.int32), "slots": kv_cache.slots(position_ids),
+                        "kv_lens": (position_ids[:, -1] + 1).to(torch.int32)}
+            for layer in self.layers:
+                hidden = layer.fwd(hidden, position_ids, self.cos_sin_cache, kv_cache, step)
+            hidden = layer_norm(hidden, self.eps, self.norm_w)
+            if self.mode == "triton_dist":
+                full = torch.empty((bsz, seqlen, hidden.shape[-1]), dtype=hidden.dtype, device=hidden.device)
+                dist.all_gather_into_tensor(full, hidden.contiguous(), group=self.group)
+                hidden = full
+        if wo_lm_head:
+            return hidden
+        last = hidden[:, -1, :].contiguous()
+        if self.mode == "torch":
+            local = F.linear(last, self.lm_head)
+        else:
+            local = ops.linear(last, self.lm_head)
+        if self.world_size > 1:
+            gathered = torch.empty((self.world_size, bsz, local.shape[-1]), dtype=local.dtype, device=local.device)
+            dist.all_gather_into_tensor(gathered, local.contiguous(), group=self.group)
+            local = gathered.permute(1, 0, 2).reshape(bsz, -1)
+        return local[:, : self.arch.vocab_size].float().unsqueeze(1)
