@@ -211,7 +211,23 @@ def main() -> None:
             eng = eng_saved
     if rank == 0:
         print(json.dumps(out), flush=True)
-    utils.finalize_distributed()
+    # Teardown must never outlive the measurement: CUDA graphs that captured NCCL kernels are dropped before the
+    # communicator, and a watchdog ends the process if a collective teardown stalls.
+    sys.stdout.flush()
+    watchdog = threading.Timer(30.0, lambda: os._exit(0))
+    watchdog.daemon = True
+    watchdog.start()
+    try:
+        for e in (eng, locals().get("eng_ref"), locals().get("eng_saved")):
+            if e is not None:
+                e.graph = None
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
+        utils.finalize_distributed()
+    finally:
+        watchdog.cancel()
+    os._exit(0)
 
 
 if __name__ == "__main__":

@@ -6,10 +6,11 @@
 //   * swap-AB: the 128 weight rows of a tile are the M side of tcgen05.mma (M128, K16) and the tokens,
 //     padded to a multiple of 16, are the N side, so no tensor-core rows are wasted on padding and the
 //     weights are read exactly once;
-//   * split-K over gridDim.y so that N/128 tiles x splits covers all SMs; each CTA runs a deep TMA ring
-//     (up to 12 stages, ~190 KB in flight per SM);
-//   * partial sums meet in an fp32 scratch tile through red.global.add; the CTA that takes the last
-//     ticket of a tile converts (and applies SwiGLU), writes C, and re-zeroes scratch and ticket, so the
+//   * stream-K: the (tile, k-block) work units are cut into one equal contiguous range per SM, so every
+//     SM streams the same number of weight bytes for any shape (no wave quantisation); each CTA runs a
+//     deep TMA ring (up to 12 stages, ~190 KB in flight per SM) and double-buffers its accumulator;
+//   * a tile covered by several CTAs is summed in an fp32 scratch tile through red.global.add; the CTA
+//     that takes the last ticket of a tile converts (and applies SwiGLU), writes C, and re-zeroes scratch and ticket, so the
 //     scratch is clean for the next launch without a memset.
 // The tokens are the TMEM columns, so an epilogue thread owns one output feature for all tokens and a
 // warp writes 32 consecutive features of one token: coalesced without a shared-memory transpose.
@@ -36,7 +37,9 @@ struct SkinnyParams {
   int MB;             // tokens padded to a multiple of 16
   int stages;
   int stage_bytes;
-  int kb_per_split;
+  int num_kb;         // k-blocks per tile
+  int units_total;    // tiles * num_kb
+  int units_per_cta;  // contiguous (tile, k-block) units owned by one CTA
   int up_row0;        // dual: first row of the `up` projection inside W
   int bf16;
   void* C;
@@ -47,6 +50,21 @@ struct SkinnyParams {
 
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
 
+// Stream-K: the (tile, k-block) units are numbered tile-major and cut into gridDim.x equal contiguous
+// ranges, so every SM streams the same number of weight bytes whatever the shape. A CTA's range is a
+// sequence of segments, each inside one tile; a tile covered by several CTAs is summed in scratch.
+struct Segment {
+  int tile, kb0, kb1;
+};
+__device__ __forceinline__ bool next_segment(const SkinnyParams& p, int& u, int u1, Segment& s) {
+  if (u >= u1) return false;
+  s.tile = u / p.num_kb;
+  s.kb0 = u - s.tile * p.num_kb;
+  s.kb1 = min(p.num_kb, s.kb0 + (u1 - u));
+  u += s.kb1 - s.kb0;
+  return true;
+}
+
 template <bool kDual>
 __global__ void __launch_bounds__(256, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const SkinnyParams p) {
@@ -54,28 +72,31 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t full_bar[kSkMaxStages];
   __shared__ uint64_t empty_bar[kSkMaxStages];
-  __shared__ uint64_t done_bar;
+  __shared__ uint64_t tfull_bar[2];
+  __shared__ uint64_t tempty_bar[2];
   __shared__ uint32_t tmem_slot;
   __shared__ uint32_t abort_word;
   __shared__ uint32_t last_flag;
   volatile uint32_t* abort_flag = &abort_word;
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y;
-  const int num_kb = (p.K + kSkBK - 1) / kSkBK;
-  const int kb0 = split * p.kb_per_split;
-  const int kb1 = min(num_kb, kb0 + p.kb_per_split);
-  const int nkb = max(0, kb1 - kb0);
+  const int warp = threadIdx.x >> 5;
   constexpr int kW = kDual ? 2 : 1;
-  const uint32_t tmem_cols = kW * p.MB <= 32 ? 32 : kW * p.MB <= 64 ? 64 : kW * p.MB <= 128 ? 128 : kW * p.MB <= 256 ? 256 : 512;
+  const int acc_cols = kW * p.MB;  // TMEM columns of one accumulator set
+  const uint32_t need = 2 * acc_cols;
+  const uint32_t tmem_cols = need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512;
   const uint64_t timeout_ns = 4000000000ull;
+  const int u_begin = blockIdx.x * p.units_per_cta;
+  const int u_end = min(p.units_total, u_begin + p.units_per_cta);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < p.stages; ++i) {
       mbar_init(full_bar + i, 1);
       mbar_init(empty_bar + i, 1);
     }
-    mbar_init(&done_bar, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tfull_bar + i, 1);
+      mbar_init(tempty_bar + i, 4);
+    }
     abort_word = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmW);
@@ -90,99 +111,128 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   if (warp == 0) {
     if (elect_one()) {
       uint32_t stage = 0, phase = 0;
-      for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, timeout_ns)) break;
-        uint8_t* s = smem + stage * p.stage_bytes;
-        mbar_expect_tx(full_bar + stage, p.stage_bytes);
-        tma_load_2d(s, &tmW, full_bar + stage, kb * kSkBK, tile * kSkBN);
-        if (kDual) tma_load_2d(s + kSkWBytes, &tmW, full_bar + stage, kb * kSkBK, p.up_row0 + tile * kSkBN);
-        tma_load_2d(s + kW * kSkWBytes, &tmX, full_bar + stage, kb * kSkBK, 0);
-        if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
+      int u = u_begin;
+      Segment sg;
+      bool ok = true;
+      while (ok && next_segment(p, u, u_end, sg)) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+          if (!mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, timeout_ns)) { ok = false; break; }
+          uint8_t* s = smem + stage * p.stage_bytes;
+          mbar_expect_tx(full_bar + stage, p.stage_bytes);
+          tma_load_2d(s, &tmW, full_bar + stage, kb * kSkBK, sg.tile * kSkBN);
+          if (kDual) tma_load_2d(s + kSkWBytes, &tmW, full_bar + stage, kb * kSkBK, p.up_row0 + sg.tile * kSkBN);
+          tma_load_2d(s + kW * kSkWBytes, &tmX, full_bar + stage, kb * kSkBK, 0);
+          if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
+        }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     if (elect_one()) {
       const uint32_t idesc = umma_idesc_f16(kSkBN, p.MB, p.bf16 != 0);
-      uint32_t stage = 0, phase = 0;
+      uint32_t stage = 0, phase = 0, it = 0;
+      int u = u_begin;
+      Segment sg;
       bool ok = true;
-      for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait(full_bar + stage, phase, abort_flag, timeout_ns)) { ok = false; break; }
+      while (ok && next_segment(p, u, u_end, sg)) {
+        const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(tempty_bar + acc, acc_phase ^ 1, abort_flag, timeout_ns)) break;
         tc_fence_after_sync();
-        const uint32_t s = smem_u32(smem + stage * p.stage_bytes);
-        const uint64_t dw = umma_desc_sw128_kmajor(s);
-        const uint64_t dx = umma_desc_sw128_kmajor(s + kW * kSkWBytes);
+        const uint32_t d_tmem = tmem_base + acc * acc_cols;
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+          if (!mbar_wait(full_bar + stage, phase, abort_flag, timeout_ns)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t s = smem_u32(smem + stage * p.stage_bytes);
+          const uint64_t dw = umma_desc_sw128_kmajor(s);
+          const uint64_t dx = umma_desc_sw128_kmajor(s + kW * kSkWBytes);
 #pragma unroll
-        for (int k = 0; k < kSkBK / 16; ++k) {
-          const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
-          umma_f16(tmem_base, dw + 2 * k, dx + 2 * k, idesc, accum);
-          if (kDual) umma_f16(tmem_base + p.MB, umma_desc_sw128_kmajor(s + kSkWBytes) + 2 * k, dx + 2 * k, idesc, accum);
+          for (int k = 0; k < kSkBK / 16; ++k) {
+            const uint32_t accum = (kb > sg.kb0 || k > 0) ? 1u : 0u;
+            umma_f16(d_tmem, dw + 2 * k, dx + 2 * k, idesc, accum);
+            if (kDual) umma_f16(d_tmem + p.MB, umma_desc_sw128_kmajor(s + kSkWBytes) + 2 * k, dx + 2 * k, idesc, accum);
+          }
+          umma_commit(empty_bar + stage);
+          if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
         }
-        umma_commit(empty_bar + stage);
-        if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
+        if (ok) umma_commit(tfull_bar + acc);
+        ++it;
       }
-      if (ok) umma_commit(&done_bar);
     }
     __syncwarp();
   } else if (warp >= 4) {
     const int w = warp - 4;
     const int et = threadIdx.x - 128;  // 0..127 == feature index inside the tile
-    const int n = tile * kSkBN + et;
-    bool ok = nkb > 0 ? mbar_wait(&done_bar, 0, abort_flag, timeout_ns) : true;
-    tc_fence_after_sync();
-    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(w * 32) << 16);
-    float* scratch = p.scratch + static_cast<size_t>(tile) * kW * p.MB * kSkBN;
-    auto store_out = [&](int m, float g, float u) {
-      if (m < p.M && n < p.N) {
-        const float v = kDual ? g / (1.f + __expf(-g)) * u : g;
-        if (p.bf16) static_cast<__nv_bfloat16*>(p.C)[static_cast<size_t>(m) * p.ldc + n] = __float2bfloat16(v);
-        else static_cast<__half*>(p.C)[static_cast<size_t>(m) * p.ldc + n] = __float2half(v);
-      }
-    };
-    if (ok && nkb > 0) {
+    const int lane = threadIdx.x & 31;
+    uint32_t it = 0;
+    int u = u_begin;
+    Segment sg;
+    while (next_segment(p, u, u_end, sg)) {
+      const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+      ++it;
+      const int n = sg.tile * kSkBN + et;
+      // how many CTAs contribute to this tile
+      const int first_cta = (sg.tile * p.num_kb) / p.units_per_cta;
+      const int last_cta = ((sg.tile + 1) * p.num_kb - 1) / p.units_per_cta;
+      const int contributors = last_cta - first_cta + 1;
+      if (!mbar_wait(tfull_bar + acc, acc_phase, abort_flag, timeout_ns)) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(w * 32) << 16) + acc * acc_cols;
+      float* scratch = p.scratch + static_cast<size_t>(sg.tile) * kW * p.MB * kSkBN;
+      auto store_out = [&](int m, float g, float uu) {
+        if (m < p.M && n < p.N) {
+          const float v = kDual ? g / (1.f + __expf(-g)) * uu : g;
+          if (p.bf16) static_cast<__nv_bfloat16*>(p.C)[static_cast<size_t>(m) * p.ldc + n] = __float2bfloat16(v);
+          else static_cast<__half*>(p.C)[static_cast<size_t>(m) * p.ldc + n] = __float2half(v);
+        }
+      };
       for (int c0 = 0; c0 < p.MB; c0 += 16) {
-        uint32_t g[16], u[16];
+        uint32_t g[16], uu[16];
         tmem_ld_32x16(taddr + c0, g);
-        if (kDual) tmem_ld_32x16(taddr + p.MB + c0, u);
+        if (kDual) tmem_ld_32x16(taddr + p.MB + c0, uu);
         tmem_ld_wait();
-        if (nsplit == 1) {
+        if (contributors == 1) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) store_out(c0 + j, __uint_as_float(g[j]), kDual ? __uint_as_float(u[j]) : 0.f);
+          for (int j = 0; j < 16; ++j) store_out(c0 + j, __uint_as_float(g[j]), kDual ? __uint_as_float(uu[j]) : 0.f);
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (c0 + j < p.M) {
               atomicAdd(scratch + static_cast<size_t>(c0 + j) * kSkBN + et, __uint_as_float(g[j]));
-              if (kDual) atomicAdd(scratch + static_cast<size_t>(p.MB + c0 + j) * kSkBN + et, __uint_as_float(u[j]));
+              if (kDual) atomicAdd(scratch + static_cast<size_t>(p.MB + c0 + j) * kSkBN + et, __uint_as_float(uu[j]));
             }
           }
         }
       }
-    }
-    if (nsplit > 1) {
-      // ticket: the last CTA of this tile finishes it and leaves scratch + ticket zeroed
-      __threadfence();
-      epi_bar();
-      if (et == 0) {
-        const uint32_t t = atomicAdd(p.tickets + tile, 1u);
-        last_flag = (t == static_cast<uint32_t>(nsplit - 1)) ? 1u : 0u;
-      }
-      epi_bar();
-      if (last_flag) {
+      // accumulator read: give it back to the MMA warp before the (slower) ticket protocol
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar + acc);
+      if (contributors > 1) {
+        // the last contributor of the tile finishes it and leaves scratch + ticket zeroed
         __threadfence();
-        for (int m = 0; m < p.M; ++m) {
-          float* gs = scratch + static_cast<size_t>(m) * kSkBN + et;
-          const float g = __ldcg(gs);
-          float u = 0.f;
-          __stcg(gs, 0.f);
-          if (kDual) {
-            float* us = scratch + static_cast<size_t>(p.MB + m) * kSkBN + et;
-            u = __ldcg(us);
-            __stcg(us, 0.f);
-          }
-          store_out(m, g, u);
+        epi_bar();
+        if (et == 0) {
+          const uint32_t t = atomicAdd(p.tickets + sg.tile, 1u);
+          last_flag = (t == static_cast<uint32_t>(contributors - 1)) ? 1u : 0u;
         }
-        if (et == 0) p.tickets[tile] = 0;
+        epi_bar();
+        if (last_flag) {
+          __threadfence();
+          for (int m = 0; m < p.M; ++m) {
+            float* gs = scratch + static_cast<size_t>(m) * kSkBN + et;
+            const float g = __ldcg(gs);
+            float uv = 0.f;
+            __stcg(gs, 0.f);
+            if (kDual) {
+              float* us = scratch + static_cast<size_t>(p.MB + m) * kSkBN + et;
+              uv = __ldcg(us);
+              __stcg(us, 0.f);
+            }
+            store_out(m, g, uv);
+          }
+          if (et == 0) p.tickets[sg.tile] = 0;
+        }
+        epi_bar();  // last_flag is reused by the next segment
       }
     }
   }
@@ -222,7 +272,7 @@ B200_API long long b200_gemm_skinny_scratch_floats(int M, int N, int dual) {
 // X [M, K] (row pitch ldx), W [Nw, K] (row pitch ldw), C [M, N] (row pitch ldc).
 // dual == 0: N = Nw. dual == 1: W = [gate (N rows); up (N rows)], C = silu(X gate^T) * (X up^T).
 // scratch / tickets: zero-initialised once by the caller; every call leaves them zeroed.
-// splits <= 0 lets the launcher choose.
+// splits <= 0: one CTA per SM (stream-K); splits > 0 forces tiles * splits CTAs.
 B200_API int b200_gemm_skinny(const void* X, const void* W, void* C, int M, int N, int K, int ldx, int ldw, int ldc,
                               int dual, int dtype, float* scratch, uint32_t* tickets, int splits, void* stream) {
   B200_REQUIRE(dtype == kBF16 || dtype == kF16, "gemm_skinny supports bf16/f16");
@@ -242,25 +292,21 @@ B200_API int b200_gemm_skinny(const void* X, const void* W, void* C, int M, int 
   p.bf16 = dtype == kBF16;
   p.C = C; p.ldc = ldc; p.scratch = scratch; p.tickets = tickets;
   const int tiles = (N + kSkBN - 1) / kSkBN;
-  const int num_kb = (K + kSkBK - 1) / kSkBK;
-  if (splits <= 0) {
-    const int sms = sm_count();
-    splits = (sms + tiles - 1) / tiles;          // cover the machine at least once
-    const int max_by_k = num_kb / 4 > 0 ? num_kb / 4 : 1;  // keep >= 4 k-blocks per CTA
-    if (splits > max_by_k) splits = max_by_k;
-  }
-  if (splits > num_kb) splits = num_kb;
-  if (splits < 1) splits = 1;
-  p.kb_per_split = (num_kb + splits - 1) / splits;
-  splits = (num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty splits
-  B200_REQUIRE(splits == 1 || (scratch && tickets), "split-K needs scratch and tickets");
+  p.num_kb = (K + kSkBK - 1) / kSkBK;
+  p.units_total = tiles * p.num_kb;
+  // `splits` > 0 forces that many CTAs per tile (tests); otherwise one CTA per SM
+  int ctas = splits > 0 ? tiles * splits : sm_count();
+  if (ctas > p.units_total) ctas = p.units_total;
+  p.units_per_cta = (p.units_total + ctas - 1) / ctas;
+  ctas = (p.units_total + p.units_per_cta - 1) / p.units_per_cta;
+  B200_REQUIRE(scratch && tickets, "gemm_skinny needs scratch and tickets");
   CUtensorMap tw, tx;
   int rc = make_tma_2d(&tw, W, dtype, static_cast<uint64_t>(kw) * N, K, ldw, kSkBN, kSkBK, true);
   if (rc != kOk) return rc;
   rc = make_tma_2d(&tx, X, dtype, M, K, ldx, p.MB, kSkBK, true);
   if (rc != kOk) return rc;
   const int smem = p.stages * p.stage_bytes + 1024;
-  dim3 grid(tiles, splits);
+  dim3 grid(ctas);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return dual ? launch_skinny<true>(tw, tx, p, grid, smem, s) : launch_skinny<false>(tw, tx, p, grid, smem, s);
 }
