@@ -166,3 +166,35 @@ def test_paged_decode_attention(B, Hq, Hkv, page, max_len, splits, soft_cap):
     ref, ref_lse = _paged_attn_ref(q, kc, vc, kv_lens, perm, scale, soft_cap)
     torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(lse, ref_lse, rtol=1e-2, atol=1e-2)
+
+
+def test_top_p_sampling_matches_sorted_reference():
+    from triton_distributed_b200 import ops
+    torch.manual_seed(7)
+    B, V = 6, 151936
+    logits = torch.randn(B, V, device="cuda") * 3
+    temperature, top_p = 0.6, 0.95
+    probs = torch.softmax(logits / temperature, -1)
+    sp, si = torch.sort(probs, -1, descending=True)
+    keep = (torch.cumsum(sp, -1) - sp) < top_p
+    nucleus = torch.zeros_like(probs, dtype=torch.bool).scatter(1, si, keep)
+    counts = torch.zeros(B, V, device="cuda")
+    n_draws = 400
+    for _ in range(n_draws):
+        ids = ops.top_p_sample(logits, temperature, top_p)
+        assert ids.shape == (B, 1) and ids.dtype == torch.int64
+        assert bool(nucleus.gather(1, ids).all()), "sampled a token outside the nucleus"
+        counts.scatter_add_(1, ids, torch.ones(B, 1, device="cuda"))
+    # the most likely token must be drawn about as often as its renormalised probability says
+    pn = probs * nucleus
+    pn = pn / pn.sum(-1, keepdim=True)
+    top = pn.argmax(-1, keepdim=True)
+    want = pn.gather(1, top).squeeze(1)
+    got = counts.gather(1, top).squeeze(1) / n_draws
+    assert torch.all((got - want).abs() < 4 * torch.sqrt(want * (1 - want) / n_draws) + 0.02)
+    # u = 0 picks the first kept index, and peaked logits are deterministic
+    peaked = torch.full((2, 1000), -30.0, device="cuda")
+    peaked[0, 123] = 10.0
+    peaked[1, 999] = 10.0
+    ids = ops.top_p_sample(peaked, 1.0, 0.9)
+    assert ids.flatten().tolist() == [123, 999]

@@ -22,6 +22,9 @@ def sample_token(logits: torch.Tensor, temperature: float = 0.6, top_p: float = 
     logits = logits[:, -1, :].float() if logits.dim() == 3 else logits.float()
     if temperature <= 0.0:
         return logits.argmax(-1, keepdim=True)
+    if logits.is_cuda:
+        from .. import ops
+        return ops.top_p_sample(logits, temperature, top_p)
     probs = torch.softmax(logits / temperature, dim=-1)
     sp, si = torch.sort(probs, dim=-1, descending=True)
     keep = (torch.cumsum(sp, -1) - sp) < top_p

@@ -177,6 +177,21 @@ def topk_softmax(logits: torch.Tensor, k: int, renormalize: bool = False):
     return ids, w
 
 
+def top_p_sample(logits: torch.Tensor, temperature: float, top_p: float, uniform: torch.Tensor | None = None) -> torch.Tensor:
+    """Nucleus sampling without a sort. logits fp32 [B, V]; returns int64 token ids [B, 1]."""
+    _lib.require_cuda()
+    if logits.dtype != torch.float32 or logits.stride(-1) != 1:
+        logits = logits.float().contiguous()
+    B, V = logits.shape
+    if uniform is None:
+        uniform = torch.rand(B, dtype=torch.float32, device=logits.device)
+    out = torch.empty((B, 1), dtype=torch.int64, device=logits.device)
+    _lib.call("b200_top_p_sample", ptr(logits), logits.stride(0), B, V, c_float(temperature), c_float(top_p),
+              ptr(uniform), ptr(out), stream_ptr())
+    _count()
+    return out
+
+
 def choose_kv_splits(batch: int, num_kv_heads: int, group: int, max_kv_len: int, sm_count: int = 148) -> int:
     """Split count so that batch x kv-heads x splits fills the machine about twice, with >= 256 tokens per split."""
     ctas = batch * num_kv_heads * ((group + 15) // 16)
