@@ -310,3 +310,68 @@ B200_API int b200_gemm_skinny(const void* X, const void* W, void* C, int M, int 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return dual ? launch_skinny<true>(tw, tx, p, grid, smem, s) : launch_skinny<false>(tw, tx, p, grid, smem, s);
 }
+
+// ------------------------------------------------------------------------------------------------
+// Entry point that allocates nothing (declared and documented in b200/no_alloc_api.h).
+// ------------------------------------------------------------------------------------------------
+#include "b200/no_alloc_api.h"
+
+namespace b200 {
+constexpr long long kStaticScratchFloats = 1 << 20;
+constexpr int kStaticTickets = 4096;
+// The split accumulation area and the tickets, part of the library image on every device that loads it.
+// In host code these names are stand-ins, not device addresses: the address a kernel may use comes from
+// cudaGetSymbolAddress on the device in question.
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+static __device__ __align__(256) uint32_t g_static_tickets[kStaticTickets];
+
+struct StaticArea {
+  float* scratch = nullptr;
+  uint32_t* tickets = nullptr;
+};
+// Resolved once per device, with that device current.
+static int static_area(StaticArea** out) {
+  static StaticArea areas[64];
+  int dev = 0;
+  B200_CHECK_CUDA(cudaGetDevice(&dev));
+  B200_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
+  StaticArea& a = areas[dev];
+  if (a.scratch == nullptr) {
+    void* ps = nullptr;
+    void* pt = nullptr;
+    B200_CHECK_CUDA(cudaGetSymbolAddress(&ps, g_static_scratch));
+    B200_CHECK_CUDA(cudaGetSymbolAddress(&pt, g_static_tickets));
+    a.tickets = static_cast<uint32_t*>(pt);
+    a.scratch = static_cast<float*>(ps);
+  }
+  *out = &a;
+  return kOk;
+}
+}  // namespace b200
+
+B200_API long long b200_gemm_skinny_static_capacity_floats() { return b200::kStaticScratchFloats; }
+
+B200_API int b200_gemm_skinny_static(const void* X, const void* W, void* C, int M, int N, int K, int ldx, int ldw,
+                                     int ldc, int dual, int dtype, void* stream) {
+  B200_REQUIRE(M >= 1 && M <= 256 && N >= 1, "b200_gemm_skinny_static: M must be in [1, 256] and N >= 1");
+  const long long need = b200_gemm_skinny_scratch_floats(M, N, dual);
+  const long long tiles = (N + kSkBN - 1) / kSkBN;
+  B200_REQUIRE(need <= kStaticScratchFloats && tiles <= kStaticTickets,
+               "b200_gemm_skinny_static: problem needs %lld scratch floats and %lld tiles; the built-in area holds "
+               "%lld floats and %d tiles (use b200_gemm_skinny with caller-provided scratch instead)",
+               need, tiles, kStaticScratchFloats, kStaticTickets);
+  StaticArea* area = nullptr;
+  int rc = static_area(&area);
+  if (rc != kOk) return rc;
+  return b200_gemm_skinny(X, W, C, M, N, K, ldx, ldw, ldc, dual, dtype, area->scratch, area->tickets, 0, stream);
+}
+
+B200_API int b200_gemm_skinny_static_reset(void* stream) {
+  StaticArea* area = nullptr;
+  int rc = static_area(&area);
+  if (rc != kOk) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  B200_CHECK_CUDA(cudaMemsetAsync(area->scratch, 0, sizeof(float) * kStaticScratchFloats, s));
+  B200_CHECK_CUDA(cudaMemsetAsync(area->tickets, 0, sizeof(uint32_t) * kStaticTickets, s));
+  return kOk;
+}
