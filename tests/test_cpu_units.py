@@ -1,0 +1,169 @@
+"""Host-side logic that needs no GPU: index/sort metadata references, weights I/O, sampling, helpers."""
+import json
+
+import pytest
+import torch
+
+
+def test_gather_scatter_index_is_a_stable_sort_with_padding():
+    from triton_distributed_b200 import ref
+    torch.manual_seed(0)
+    T, topk, E, align = 37, 3, 8, 16
+    ids = torch.stack([torch.randperm(E)[:topk] for _ in range(T)]).to(torch.int32)
+    counts, scatter, gather, expert_index, m_pad = ref.calc_gather_scatter_index_ref(ids, E, align)
+    assert int(counts.sum()) == T * topk and m_pad % align == 0 and gather.numel() == m_pad
+    flat = ids.reshape(-1)
+    valid = gather < T * topk
+    assert int(valid.sum()) == T * topk
+    # every tile holds one expert; rows of an expert keep their original order
+    for tile in range(m_pad // align):
+        rows = gather[tile * align:(tile + 1) * align]
+        rows = rows[rows < T * topk].long()
+        assert torch.all(flat[rows] == expert_index[tile])
+        assert torch.all(rows[1:] > rows[:-1])
+    # scatter is the inverse of gather
+    assert torch.equal(gather[scatter.reshape(-1).long()].long(), torch.arange(T * topk))
+
+
+def test_moe_align_per_rank_blocks():
+    from triton_distributed_b200 import ref
+    torch.manual_seed(1)
+    T, topk, E, bm, ranks = 64, 2, 4, 8, 4
+    ids = torch.randint(0, E, (T, topk), dtype=torch.int32)
+    sorted_ids, expert_ids, barrier_ids, rank_blocks, npad = ref.moe_align_block_size_ref(ids, E, bm, ranks)
+    assert npad == sorted_ids.numel() == expert_ids.numel() * bm and int(rank_blocks.sum()) == expert_ids.numel()
+    per = T // ranks * topk
+    for tile in range(expert_ids.numel()):
+        rows = sorted_ids[tile * bm:(tile + 1) * bm]
+        rows = rows[rows < T * topk].long()
+        assert torch.all(ids.reshape(-1)[rows] == expert_ids[tile])
+        assert torch.all(rows // per == barrier_ids[tile])
+    assert sorted(sorted_ids[sorted_ids < T * topk].tolist()) == list(range(T * topk))
+
+
+def test_ag_moe_schedule_orders_tiles_by_arrival_stage():
+    from triton_distributed_b200 import ref
+    torch.manual_seed(2)
+    T, topk, E, bm, world = 128, 2, 4, 16, 4
+    ids = torch.randint(0, E, (T, topk), dtype=torch.int32)
+    for rank in range(world):
+        gather, tile_expert, s0, s1, order = ref.ag_moe_tile_schedule_ref(ids, E, bm, rank, world)
+        stage = (s1.long() - rank) % world
+        assert torch.all(stage[order.long()][1:] >= stage[order.long()][:-1])
+        assert sorted(order.tolist()) == list(range(tile_expert.numel()))
+        per = T // world
+        for tile in range(tile_expert.numel()):
+            rows = gather[tile * bm:(tile + 1) * bm]
+            rows = rows[rows < T * topk].long()
+            src = (rows // topk) // per
+            assert int(src.min()) == int(s0[tile]) and int(src.max()) == int(s1[tile])
+
+
+def test_fp8_block_quant_roundtrip():
+    from triton_distributed_b200 import ref
+    torch.manual_seed(3)
+    x = torch.randn(16, 512) * 3
+    q, s = ref.fp8_quant_ref(x)
+    assert q.dtype == torch.float8_e4m3fn and s.shape == (16, 4)
+    back = ref.fp8_dequant_ref(q, s, dtype=torch.float32)
+    assert (back - x).abs().max() <= x.abs().max() * 0.07
+    # quantisation of an already representable tensor is exact
+    q2, s2 = ref.fp8_quant_ref(back)
+    torch.testing.assert_close(ref.fp8_dequant_ref(q2, s2, dtype=torch.float32), back, rtol=1e-5, atol=1e-5)
+
+
+def test_combine_partials_skips_empty_and_matches_full_softmax():
+    from triton_distributed_b200 import ref
+    torch.manual_seed(4)
+    s = torch.randn(5, 3, 40)
+    v = torch.randn(5, 40, 8)
+    full = torch.softmax(s.reshape(5, 120)[:, :], -1)  # three parts of 40 keys each -> one softmax over 120
+    vv = torch.cat([v, v * 2, v * 3], 1)
+    want = torch.einsum("bl,bld->bd", full, vv)
+    parts_o, parts_l = [], []
+    for r, scale in enumerate((1, 2, 3)):
+        sr = s[:, r]
+        parts_l.append(torch.logsumexp(sr, -1))
+        parts_o.append(torch.einsum("bl,bld->bd", torch.softmax(sr, -1), v * scale))
+    parts_o.append(torch.zeros(5, 8))
+    parts_l.append(torch.full((5,), float("-inf")))
+    out, lse = ref.combine_partials_ref(torch.stack(parts_o), torch.stack(parts_l))
+    torch.testing.assert_close(out, want, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(lse, torch.logsumexp(s.reshape(5, 120), -1), rtol=1e-5, atol=1e-5)
+
+
+def test_checkpoint_writer_and_sliced_reader(tmp_path):
+    from triton_distributed_b200.models import ARCHS
+    from triton_distributed_b200.models.weights import (RandomSource, SafetensorsSource, hf_param_shapes,
+                                                       read_arch_from_checkpoint, write_random_checkpoint)
+    arch = ARCHS["tiny-qwen3"]
+    write_random_checkpoint(str(tmp_path), arch, torch.bfloat16, seed=5, max_shard_bytes=2 << 20)
+    idx = json.load(open(tmp_path / "model.safetensors.index.json"))
+    assert set(idx["weight_map"]) == set(hf_param_shapes(arch))
+    assert read_arch_from_checkpoint(str(tmp_path)) == arch
+    src = SafetensorsSource(str(tmp_path), device="cpu")
+    rnd = RandomSource(arch, torch.bfloat16, seed=5, device="cpu", consistent=True)
+    name = "model.layers.1.mlp.down_proj.weight"
+    assert torch.equal(src.get(name, cols=slice(128, 256)), rnd.get(name, cols=slice(128, 256)))
+    assert torch.equal(src.get("model.layers.0.self_attn.q_proj.weight", rows=slice(0, 128)),
+                       rnd.get("model.layers.0.self_attn.q_proj.weight", rows=slice(0, 128)))
+    assert torch.all(src.get("model.norm.weight") == 1)
+    # per-slice random source: right shapes, deterministic
+    fast = RandomSource(arch, torch.bfloat16, seed=5, device="cpu", consistent=False)
+    a = fast.get(name, cols=slice(0, 64))
+    assert a.shape == (arch.hidden_size, 64) and torch.equal(a, fast.get(name, cols=slice(0, 64)))
+
+
+def test_sample_token_cpu_paths():
+    from triton_distributed_b200.models import sample_token
+    logits = torch.full((2, 1, 50), -20.0)
+    logits[0, 0, 7] = 5.0
+    logits[1, 0, 33] = 5.0
+    assert sample_token(logits, temperature=0.0).flatten().tolist() == [7, 33]
+    torch.manual_seed(0)
+    assert sample_token(logits, temperature=0.6, top_p=0.9).flatten().tolist() == [7, 33]
+
+
+def test_allreduce_method_names_and_auto_choice():
+    from triton_distributed_b200.kernels.allreduce import AllReduceMethod, get_allreduce_methods, to_allreduce_method
+    from triton_distributed_b200.kernels.nvidia.allreduce import get_auto_allreduce_method
+    assert set(get_allreduce_methods()) >= {"double_tree", "one_shot", "two_shot", "one_shot_multimem", "two_shot_multimem"}
+    assert to_allreduce_method("two_shot_multimem") is AllReduceMethod.TwoShot_Multimem
+    with pytest.raises(ValueError):
+        to_allreduce_method("ring")
+    assert get_auto_allreduce_method(8 << 10, has_multicast=True) is AllReduceMethod.OneShot_Multimem
+    assert get_auto_allreduce_method(8 << 20, has_multicast=True) is AllReduceMethod.TwoShot_Multimem
+    assert get_auto_allreduce_method(8 << 10, has_multicast=False) is AllReduceMethod.OneShot
+    assert get_auto_allreduce_method(8 << 20, has_multicast=False) is AllReduceMethod.TwoShot
+
+
+def test_trace_merge_and_helpers(capsys):
+    from triton_distributed_b200 import utils
+    a = {"traceEvents": [{"ph": "X", "pid": 1, "tid": 2, "name": "k"}, {"ph": "M", "pid": 1, "args": {"name": "proc"}}], "meta": 1}
+    b = {"traceEvents": [{"ph": "X", "pid": 1, "tid": 2, "name": "k"}]}
+    m = utils.merge_traces([a, b])
+    assert len(m["traceEvents"]) == 3 and m["meta"] == 1
+    assert m["traceEvents"][2]["pid"] == 1 + 100_000_000 and m["traceEvents"][1]["args"]["name"] == "proc_rank0"
+    utils.assert_allclose(torch.ones(4), torch.ones(4), 1e-3, 1e-3, verbose=False)
+    with pytest.raises(RuntimeError, match="mismatches"):
+        utils.assert_allclose(torch.ones(4), torch.zeros(4), 1e-3, 1e-3)
+    utils.dist_print("hello", allowed_ranks="all", prefix=True)
+    assert "hello" in capsys.readouterr().out
+
+
+def test_native_library_builds_and_reports_errors():
+    """The shared object loads without a driver; entry points that need one fail with a message, not a crash."""
+    import ctypes
+    from triton_distributed_b200 import _lib
+    lib = _lib.load()
+    assert lib.b200_symm_ctx_size() >= 96
+    lib.b200_gemm_skinny_scratch_floats.restype = ctypes.c_longlong
+    assert lib.b200_gemm_skinny_scratch_floats(8, 1280, 0) == 10 * 16 * 128
+    assert lib.b200_allreduce_ws_factor(0, 8, 0) == 8 and lib.b200_allreduce_ws_factor(3, 8, 1) == 3
+    if not torch.cuda.is_available():
+        h = ctypes.c_void_p()
+        rc = lib.b200_heap_create(0, 0, 1, ctypes.c_uint64(1 << 20), 0, ctypes.byref(h))
+        assert rc != 0 and lib.b200_last_error()
+        from triton_distributed_b200 import ops
+        with pytest.raises(RuntimeError, match="CUDA"):
+            ops.gemm(torch.zeros(2, 8), torch.zeros(2, 8))
