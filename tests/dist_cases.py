@@ -241,6 +241,40 @@ def gemm_rs_shapes():
     _gemm_rs_case(8192, 8192, 3584, torch.bfloat16, iters=2)
 
 
+@case
+def moe_tp_ag_group_gemm_and_reduce_rs():
+    from triton_distributed_b200 import ref
+    from triton_distributed_b200.kernels.nvidia import (ag_group_gemm, create_ag_group_gemm_context, create_moe_rs_context,
+                                                        moe_reduce_rs, select_experts)
+    rank, world = _rank_world()
+    group = U.TP_GROUP()
+    for (Tr, topk, E, K, N, H) in ((64, 2, 8, 256, 128, 256), (256, 8, 32, 1024, 384, 1024), (100, 4, 16, 520, 200, 776)):
+        T = Tr * world
+        torch.manual_seed(100 + rank)
+        a = torch.randn(Tr, K, device="cuda", dtype=torch.bfloat16)
+        logits = torch.randn(Tr, E, device="cuda")
+        torch.manual_seed(7)
+        w1 = torch.randn(E, N, K, device="cuda", dtype=torch.bfloat16) * 0.05   # this rank's N shard (same values on all ranks is fine)
+        w2 = torch.randn(E, H, N, device="cuda", dtype=torch.bfloat16) * 0.05   # K shard of the down projection
+        ids, wt = select_experts(group, world, topk, torch.bfloat16, "cuda", logits)
+        ids_ref, wt_ref = ref.select_experts_ref(logits, topk, group)
+        assert torch.equal(ids, ids_ref)
+        ctx = create_ag_group_gemm_context(T, N, K, E, topk, torch.bfloat16, rank, world)
+        rctx = create_moe_rs_context(group, world, T, H, E, topk, torch.bfloat16, torch.bfloat16)
+        for it in range(3):
+            up = ag_group_gemm(a, w1, ctx, ids)
+            torch.cuda.synchronize()
+            torch.testing.assert_close(up.float(), ref.ag_group_gemm_ref(a, w1, ids, group).float(), rtol=2e-2, atol=2e-2,
+                                       msg=lambda s_: f"ag_group_gemm Tr={Tr} it={it}: {s_}")
+            x = (up * (0.5 + rank)).contiguous()
+            down = moe_reduce_rs(x, w2, ids, wt, rctx)
+            torch.cuda.synchronize()
+            torch.testing.assert_close(down.float(), ref.moe_reduce_rs_ref(x, w2, ids, wt, group).float(), rtol=5e-2,
+                                       atol=5e-2 * world, msg=lambda s_: f"moe_reduce_rs Tr={Tr} it={it}: {s_}")
+        ctx.finalize()
+        rctx.finalize()
+
+
 def main() -> int:
     U.initialize_distributed(seed=0, heap_bytes=int(os.environ.get("B200DIST_TEST_HEAP", 3 << 30)))
     rank, world = _rank_world()

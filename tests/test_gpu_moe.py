@@ -1,0 +1,92 @@
+"""MoE kernels on one GPU: routing metadata against the CPU references, grouped GEMM against per-expert matmuls,
+and the fused AG / RS forms with this GPU as the only rank."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("T,topk,E,bm,segments", [(37, 3, 8, 16, 1), (512, 8, 128, 128, 1), (64, 2, 4, 8, 4), (1024, 8, 256, 128, 8)])
+def test_moe_sort_matches_reference(T, topk, E, bm, segments):
+    from triton_distributed_b200 import ref
+    from triton_distributed_b200.kernels.nvidia import create_sort_plan, moe_sort, order_tiles
+    torch.manual_seed(0)
+    ids = torch.stack([torch.randperm(E)[:topk] for _ in range(T)]).to(torch.int32).cuda()
+    plan = create_sort_plan(T * topk, topk, E, bm, segments)
+    for _ in range(2):  # epochs
+        moe_sort(ids, plan, tokens_per_rank=max(1, T // 4))
+    torch.cuda.synchronize()
+    m_pad, tiles = int(plan.totals[0]), int(plan.totals[1])
+    if segments == 1:
+        counts, _, gather, expert_index, want_pad = ref.calc_gather_scatter_index_ref(ids.cpu(), E, bm)
+        assert m_pad == want_pad and tiles == want_pad // bm
+        assert torch.equal(plan.sorted_ids[:m_pad].cpu(), gather)
+        assert torch.equal(plan.tile_expert[:tiles].cpu(), expert_index)
+        assert torch.equal(plan.group_count.cpu(), counts)
+        world = 4
+        _, _, s0, s1, order = ref.ag_moe_tile_schedule_ref(ids.cpu(), E, bm, 1, world) if T % world == 0 else (0, 0, None, None, None)
+        if s0 is not None:
+            assert torch.equal(plan.tile_seg_start[:tiles].cpu(), s0) and torch.equal(plan.tile_seg_end[:tiles].cpu(), s1)
+            got = order_tiles(plan, 1, world)
+            torch.cuda.synchronize()
+            assert torch.equal(got[:tiles].cpu(), order)
+    else:
+        sorted_ids, expert_ids, barrier_ids, rank_blocks, npad = ref.moe_align_block_size_ref(ids.cpu(), E, bm, segments)
+        assert m_pad == npad
+        assert torch.equal(plan.sorted_ids[:m_pad].cpu(), sorted_ids)
+        assert torch.equal(plan.tile_expert[:tiles].cpu(), expert_ids)
+        assert torch.equal(plan.tile_seg_end[:tiles].cpu(), barrier_ids)
+        assert torch.equal(plan.totals[2:].cpu(), torch.cumsum(rank_blocks, 0).to(torch.int32))
+    assert int(plan.status[0]) == 0
+
+
+@pytest.mark.parametrize("T,topk,E,N,K", [(64, 2, 4, 128, 64), (300, 4, 16, 384, 512), (1024, 8, 32, 200, 1032)])
+def test_grouped_gemm_matches_per_expert_matmul(T, topk, E, N, K):
+    from triton_distributed_b200 import ref
+    from triton_distributed_b200.kernels.nvidia import grouped_gemm
+    torch.manual_seed(1)
+    a = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(E, N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    ids = torch.stack([torch.randperm(E)[:topk] for _ in range(T)]).to(torch.int32).cuda()
+    out = grouped_gemm(a, w, ids)
+    torch.cuda.synchronize()
+    want = ref.grouped_gemm_ref(a.repeat_interleave(topk, 0), w, ids.reshape(-1).long())
+    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
+    # per-pair input and routing weights (the down-projection form)
+    x = torch.randn(T * topk, K, device="cuda", dtype=torch.bfloat16)
+    sc = torch.rand(T, topk, device="cuda")
+    out2 = grouped_gemm(x, w, ids, a_per_pair=True, row_scale=sc)
+    want2 = ref.grouped_gemm_ref(x, w, ids.reshape(-1).long()) * sc.reshape(-1, 1)
+    torch.testing.assert_close(out2.float(), want2, rtol=2e-2, atol=2e-2)
+
+
+def test_ag_group_gemm_and_moe_reduce_rs_world1(dist1):
+    from triton_distributed_b200 import ref
+    from triton_distributed_b200.kernels.nvidia import (ag_group_gemm, create_ag_group_gemm_context, create_moe_rs_context,
+                                                        moe_reduce_rs)
+    from triton_distributed_b200.runtime.heap import get_heap
+    torch.manual_seed(2)
+    T, topk, E, K, N = 256, 4, 16, 512, 384
+    a = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    w1 = torch.randn(E, N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    logits = torch.randn(T, E, device="cuda")
+    wt, ids = torch.topk(torch.softmax(logits, -1), topk, -1)
+    ids = ids.to(torch.int32)
+    ctx = create_ag_group_gemm_context(T, N, K, E, topk, torch.bfloat16, 0, 1)
+    for _ in range(3):
+        up = ag_group_gemm(a, w1, ctx, ids)
+        torch.cuda.synchronize()
+        get_heap().check_status("ag_group_gemm")
+        torch.testing.assert_close(up.float(), ref.ag_group_gemm_ref(a, w1, ids).float(), rtol=2e-2, atol=2e-2)
+    # the reference's [E, K, N] weight layout is accepted too
+    up_t = ag_group_gemm(a, w1.transpose(1, 2).contiguous(), ctx, ids)
+    torch.testing.assert_close(up_t, up)
+    ctx.finalize()
+    w2 = torch.randn(E, 640, N, device="cuda", dtype=torch.bfloat16) * 0.05
+    rctx = create_moe_rs_context(dist1, 1, T, 640, E, topk, torch.bfloat16, torch.bfloat16)
+    for _ in range(3):
+        down = moe_reduce_rs(up, w2, ids, wt, rctx)
+        torch.cuda.synchronize()
+        get_heap().check_status("moe_reduce_rs")
+        torch.testing.assert_close(down.float(), ref.moe_reduce_rs_ref(up, w2, ids, wt).float(), rtol=3e-2, atol=3e-2)
+    rctx.finalize()

@@ -1,0 +1,119 @@
+"""AG + grouped GEMM (tensor-parallel MoE up-projection) in one fused sm_100a kernel.
+
+API parity with ``python/triton_dist/kernels/nvidia/allgather_group_gemm.py`` (``create_ag_group_gemm_context`` :334,
+``ag_group_gemm`` :398): ``a`` is this rank's tokens ``[ntokens / r, K]``, ``b`` the experts' weight shards, and the
+result row ``t * topk + k`` is token t times the weights of its k-th expert.
+
+Weights are consumed K-major, ``[E, N_per_rank, K]`` (the Hugging Face layout of an expert's ``nn.Linear``). The
+reference's ``[E, K, N_per_rank]`` layout is accepted and transposed once per weight tensor.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+from ... import _lib, ops
+from ..._lib import dtype_code, ptr, stream_ptr
+from ...runtime.heap import SymmHeap, get_heap
+from .moe_utils import MoeSortPlan, create_sort_plan, moe_sort, order_tiles
+
+
+@dataclasses.dataclass
+class MoEAllGatherGroupGEMMTensorParallelContext:
+    rank: int
+    num_ranks: int
+    max_ntokens: int
+    N_per_rank: int
+    K: int
+    num_experts: int
+    topk: int
+    dtype: torch.dtype
+    heap: SymmHeap
+    symm_workspaces: list[torch.Tensor]
+    symm_ready: torch.Tensor
+    rank_cnt: torch.Tensor
+    rank_flag: torch.Tensor
+    sync: torch.Tensor
+    plans: dict
+    _weights_nk: dict
+
+    def plan_for(self, ntokens: int) -> MoeSortPlan:
+        if ntokens not in self.plans:
+            self.plans[ntokens] = create_sort_plan(ntokens * self.topk, self.topk, self.num_experts, 128, 1)
+        return self.plans[ntokens]
+
+    def weights_nk(self, b: torch.Tensor) -> torch.Tensor:
+        """[E, N, K] view of the weights; a [E, K, N] tensor is transposed once and cached."""
+        if b.shape[2] == self.K and b.shape[1] == self.N_per_rank and self.K != self.N_per_rank:
+            return b
+        if b.shape[1] == self.K and b.shape[2] == self.N_per_rank:
+            key = (b.data_ptr(), b._version)
+            if key not in self._weights_nk:
+                self._weights_nk = {key: b.transpose(1, 2).contiguous()}
+            return self._weights_nk[key]
+        return b  # square: taken as [E, N, K]
+
+    def finalize(self) -> None:
+        torch.cuda.synchronize()
+        for t in self.symm_workspaces + [self.symm_ready]:
+            self.heap.free(t)
+        self.symm_workspaces = []
+
+
+def create_ag_group_gemm_context(max_ntokens: int, N_per_rank: int, K: int, num_experts: int, topk: int,
+                                 dtype: torch.dtype, rank: int, num_ranks: int, num_local_ranks: int | None = None,
+                                 ag_intranode_stream=None, ag_internode_stream=None, BLOCK_SIZE_M: int = 128,
+                                 BLOCK_SIZE_N: int = 128, BLOCK_SIZE_K: int = 64, GROUP_SIZE_M: int = 8, stages: int = 6,
+                                 num_warps: int = 12) -> MoEAllGatherGroupGEMMTensorParallelContext:
+    heap = get_heap()
+    if num_ranks != heap.world:
+        raise ValueError("AG + grouped GEMM spans the ranks of the symmetric heap (single node)")
+    ws = [heap.create_tensor((max_ntokens, K), dtype, align=1024) for _ in range(2)]
+    ready = heap.create_tensor((16,), torch.int32)
+    z = lambda n: torch.zeros(n, dtype=torch.int32, device="cuda")  # noqa: E731
+    ctx = MoEAllGatherGroupGEMMTensorParallelContext(rank, num_ranks, max_ntokens, N_per_rank, K, num_experts, topk, dtype,
+                                                     heap, ws, ready, z(16), z(16), z(4), {}, {})
+    heap.barrier_all()
+    torch.cuda.synchronize()
+    return ctx
+
+
+def ag_group_gemm(a: torch.Tensor, b: torch.Tensor, ctx: MoEAllGatherGroupGEMMTensorParallelContext,
+                  full_topk_ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """a [ntokens / r, K]; b [E, N / r, K] (or [E, K, N / r]); full_topk_ids int32 [ntokens, topk] (all ranks' tokens).
+    Returns [ntokens * topk, N / r]."""
+    Tr, K = a.shape
+    T = Tr * ctx.num_ranks
+    if T > ctx.max_ntokens or K != ctx.K or full_topk_ids.shape != (T, ctx.topk):
+        raise ValueError("problem does not fit the context")
+    w = ctx.weights_nk(b)
+    E, N, _ = w.shape
+    plan = ctx.plan_for(T)
+    moe_sort(full_topk_ids.to(torch.int32).contiguous(), plan, tokens_per_rank=Tr)
+    order = order_tiles(plan, ctx.rank, ctx.num_ranks, 0)
+    if out is None:
+        out = torch.empty((T * ctx.topk, N), dtype=a.dtype, device=a.device)
+    _lib.call("b200_ag_grouped_gemm", ctx.heap.ctx, ptr(a.contiguous()), ptr(ctx.symm_workspaces[0]),
+              ptr(ctx.symm_workspaces[1]), Tr, ctx.topk, ptr(w), E, N, K, ptr(plan.sorted_ids), ptr(plan.tile_expert),
+              ptr(order), ptr(plan.totals), plan.max_tiles, ptr(out), out.stride(0), ptr(ctx.symm_ready), ptr(ctx.rank_cnt),
+              ptr(ctx.rank_flag), ptr(ctx.sync), dtype_code(a.dtype), stream_ptr())
+    ops._count()
+    return out
+
+
+def grouped_gemm(a: torch.Tensor, w: torch.Tensor, topk_ids: torch.Tensor, a_per_pair: bool = False,
+                 row_scale: torch.Tensor | None = None, plan: MoeSortPlan | None = None) -> torch.Tensor:
+    """Local grouped GEMM: out[t * topk + k] = a[t (or pair)] @ w[topk_ids[t, k]].T (* row_scale). w [E, N, K]."""
+    T, topk = topk_ids.shape
+    E, N, K = w.shape
+    if plan is None:
+        plan = create_sort_plan(T * topk, topk, E, 128, 1, a.device)
+    moe_sort(topk_ids.to(torch.int32).contiguous(), plan)
+    out = torch.empty((T * topk, N), dtype=a.dtype, device=a.device)
+    rs = row_scale.reshape(-1).float().contiguous() if row_scale is not None else None
+    _lib.call("b200_grouped_gemm", ptr(a), a.stride(0), 1 if a_per_pair else topk, ptr(w), E, N, K, T * topk,
+              ptr(plan.sorted_ids), ptr(plan.tile_expert), None, ptr(plan.totals), plan.max_tiles, ptr(out), out.stride(0),
+              ptr(rs), dtype_code(a.dtype), stream_ptr())
+    ops._count()
+    return out
