@@ -275,6 +275,71 @@ def moe_tp_ag_group_gemm_and_reduce_rs():
         rctx.finalize()
 
 
+@case
+def ep_all_to_all_dispatch_combine():
+    from triton_distributed_b200 import ref
+    from triton_distributed_b200.kernels.nvidia import all_to_all_post_process, create_all_to_all_context, fast_all_to_all
+    from triton_distributed_b200.layers.nvidia import EPAll2AllLayer
+    rank, world = _rank_world()
+    group = U.TP_GROUP()
+    for (T, H, E, topk) in ((64, 256, 8 * world, 2), (128, 7168, 32 * world, 8)):
+        torch.manual_seed(50 + rank)
+        x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+        logits = torch.randn(T, E, device="cuda")
+        wt, ids = torch.topk(torch.softmax(logits, -1), topk, -1)
+        ids = ids.to(torch.int32)
+        # --- sorted-rows all-to-all (reference low-latency API) ---
+        flat = ids.reshape(-1).long()
+        order = torch.argsort(flat, stable=True)
+        send = x.repeat_interleave(topk, 0)[order].contiguous()
+        cum = torch.cat([torch.zeros(1, dtype=torch.int64, device="cuda"), torch.cumsum(torch.bincount(flat, minlength=E), 0)]).to(torch.int32)
+        scale = torch.rand(send.shape[0], device="cuda")
+        actx = create_all_to_all_context(T * topk, H, rank, E, world, E // world, torch.bfloat16)
+        for it in range(3):
+            splits, recv, rscale = fast_all_to_all(actx, send, cum, scale)
+            torch.cuda.synchronize()
+            want_splits, want_recv, want_scale = ref.fast_all_to_all_ref(send, cum, T * topk, group, scale[:, None])
+            assert torch.equal(splits, want_splits), "splits"
+            got, gscale = all_to_all_post_process(actx, splits, recv, rscale)
+            want, wscale = ref.all_to_all_post_process_ref(T * topk, want_splits, want_recv, want_scale)
+            assert torch.equal(got, want), f"fast_all_to_all rows it={it}"
+            assert torch.equal(gscale, wscale.view(-1)), "scales"
+        actx.finalize()
+        # --- fused dispatch / combine layer ---
+        for fp8 in (False, True):
+            layer = EPAll2AllLayer(group, T, H, topk, rank, E, world, world, torch.bfloat16, fp8=fp8)
+            for it in range(2):
+                res = layer.dispatch(x, ids)
+                torch.cuda.synchronize()
+                sorted_ids, tile_expert, totals, rows_per_expert = layer.recv_plan()
+                m_pad = int(totals[0])
+                sel = sorted_ids[:m_pad]
+                valid = sel < world * layer.max_m
+                want_rows, want_expert, origin = ref.ep_dispatch_ref(x, ids, E, group)
+                assert int(valid.sum()) == want_rows.shape[0], "received row count"
+                exp_of_row = tile_expert[: m_pad // 128].repeat_interleave(128)[valid]
+                assert torch.equal(exp_of_row, want_expert), "expert grouping"
+                if fp8:
+                    q, sc = res
+                    rows = ref.fp8_dequant_ref(q[sel[valid].long()], sc[sel[valid].long()], dtype=torch.float32)
+                    wq, ws = ref.fp8_quant_ref(want_rows)
+                    torch.testing.assert_close(rows, ref.fp8_dequant_ref(wq, ws, dtype=torch.float32), rtol=0.13, atol=1e-3)  # one e4m3 ulp: tie rounding differs between converters
+                    expert_out = torch.zeros(world * layer.max_m, H, device="cuda", dtype=torch.bfloat16)
+                    expert_out[sel[valid].long()] = rows.to(torch.bfloat16)
+                    tol = 0.1
+                else:
+                    assert torch.equal(res[sel[valid].long()], want_rows), "dispatched rows"
+                    expert_out = res
+                    tol = 2e-2
+                back = layer.combine(expert_out, wt)
+                torch.cuda.synchronize()
+                torch.testing.assert_close(back.float(), x.float() * wt.sum(-1, keepdim=True), rtol=tol, atol=tol)
+                if not fp8:
+                    back2 = layer.combine(expert_out)
+                    torch.testing.assert_close(back2.float(), x.float() * topk, rtol=2e-2, atol=2e-2 * topk)
+            layer.finalize()
+
+
 def main() -> int:
     U.initialize_distributed(seed=0, heap_bytes=int(os.environ.get("B200DIST_TEST_HEAP", 3 << 30)))
     rank, world = _rank_world()

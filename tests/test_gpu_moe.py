@@ -90,3 +90,36 @@ def test_ag_group_gemm_and_moe_reduce_rs_world1(dist1):
         get_heap().check_status("moe_reduce_rs")
         torch.testing.assert_close(down.float(), ref.moe_reduce_rs_ref(up, w2, ids, wt).float(), rtol=3e-2, atol=3e-2)
     rctx.finalize()
+
+
+def test_ep_dispatch_combine_world1(dist1):
+    from triton_distributed_b200 import ref
+    from triton_distributed_b200.layers.nvidia import EPAll2AllLayer
+    from triton_distributed_b200.runtime.heap import get_heap
+    torch.manual_seed(3)
+    T, H, E, topk = 96, 512, 16, 4
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    wt, ids = torch.topk(torch.softmax(torch.randn(T, E, device="cuda"), -1), topk, -1)
+    ids = ids.to(torch.int32)
+    for fp8 in (False, True):
+        layer = EPAll2AllLayer(dist1, T, H, topk, 0, E, 1, 1, torch.bfloat16, fp8=fp8)
+        for _ in range(3):
+            res = layer.dispatch(x, ids)
+            torch.cuda.synchronize()
+            get_heap().check_status("ep dispatch")
+            sorted_ids, tile_expert, totals, rows_per_expert = layer.recv_plan()
+            assert int(rows_per_expert.sum()) == T * topk
+            assert torch.equal(rows_per_expert.cpu(), torch.bincount(ids.reshape(-1).long().cpu(), minlength=E).to(torch.int32))
+            if fp8:
+                q, sc = res
+                rows = ref.fp8_dequant_ref(q[: T * topk], sc[: T * topk], dtype=torch.bfloat16)
+                expert_out = torch.zeros(layer.max_m, H, device="cuda", dtype=torch.bfloat16)
+                expert_out[: T * topk] = rows
+            else:
+                expert_out = res
+            out = layer.combine(expert_out, wt)
+            torch.cuda.synchronize()
+            get_heap().check_status("ep combine")
+            torch.testing.assert_close(out.float(), x.float() * wt.sum(-1, keepdim=True), rtol=0.1 if fp8 else 2e-2,
+                                       atol=0.1 if fp8 else 2e-2)
+        layer.finalize()

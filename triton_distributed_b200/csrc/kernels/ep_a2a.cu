@@ -1,0 +1,385 @@
+// Expert-parallel all-to-all: dispatch (tokens -> the ranks that own their experts) and combine (expert outputs
+// -> back to the token's rank, summed over its k experts), plus the generic sorted-rows all-to-all of the
+// reference's low-latency API.
+//
+//   ep_row_a2a    rows already sorted by global expert; rank d receives the rows of its experts from source s at
+//                 rows s * max_m ... of its receive buffer, with the per-expert counts and optional per-row scales
+//                 (fast_all_to_all, python/triton_dist/kernels/nvidia/low_latency_all_to_all.py:35-118, 198-257)
+//   ep_dispatch   fused permute + optional online fp8 quantisation + send: one warp per token reads the bf16 row
+//                 once, quantises every 128 channels to e4m3 with an fp32 scale (amax / 448, as in
+//                 tutorials/04-deepseek-infer-all2all.py:189-193) and stores the row (+ scales) straight into the
+//                 slot of each of its k experts' ranks, in the sender's expert order (grouped-GEMM ready)
+//   ep_combine    sends the expert outputs back and, once all peers' rows have landed, sums the k returned rows of
+//                 every token with its routing weights (the reference leaves the weighted sum to torch index_add,
+//                 test_all_to_all.py:366-367, and kernel_combine_token ignores the weights, ep_a2a.py:192-206)
+//   ep_recv_plan  turns the received [source, local expert] counts into the sorted-row / tile metadata of the
+//                 grouped GEMM (rows grouped by local expert, then source), without a host round trip
+//                 (kernel_get_ag_splits_and_recv_offset + CPU polling in the reference, ep_a2a.py:243-306,
+//                 layers/nvidia/ep_a2a_layer.py:173-193)
+//
+// Many CTAs per kernel (the reference uses one CTA per peer), 16-byte P2P stores, receive buffers double-buffered
+// by epoch parity, one release flag per (source, destination) written by the last CTA to finish, bounded waits.
+#include "b200/host.h"
+#include "b200/primitives.cuh"
+
+#include <cstring>
+#include <cuda_fp8.h>
+
+namespace b200 {
+
+constexpr int kEpThreads = 256;
+constexpr int kEpMaxExperts = 1024;
+
+struct EpParams {
+  int world_unused;
+  int T, H, topk, E, E_local, max_m;
+  int row_bytes;            // payload bytes per row as sent (H * 2 for bf16, H for fp8)
+  int scale_floats;         // fp32 scales per row (0 = none)
+  int quant;                // dispatch: 1 = bf16 -> e4m3 online
+  const void* x;            // dispatch: [T, H] bf16; row_a2a: rows [n, row_bytes]
+  const float* x_scale;     // row_a2a: [n, scale_floats] or null
+  const int32_t* topk_ids;  // [T, topk]
+  const int32_t* pair_pos;  // [T * topk] position of every pair in the expert-sorted order (unpadded sort)
+  const int32_t* counts;    // [E] pairs per global expert (dispatch / combine); row_a2a: null
+  const int32_t* cum_in;    // row_a2a: [E + 1] cumulative splits
+  uint8_t* recv[2];         // symmetric [world * max_m, row_bytes]
+  float* recv_scale[2];     // symmetric [world * max_m, scale_floats]
+  int32_t* recv_splits[2];  // symmetric [world, E_local]
+  uint32_t* flags;          // symmetric u32[2][kMaxRanks]
+  uint32_t* sync;           // local u32[4]: epoch, done counter, CTA arrival counter
+  // combine
+  const void* expert_out;   // [world * max_m, H] bf16 rows in the receive layout of the matching dispatch
+  const uint32_t* dispatch_sync;  // epoch word of the dispatch whose layout is being reversed
+  const int32_t* dispatch_splits[2];
+  uint8_t* comb[2];         // symmetric [world * max_m, H] bf16
+  const float* topk_weight; // [T, topk] or null (plain sum)
+  void* out;                // [T, H] bf16
+};
+
+// cum[e] = pairs of experts < e; every CTA computes it for itself (E <= 1024)
+__device__ __forceinline__ void build_cum(const int32_t* counts, const int32_t* cum_in, int E, int* cum) {
+  if (cum_in) {
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) cum[e] = cum_in[e];
+  } else if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) { cum[e] = run; run += counts[e]; }
+    cum[E] = run;
+  }
+  __syncthreads();
+}
+
+// Last CTA to arrive releases flag[me] = epoch on every rank; then CTA 0 (or every CTA) waits for all sources.
+__device__ __forceinline__ bool signal_and_wait(const SymmCtx& ctx, uint32_t* flags_par, uint32_t* arrive_ctr, uint32_t epoch,
+                                                bool every_cta_waits) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    fence_acq_rel_sys();
+    if (atom_add_acqrel_gpu(arrive_ctr, 1u) == gridDim.x - 1) {
+      *arrive_ctr = 0;
+      fence_acq_rel_sys();
+      for (int d = 0; d < ctx.world; ++d) st_release_sys(symm_at(ctx, flags_par + ctx.rank, d), epoch);
+    }
+  }
+  bool ok = true;
+  if ((every_cta_waits || blockIdx.x == 0) && threadIdx.x < ctx.world)
+    ok = wait_flag<WaitCmp::EQ, true>(ctx, flags_par + threadIdx.x, epoch, threadIdx.x, __LINE__);
+  return __syncthreads_and(ok);
+}
+
+__device__ __forceinline__ void copy_row_warp(uint8_t* dst, const uint8_t* src, int bytes, int lane) {
+  for (int i = lane * 16; i < bytes; i += 32 * 16) st_v4(dst + i, *reinterpret_cast<const uint4*>(src + i));
+}
+
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kEpThreads) ep_row_a2a_kernel(const EpParams p, const SymmCtx ctx) {
+  __shared__ int cum[kEpMaxExperts + 1];
+  const uint32_t epoch = epoch_begin(p.sync);
+  const int par = epoch & 1;
+  build_cum(nullptr, p.cum_in, p.E, cum);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = kEpThreads / 32;
+  const int n = cum[p.E];
+  if (blockIdx.x == 0)
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
+      const int d = e / p.E_local;
+      *symm_at(ctx, p.recv_splits[par] + ctx.rank * p.E_local + (e - d * p.E_local), d) = cum[e + 1] - cum[e];
+    }
+  for (int r = blockIdx.x * warps + warp; r < n; r += gridDim.x * warps) {
+    int d = 0;
+    while (d + 1 < ctx.world && r >= cum[(d + 1) * p.E_local]) ++d;
+    const size_t slot = static_cast<size_t>(ctx.rank) * p.max_m + (r - cum[d * p.E_local]);
+    copy_row_warp(symm_at(ctx, p.recv[par] + slot * p.row_bytes, d), static_cast<const uint8_t*>(p.x) + static_cast<size_t>(r) * p.row_bytes,
+                  p.row_bytes, lane);
+    if (p.scale_floats && lane < p.scale_floats)
+      for (int j = lane; j < p.scale_floats; j += 32)
+        symm_at(ctx, p.recv_scale[par] + slot * p.scale_floats, d)[j] = p.x_scale[static_cast<size_t>(r) * p.scale_floats + j];
+  }
+  signal_and_wait(ctx, p.flags + par * kMaxRanks, p.sync + 2, epoch, false);
+  if (threadIdx.x == 0) epoch_end(p.sync, p.sync + 1, epoch, gridDim.x);
+}
+
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const EpParams p, const SymmCtx ctx) {
+  __shared__ int cum[kEpMaxExperts + 1];
+  const uint32_t epoch = epoch_begin(p.sync);
+  const int par = epoch & 1;
+  build_cum(p.counts, nullptr, p.E, cum);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = kEpThreads / 32;
+  if (blockIdx.x == 0)
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
+      const int d = e / p.E_local;
+      *symm_at(ctx, p.recv_splits[par] + ctx.rank * p.E_local + (e - d * p.E_local), d) = p.counts[e];
+    }
+  const uint8_t* x = static_cast<const uint8_t*>(p.x);
+  for (int t = blockIdx.x * warps + warp; t < p.T; t += gridDim.x * warps) {
+    // destination of each of the k copies (lane k holds copy k)
+    uint8_t* my_dst = nullptr;
+    float* my_sdst = nullptr;
+    if (lane < p.topk) {
+      const int e = p.topk_ids[t * p.topk + lane];
+      const int d = e / p.E_local;
+      const size_t slot = static_cast<size_t>(ctx.rank) * p.max_m + (p.pair_pos[t * p.topk + lane] - cum[d * p.E_local]);
+      my_dst = symm_at(ctx, p.recv[par] + slot * p.row_bytes, d);
+      if (p.scale_floats) my_sdst = symm_at(ctx, p.recv_scale[par] + slot * p.scale_floats, d);
+    }
+    const uint8_t* row = x + static_cast<size_t>(t) * p.H * 2;
+    if (!p.quant) {
+      for (int i = lane * 16; i < p.H * 2; i += 512) {
+        const uint4 v = *reinterpret_cast<const uint4*>(row + i);
+        for (int k = 0; k < p.topk; ++k) {
+          uint8_t* dst = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_dst), k));
+          st_v4(dst + i, v);
+        }
+      }
+    } else {
+      // each half-warp owns one 128-channel block per iteration: lane holds 8 channels
+      const int half = lane >> 4, hl = lane & 15;
+      for (int b0 = 0; b0 < p.H / 128; b0 += 2) {
+        const int blk = b0 + half;
+        const bool in = blk < p.H / 128;
+        float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (in) {
+          const uint4 v = *reinterpret_cast<const uint4*>(row + (static_cast<size_t>(blk) * 128 + hl * 8) * 2);
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 u = unpack_bf16x2(w[q]);
+            f[2 * q] = u.x;
+            f[2 * q + 1] = u.y;
+          }
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) amax = fmaxf(amax, fabsf(f[q]));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float scale = amax / 448.f;
+        const float den = scale > 0.f ? scale : 1.f;  // exact division, so that rounding ties fall as in x / scale
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t a = __nv_cvt_float_to_fp8(__fdiv_rn(f[q], den), __NV_SATFINITE, __NV_E4M3);
+          const uint32_t c = __nv_cvt_float_to_fp8(__fdiv_rn(f[4 + q], den), __NV_SATFINITE, __NV_E4M3);
+          lo |= a << (8 * q);
+          hi |= c << (8 * q);
+        }
+        for (int k = 0; k < p.topk; ++k) {
+          uint8_t* dst = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_dst), k));
+          float* sdst = reinterpret_cast<float*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_sdst), k));
+          if (in) {
+            *reinterpret_cast<uint2*>(dst + blk * 128 + hl * 8) = make_uint2(lo, hi);
+            if (hl == 0) sdst[blk] = scale;
+          }
+        }
+      }
+    }
+  }
+  signal_and_wait(ctx, p.flags + par * kMaxRanks, p.sync + 2, epoch, false);
+  if (threadIdx.x == 0) epoch_end(p.sync, p.sync + 1, epoch, gridDim.x);
+}
+
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const EpParams p, const SymmCtx ctx) {
+  __shared__ int cum[kEpMaxExperts + 1];
+  __shared__ int src_rows[kMaxRanks];
+  const uint32_t epoch = epoch_begin(p.sync);
+  const int par = epoch & 1;
+  const int dpar = ld_relaxed_gpu(p.dispatch_sync) & 1;  // layout of the last completed dispatch
+  build_cum(p.counts, nullptr, p.E, cum);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = kEpThreads / 32;
+  if (threadIdx.x < ctx.world) {
+    int n = 0;
+    for (int e = 0; e < p.E_local; ++e) n += p.dispatch_splits[dpar][threadIdx.x * p.E_local + e];
+    src_rows[threadIdx.x] = n;
+  }
+  __syncthreads();
+  // phase 1: return every received row's output to the rank it came from, same slot numbering
+  const uint8_t* eo = static_cast<const uint8_t*>(p.expert_out);
+  const int row_bytes = p.H * 2;
+  for (int s = 0; s < ctx.world; ++s) {
+    const int n = src_rows[s];
+    for (int i = blockIdx.x * warps + warp; i < n; i += gridDim.x * warps) {
+      const size_t from = (static_cast<size_t>(s) * p.max_m + i) * row_bytes;
+      const size_t to = (static_cast<size_t>(ctx.rank) * p.max_m + i) * row_bytes;
+      copy_row_warp(symm_at(ctx, p.comb[par] + to, s), eo + from, row_bytes, lane);
+    }
+  }
+  const bool ok = signal_and_wait(ctx, p.flags + par * kMaxRanks, p.sync + 2, epoch, true);
+  // phase 2: weighted sum of the k returned rows of every token
+  if (ok) {
+    for (int t = blockIdx.x * warps + warp; t < p.T; t += gridDim.x * warps) {
+      const uint8_t* my_src = nullptr;
+      float my_w = 1.f;
+      if (lane < p.topk) {
+        const int e = p.topk_ids[t * p.topk + lane];
+        const int d = e / p.E_local;
+        const size_t slot = static_cast<size_t>(d) * p.max_m + (p.pair_pos[t * p.topk + lane] - cum[d * p.E_local]);
+        my_src = p.comb[par] + slot * row_bytes;
+        if (p.topk_weight) my_w = p.topk_weight[t * p.topk + lane];
+      }
+      for (int i = lane * 16; i < row_bytes; i += 512) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int k = 0; k < p.topk; ++k) {
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_src), k));
+          const float wk = __shfl_sync(0xffffffffu, my_w, k);
+          const uint4 v = ld_v4_relaxed_sys(src + i);
+          const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 u = unpack_bf16x2(w4[q]);
+            acc[2 * q] += wk * u.x;
+            acc[2 * q + 1] += wk * u.y;
+          }
+        }
+        st_v4(static_cast<uint8_t*>(p.out) + static_cast<size_t>(t) * row_bytes + i,
+              make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7])));
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) epoch_end(p.sync, p.sync + 1, epoch, gridDim.x);
+}
+
+// Build grouped-GEMM metadata from recv_splits [world, E_local]: rows grouped by local expert, then source.
+// sorted_ids[i] = row index in the receive buffer (s * max_m + offset), pad = world * max_m. One CTA.
+__global__ void __launch_bounds__(1024) ep_recv_plan_kernel(const int32_t* splits, int world, int E_local, int max_m, int block_m,
+                                                            int32_t* sorted_ids, int32_t* tile_expert, int32_t* totals,
+                                                            int32_t* rows_per_expert, int cap_rows) {
+  __shared__ int estart[kEpMaxExperts + 1];         // padded start row of every local expert
+  __shared__ int src_off[kMaxRanks][kEpMaxExperts]; // offset of (s, e) inside source s's area
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < E_local; ++e) {
+      estart[e] = run;
+      int c = 0;
+      for (int s = 0; s < world; ++s) c += splits[s * E_local + e];
+      rows_per_expert[e] = c;
+      run += (c + block_m - 1) / block_m * block_m;
+    }
+    estart[E_local] = run;
+    totals[0] = run;
+    totals[1] = run / block_m;
+    for (int s = 0; s < world; ++s) {
+      int o = 0;
+      for (int e = 0; e < E_local; ++e) { src_off[s][e] = o; o += splits[s * E_local + e]; }
+    }
+  }
+  __syncthreads();
+  const int pad = world * max_m;
+  for (int i = threadIdx.x; i < min(estart[E_local], cap_rows); i += blockDim.x) sorted_ids[i] = pad;
+  __syncthreads();
+  for (int e = 0; e < E_local; ++e) {
+    int dst = estart[e];
+    for (int s = 0; s < world; ++s) {
+      const int n = splits[s * E_local + e];
+      for (int i = threadIdx.x; i < n; i += blockDim.x)
+        if (dst + i < cap_rows) sorted_ids[dst + i] = s * max_m + src_off[s][e] + i;
+      dst += n;
+    }
+    for (int t = estart[e] / block_m + threadIdx.x; t < estart[e + 1] / block_m; t += blockDim.x) tile_expert[t] = e;
+  }
+}
+
+static int ep_grid(int rows) {
+  int g = (rows + 7) / 8;
+  const int cap = sm_count();
+  return g < 1 ? 1 : (g > cap ? cap : g);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+#define EP_CTX()      \
+  SymmCtx ctx;        \
+  memcpy(&ctx, symm_ctx, sizeof(ctx))
+
+// rows [n, row_bytes] sorted by global expert; cum int32 [E + 1]; scales fp32 [n, scale_floats] or null.
+B200_API int b200_ep_row_a2a(const void* symm_ctx, const void* rows, int row_bytes, const int32_t* cum, int n_upper, int E,
+                             int E_local, int max_m, const float* scales, int scale_floats, void* recv0, void* recv1,
+                             void* recv_scale0, void* recv_scale1, int32_t* splits0, int32_t* splits1, uint32_t* flags,
+                             uint32_t* sync, void* stream) {
+  EP_CTX();
+  B200_REQUIRE(row_bytes % 16 == 0, "row bytes (%d) must be a multiple of 16", row_bytes);
+  B200_REQUIRE(E <= kEpMaxExperts && E == E_local * ctx.world, "experts (%d) must equal E_local * world and be <= %d", E, kEpMaxExperts);
+  EpParams p;
+  memset(&p, 0, sizeof(p));
+  p.E = E; p.E_local = E_local; p.max_m = max_m; p.row_bytes = row_bytes; p.scale_floats = scales ? scale_floats : 0;
+  p.x = rows; p.x_scale = scales; p.cum_in = cum;
+  p.recv[0] = static_cast<uint8_t*>(recv0); p.recv[1] = static_cast<uint8_t*>(recv1);
+  p.recv_scale[0] = static_cast<float*>(recv_scale0); p.recv_scale[1] = static_cast<float*>(recv_scale1);
+  p.recv_splits[0] = splits0; p.recv_splits[1] = splits1; p.flags = flags; p.sync = sync;
+  ep_row_a2a_kernel<<<ep_grid(n_upper), kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(p, ctx);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+// x bf16 [T, H]; topk_ids int32 [T, topk]; pair_pos / counts from an unpadded (block 1) expert sort of the pairs.
+// quant != 0: rows travel as e4m3 [H] with H / 128 fp32 scales; else as bf16.
+B200_API int b200_ep_dispatch(const void* symm_ctx, const void* x, int T, int H, int topk, const int32_t* topk_ids,
+                              const int32_t* pair_pos, const int32_t* counts, int E, int E_local, int max_m, int quant,
+                              void* recv0, void* recv1, void* recv_scale0, void* recv_scale1, int32_t* splits0,
+                              int32_t* splits1, uint32_t* flags, uint32_t* sync, void* stream) {
+  EP_CTX();
+  B200_REQUIRE(H % 128 == 0, "hidden (%d) must be a multiple of 128", H);
+  B200_REQUIRE(topk >= 1 && topk <= 32, "top-k (%d) must be in [1, 32]", topk);
+  B200_REQUIRE(E <= kEpMaxExperts && E == E_local * ctx.world, "experts (%d) must equal E_local * world and be <= %d", E, kEpMaxExperts);
+  EpParams p;
+  memset(&p, 0, sizeof(p));
+  p.T = T; p.H = H; p.topk = topk; p.E = E; p.E_local = E_local; p.max_m = max_m; p.quant = quant;
+  p.row_bytes = quant ? H : 2 * H; p.scale_floats = quant ? H / 128 : 0;
+  p.x = x; p.topk_ids = topk_ids; p.pair_pos = pair_pos; p.counts = counts;
+  p.recv[0] = static_cast<uint8_t*>(recv0); p.recv[1] = static_cast<uint8_t*>(recv1);
+  p.recv_scale[0] = static_cast<float*>(recv_scale0); p.recv_scale[1] = static_cast<float*>(recv_scale1);
+  p.recv_splits[0] = splits0; p.recv_splits[1] = splits1; p.flags = flags; p.sync = sync;
+  ep_dispatch_kernel<<<ep_grid(T), kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(p, ctx);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+// expert_out bf16 [world * max_m, H] in the receive layout of the last dispatch; out bf16 [T, H].
+B200_API int b200_ep_combine(const void* symm_ctx, const void* expert_out, int T, int H, int topk, const int32_t* topk_ids,
+                             const int32_t* pair_pos, const int32_t* counts, const float* topk_weight, int E, int E_local,
+                             int max_m, const uint32_t* dispatch_sync, const int32_t* dsplits0, const int32_t* dsplits1,
+                             void* comb0, void* comb1, uint32_t* flags, uint32_t* sync, void* out, void* stream) {
+  EP_CTX();
+  B200_REQUIRE(H % 8 == 0 && topk >= 1 && topk <= 32, "bad hidden / top-k");
+  EpParams p;
+  memset(&p, 0, sizeof(p));
+  p.T = T; p.H = H; p.topk = topk; p.E = E; p.E_local = E_local; p.max_m = max_m;
+  p.topk_ids = topk_ids; p.pair_pos = pair_pos; p.counts = counts; p.topk_weight = topk_weight;
+  p.expert_out = expert_out; p.dispatch_sync = dispatch_sync; p.dispatch_splits[0] = dsplits0; p.dispatch_splits[1] = dsplits1;
+  p.comb[0] = static_cast<uint8_t*>(comb0); p.comb[1] = static_cast<uint8_t*>(comb1); p.flags = flags; p.sync = sync; p.out = out;
+  int grid = ep_grid(T > max_m ? T : max_m);
+  ep_combine_kernel<<<grid, kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(p, ctx);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+B200_API int b200_ep_recv_plan(const int32_t* splits, int world, int E_local, int max_m, int block_m, int32_t* sorted_ids,
+                               int32_t* tile_expert, int32_t* totals, int32_t* rows_per_expert, int cap_rows, void* stream) {
+  B200_REQUIRE(E_local <= kEpMaxExperts && world <= kMaxRanks, "too many local experts / ranks");
+  ep_recv_plan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(splits, world, E_local, max_m, block_m, sorted_ids,
+                                                                        tile_expert, totals, rows_per_expert, cap_rows);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}

@@ -31,6 +31,7 @@ struct MoeSortParams {
   int32_t* tile_expert;    // [tile cap]
   int32_t* tile_seg_start; // [tile cap]
   int32_t* tile_seg_end;   // [tile cap]
+  int32_t* pair_pos;       // nullable [n_pairs]: sorted position of every pair (inverse of sorted_ids)
   int32_t* group_count;    // [segments * experts] matches per group (unpadded)
   int32_t* totals;         // [2 + segments]: m_pad, num_tiles, tiles per segment
   uint64_t* lookback;      // [segments * experts]: (epoch << 32) | padded count
@@ -101,6 +102,7 @@ __global__ void __launch_bounds__(kSortWarps * 32) moe_sort_kernel(const MoeSort
         if (hit) {
           const int pos = written + __popc(m & ((1u << lane) - 1u));
           p.sorted_ids[offset + pos] = i;
+          if (p.pair_pos) p.pair_pos[i] = static_cast<int32_t>(offset + pos);
           // segment bounds of the tile this row falls into (only needed when sorting over all tokens)
           if (p.segments == 1) {
             const int src = (i / p.topk) / p.tokens_per_rank;
@@ -190,11 +192,11 @@ B200_API long long b200_moe_sorted_capacity(int n_pairs, int num_experts, int bl
 
 // ids int32 [n_pairs]; outputs sized by b200_moe_sorted_capacity (rows) and capacity / block_m (tiles).
 // group_count int32 [segments * E]; totals int32 [2 + segments]; lookback u64 [segments * E] and sync u32 [2] are
-// zero-initialised once and owned by the caller (one pair per concurrent user).
+// zero-initialised once and owned by the caller (one pair per concurrent user). pair_pos (nullable) int32 [n_pairs].
 B200_API int b200_moe_sort(const int32_t* ids, int n_pairs, int topk, int num_experts, int block_m, int segments,
                            int tokens_per_rank, int32_t* sorted_ids, int32_t* tile_expert, int32_t* tile_seg_start,
                            int32_t* tile_seg_end, int32_t* group_count, int32_t* totals, uint64_t* lookback,
-                           uint32_t* sync, uint32_t* status, void* stream) {
+                           uint32_t* sync, uint32_t* status, int32_t* pair_pos, void* stream) {
   B200_REQUIRE(num_experts >= 1 && num_experts <= 1024, "number of experts (%d) must be in [1, 1024]", num_experts);
   B200_REQUIRE(segments >= 1 && n_pairs % segments == 0, "pairs (%d) must divide into %d segments", n_pairs, segments);
   B200_REQUIRE(block_m >= 1 && topk >= 1 && tokens_per_rank >= 1, "bad block_m / topk / tokens_per_rank");
@@ -209,6 +211,7 @@ B200_API int b200_moe_sort(const int32_t* ids, int n_pairs, int topk, int num_ex
   p.ids = ids; p.n_pairs = n_pairs; p.topk = topk; p.num_experts = num_experts; p.block_m = block_m;
   p.segments = segments; p.pairs_per_segment = n_pairs / segments; p.tokens_per_rank = tokens_per_rank;
   p.sorted_ids = sorted_ids; p.tile_expert = tile_expert; p.tile_seg_start = tile_seg_start; p.tile_seg_end = tile_seg_end;
+  p.pair_pos = pair_pos;
   p.group_count = group_count; p.totals = totals; p.lookback = lookback; p.sync = sync;
   p.timeout_ns = 2000000000ull; p.status = status;
   moe_sort_kernel<<<ctas, kSortWarps * 32, 0, s>>>(p);

@@ -13,3 +13,4 @@ from .allgather_group_gemm import ag_group_gemm, create_ag_group_gemm_context, g
 from .moe_reduce_rs import (create_moe_rs_context, create_moe_rs_context_colwise, moe_reduce_rs, moe_reduce_rs_colwise,
                             moe_reduce_rs_rowise, select_experts)
 from .moe_utils import calc_gather_scatter_index, create_sort_plan, moe_sort, order_tiles, reduce_topk
+from .low_latency_all_to_all import all_to_all_post_process, create_all_to_all_context, fast_all_to_all

@@ -36,6 +36,7 @@ class MoeSortPlan:
     lookback: torch.Tensor
     sync: torch.Tensor
     status: torch.Tensor
+    pair_pos: torch.Tensor | None = None  # int32 [n_pairs]: sorted position of every pair (when requested)
 
     @property
     def max_tiles(self) -> int:
@@ -43,7 +44,7 @@ class MoeSortPlan:
 
 
 def create_sort_plan(n_pairs: int, topk: int, num_experts: int, block_m: int = 128, segments: int = 1,
-                     device="cuda") -> MoeSortPlan:
+                     device="cuda", with_positions: bool = False) -> MoeSortPlan:
     lib = _lib.load()
     lib.b200_moe_sorted_capacity.restype = ctypes.c_longlong
     cap = int(lib.b200_moe_sorted_capacity(n_pairs, num_experts, block_m, segments))
@@ -53,7 +54,8 @@ def create_sort_plan(n_pairs: int, topk: int, num_experts: int, block_m: int = 1
                        torch.empty(cap, **i32), torch.empty(tiles, **i32), torch.empty(tiles, **i32),
                        torch.empty(tiles, **i32), torch.empty(tiles, **i32), torch.zeros(segments * num_experts, **i32),
                        torch.zeros(2 + segments, **i32), torch.zeros(segments * num_experts, dtype=torch.int64, device=device),
-                       torch.zeros(4, **i32), torch.zeros(16, **i32))
+                       torch.zeros(4, **i32), torch.zeros(16, **i32),
+                       torch.empty(n_pairs, **i32) if with_positions else None)
 
 
 def moe_sort(topk_ids: torch.Tensor, plan: MoeSortPlan, tokens_per_rank: int | None = None) -> MoeSortPlan:
@@ -66,7 +68,7 @@ def moe_sort(topk_ids: torch.Tensor, plan: MoeSortPlan, tokens_per_rank: int | N
         tokens_per_rank = max(1, plan.n_pairs // plan.topk)
     _lib.call("b200_moe_sort", ptr(ids), plan.n_pairs, plan.topk, plan.num_experts, plan.block_m, plan.segments,
               tokens_per_rank, ptr(plan.sorted_ids), ptr(plan.tile_expert), ptr(plan.tile_seg_start), ptr(plan.tile_seg_end),
-              ptr(plan.group_count), ptr(plan.totals), ptr(plan.lookback), ptr(plan.sync), ptr(plan.status), stream_ptr())
+              ptr(plan.group_count), ptr(plan.totals), ptr(plan.lookback), ptr(plan.sync), ptr(plan.status), ptr(plan.pair_pos), stream_ptr())
     ops._count(2 if plan.segments == 1 else 1)
     return plan
 
