@@ -340,6 +340,49 @@ def ep_all_to_all_dispatch_combine():
             layer.finalize()
 
 
+@case
+def sp_flash_decode_and_allgather_layer():
+    import math
+    from triton_distributed_b200 import ref
+    from triton_distributed_b200.layers.nvidia import AllGatherLayer, SpGQAFlashDecodeAttention
+    rank, world = _rank_world()
+    group = U.TP_GROUP()
+    heap = get_heap()
+    Hq, Hkv, D, page = 64, 8, 128, 16
+    for use_mc in ([False, True] if heap.has_multicast else [False]):
+        layer = SpGQAFlashDecodeAttention(rank, 0, world, 1, Hq, Hkv, D, D, page_size=page, scale=1 / math.sqrt(D),
+                                          max_allowed_batch=8, use_multicast=use_mc)
+        for B, per_rank_len in ((1, 512), (8, 1000), (3, 37)):
+            torch.manual_seed(9)  # same q on every rank
+            q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+            torch.manual_seed(100 + rank)
+            nb = (per_rank_len + page - 1) // page
+            kc = torch.randn(B * nb, page, Hkv, D, device="cuda", dtype=torch.bfloat16)
+            vc = torch.randn_like(kc)
+            bt = torch.randperm(B * nb, device="cuda").to(torch.int32).view(B, nb)
+            lens = torch.randint(1, per_rank_len + 1, (B,), device="cuda", dtype=torch.int32)
+            if rank == world - 1:
+                lens[0] = 0  # a rank without tokens for sequence 0 must drop out of the merge
+            all_lens = torch.empty(world, B, device="cuda", dtype=torch.int32)
+            dist.all_gather_into_tensor(all_lens, lens, group=group)
+            for it in range(2):
+                out = layer(q, kc, vc, all_lens, bt)
+                torch.cuda.synchronize()
+                want = ref.sp_flash_decode_ref(q, kc, vc, lens, bt, 1 / math.sqrt(D), 0.0, group)
+                torch.testing.assert_close(out.float(), want, rtol=5e-2, atol=2e-2, msg=lambda s_: f"sp decode B={B} mc={use_mc} it={it}: {s_}")
+        layer.finalize()
+    ag = AllGatherLayer(1, world, rank, max_buffer_size=1 << 20)
+    for fn in (ag.forward_pull, ag.forward_push_2d, ag.forward_push_2d_ll, ag.forward_push_2d_ll_multimem, ag.forward_push_numa_2d_ll):
+        for n in (17 * 4, 4096):
+            local = torch.arange(n, device="cuda", dtype=torch.float32) + 10000 * rank
+            heap.barrier_all()
+            got = fn(local).clone()
+            torch.cuda.synchronize()
+            want = ref.fast_allgather_ref(local, group)
+            assert torch.equal(got, want), f"AllGatherLayer {fn.__name__}"
+    ag.finalize()
+
+
 def main() -> int:
     U.initialize_distributed(seed=0, heap_bytes=int(os.environ.get("B200DIST_TEST_HEAP", 3 << 30)))
     rank, world = _rank_world()

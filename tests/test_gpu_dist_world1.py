@@ -151,3 +151,26 @@ def test_fast_allgather_world1(dist1, mode):
     assert torch.equal(buf, torch.arange(4096, device="cuda", dtype=torch.float32))
     heap.free(buf)
     ctx.finalize()
+
+
+def test_sp_flash_decode_world1(dist1):
+    import math
+    from triton_distributed_b200 import ref
+    from triton_distributed_b200.layers.nvidia import SpGQAFlashDecodeAttention
+    from triton_distributed_b200.runtime.heap import get_heap
+    torch.manual_seed(0)
+    B, Hq, Hkv, D, page, L = 4, 32, 4, 128, 16, 700
+    layer = SpGQAFlashDecodeAttention(0, 0, 1, 1, Hq, Hkv, D, D, page_size=page, scale=1 / math.sqrt(D), max_allowed_batch=4)
+    nb = (L + page - 1) // page
+    kc = torch.randn(B * nb, page, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn_like(kc)
+    bt = torch.randperm(B * nb, device="cuda").to(torch.int32).view(B, nb)
+    lens = torch.randint(1, L + 1, (1, B), device="cuda", dtype=torch.int32)
+    q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
+    for splits in (-1, 1, 5):
+        out = layer(q, kc, vc, lens, bt, kv_split=splits)
+        torch.cuda.synchronize()
+        get_heap().check_status("sp decode")
+        want, _ = ref.paged_decode_attention_ref(q, kc, vc, lens[0], bt, 1 / math.sqrt(D))
+        torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
+    layer.finalize()

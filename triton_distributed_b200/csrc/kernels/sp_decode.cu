@@ -1,0 +1,145 @@
+// Sequence-parallel decode: merge of the split-KV partials of this rank, exchange of the per-rank (O, LSE)
+// partials with the low-latency packet protocol, and the cross-rank LSE combine, in ONE kernel.
+//
+// Each rank has attended to its own shard of the KV cache (decode_attn.cu). CTA (b, h) then
+//   1. merges this rank's split partials of head (b, h) in registers,
+//   2. sends the 128 output words and the LSE as {value, epoch} packets to every peer (plain P2P stores, or a
+//      single multimem.st per packet when the heap is bound to an NVLS multicast object),
+//   3. polls the packets of the other ranks for the same head (the data is its own arrival flag, so there is no
+//      barrier and no separate signal), and
+//   4. writes softmax-consistent output sum_r exp(lse_r - max) O_r / sum_r exp(lse_r - max); ranks whose shard was
+//      empty carry lse = -inf and drop out.
+// Packet areas are double-buffered by epoch parity; the epoch lives in device memory (CUDA-graph replayable).
+//
+// Role in the reference: SpGQAFlashDecodeAttention.forward = intra-rank combine kernel + staged copy into a
+// symmetric buffer + LL all-gather kernel + inter-rank combine kernel
+// (python/triton_dist/layers/nvidia/sp_flash_decode_layer.py:83-185, kernels/nvidia/flash_decode.py:393-532,
+// low_latency_allgather.py:530-566, 762-777).
+#include "b200/host.h"
+#include "b200/primitives.cuh"
+
+#include <cstring>
+
+namespace b200 {
+
+constexpr int kSpD = 128;
+
+struct SpParams {
+  const float* o_part;    // [BH, S, 128] split partials of this rank (normalised per split)
+  const float* lse_part;  // [BH, S]
+  int S, BH;
+  uint64_t* ll[2];        // symmetric packet areas [world][BH][129] per parity
+  uint32_t* sync;         // local u32[2]
+  void* out;              // [BH, 128] bf16 / f16
+  float* out_lse;         // [BH] or null
+  int bf16, use_mc;
+};
+
+__global__ void __launch_bounds__(kSpD) sp_decode_combine_kernel(const SpParams p, const SymmCtx ctx) {
+  __shared__ float lse_of[kMaxRanks];
+  const uint32_t epoch = epoch_begin(p.sync);
+  uint64_t* ll = p.ll[epoch & 1];
+  const int bh = blockIdx.x, d = threadIdx.x;
+  const int me = ctx.rank, world = ctx.world;
+  // 1. local merge over splits
+  float mg = -INFINITY;
+  for (int s = 0; s < p.S; ++s) mg = fmaxf(mg, p.lse_part[static_cast<size_t>(bh) * p.S + s]);
+  float lg = 0.f, og = 0.f;
+  for (int s = 0; s < p.S; ++s) {
+    const float l = p.lse_part[static_cast<size_t>(bh) * p.S + s];
+    if (l == -INFINITY) continue;
+    const float w = __expf(l - mg);
+    lg += w;
+    og += w * p.o_part[(static_cast<size_t>(bh) * p.S + s) * kSpD + d];
+  }
+  const float o_mine = lg > 0.f ? og / lg : 0.f;
+  const float lse_mine = lg > 0.f ? mg + logf(lg) : -INFINITY;
+  // 2. send packets: word d, and the LSE as word 128 (thread 0)
+  const size_t base = (static_cast<size_t>(me) * p.BH + bh) * (kSpD + 1);
+  if (world > 1) {
+    if (p.use_mc) {
+      const uint64_t v = (static_cast<uint64_t>(epoch) << 32) | __float_as_uint(o_mine);
+      asm volatile("multimem.st.relaxed.sys.global.u64 [%0], %1;" ::"l"(mc_ptr(ctx, ll + base + d)), "l"(v) : "memory");
+      if (d == 0) {
+        const uint64_t w = (static_cast<uint64_t>(epoch) << 32) | __float_as_uint(lse_mine);
+        asm volatile("multimem.st.relaxed.sys.global.u64 [%0], %1;" ::"l"(mc_ptr(ctx, ll + base + kSpD)), "l"(w) : "memory");
+      }
+    } else {
+      for (int k = 1; k < world; ++k) {
+        const int peer = (me + k) % world;
+        ll_store(symm_at(ctx, ll + base + d, peer), __float_as_uint(o_mine), epoch);
+        if (d == 0) ll_store(symm_at(ctx, ll + base + kSpD, peer), __float_as_uint(lse_mine), epoch);
+      }
+    }
+  }
+  // 3. receive the other ranks' partials of this head
+  float o_r[kMaxRanks];
+  bool ok = true;
+  if (d < world) {
+    if (d == me) {
+      lse_of[d] = lse_mine;
+    } else {
+      uint32_t w = 0;
+      ok = ll_load(ctx, ll + (static_cast<size_t>(d) * p.BH + bh) * (kSpD + 1) + kSpD, epoch, &w);
+      lse_of[d] = ok ? __uint_as_float(w) : -INFINITY;
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kMaxRanks; ++r) {
+    o_r[r] = 0.f;
+    if (r < world) {
+      if (r == me) {
+        o_r[r] = o_mine;
+      } else {
+        uint32_t w = 0;
+        ok = ll_load(ctx, ll + (static_cast<size_t>(r) * p.BH + bh) * (kSpD + 1) + d, epoch, &w) && ok;
+        o_r[r] = __uint_as_float(w);
+      }
+    }
+  }
+  ok = __syncthreads_and(ok);
+  // 4. combine
+  if (ok) {
+    float m = -INFINITY;
+    for (int r = 0; r < world; ++r) m = fmaxf(m, lse_of[r]);
+    float den = 0.f, num = 0.f;
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r) {
+      if (r < world && lse_of[r] != -INFINITY) {
+        const float w = __expf(lse_of[r] - m);
+        den += w;
+        num += w * o_r[r];
+      }
+    }
+    const float o = den > 0.f ? num / den : 0.f;
+    if (p.bf16) static_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(bh) * kSpD + d] = __float2bfloat16(o);
+    else static_cast<__half*>(p.out)[static_cast<size_t>(bh) * kSpD + d] = __float2half(o);
+    if (d == 0 && p.out_lse) p.out_lse[bh] = den > 0.f ? m + logf(den) : -INFINITY;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) epoch_end(p.sync, p.sync + 1, epoch, gridDim.x);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// o_part fp32 [BH, S, 128], lse_part fp32 [BH, S]: this rank's split partials. ll0 / ll1: symmetric u64 areas of
+// world * BH_cap * 129 packets (the kernel indexes them with this call's BH, which every rank must share).
+B200_API int b200_sp_decode_combine(const void* symm_ctx, const float* o_part, const float* lse_part, int BH, int S,
+                                    void* ll0, void* ll1, uint32_t* sync, void* out, float* out_lse, int dtype, int use_mc,
+                                    void* stream) {
+  SymmCtx ctx;
+  memcpy(&ctx, symm_ctx, sizeof(ctx));
+  B200_REQUIRE(dtype == kBF16 || dtype == kF16, "sp decode combine writes bf16/f16");
+  B200_REQUIRE(!use_mc || ctx.mc_base != 0, "multimem packets need an NVLS multicast mapping");
+  if (BH == 0) return kOk;
+  SpParams p;
+  memset(&p, 0, sizeof(p));
+  p.o_part = o_part; p.lse_part = lse_part; p.S = S; p.BH = BH;
+  p.ll[0] = static_cast<uint64_t*>(ll0); p.ll[1] = static_cast<uint64_t*>(ll1);
+  p.sync = sync; p.out = out; p.out_lse = out_lse; p.bf16 = dtype == kBF16; p.use_mc = use_mc;
+  sp_decode_combine_kernel<<<BH, kSpD, 0, static_cast<cudaStream_t>(stream)>>>(p, ctx);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
