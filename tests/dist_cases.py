@@ -383,6 +383,55 @@ def sp_flash_decode_and_allgather_layer():
     ag.finalize()
 
 
+@case
+def reduce_scatter_op_and_moe_layers():
+    from triton_distributed_b200.kernels.nvidia import create_reduce_scater_2d_ctx, reduce_scatter_2d_op
+    from triton_distributed_b200.layers.nvidia import EP_MoE, TP_MoE
+    rank, world = _rank_world()
+    group = U.TP_GROUP()
+    ctx = create_reduce_scater_2d_ctx(64 * world, 512, rank, world, world, torch.bfloat16)
+    for it in range(3):
+        torch.manual_seed(rank + it)
+        x = torch.randn(64 * world, 512, device="cuda", dtype=torch.bfloat16)
+        want = torch.empty(64, 512, device="cuda", dtype=torch.float32)
+        dist.reduce_scatter_tensor(want, x.float(), group=group)
+        got = reduce_scatter_2d_op(x, ctx)
+        torch.cuda.synchronize()
+        torch.testing.assert_close(got.float(), want, rtol=3e-2, atol=3e-2 * world)
+    ctx.finalize()
+    # TP-MoE layer: sequence-sharded fused path vs the torch forward on replicated activations
+    E, topk, H, I, T = 16, 4, 512, 256 * world, 64 * world
+    torch.manual_seed(3)
+    gate = torch.randn(E, H, device="cuda", dtype=torch.bfloat16)
+    wgu = torch.randn(E, 2 * I, H, device="cuda", dtype=torch.bfloat16) * 0.05
+    wdn = torch.randn(E, H, I, device="cuda", dtype=torch.bfloat16) * 0.05
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    il = I // world
+    sl = slice(rank * il, (rank + 1) * il)
+    tp = TP_MoE(rank, world, group, topk, True)
+    tp._init_parameters(gate, torch.cat([wgu[:, :I][:, sl], wgu[:, I:][:, sl]], dim=1), wdn[:, :, sl])
+    tp._init_ctx(T)
+    want = tp.torch_fwd(x)
+    per = T // world
+    for it in range(2):
+        got = tp.dist_triton_fwd(x[rank * per:(rank + 1) * per].contiguous())
+        torch.cuda.synchronize()
+        torch.testing.assert_close(got.float(), want[rank * per:(rank + 1) * per].float(), rtol=5e-2, atol=0.15)
+    tp.finalize()
+    # EP-MoE layer: every rank owns E / world whole experts
+    for fp8 in (False, True):
+        ep = EP_MoE(rank, world, group, E, topk, H, per, torch.bfloat16, True, fp8_dispatch=fp8)
+        el = E // world
+        ep._init_parameters(gate, wgu[rank * el:(rank + 1) * el].contiguous(), wdn[rank * el:(rank + 1) * el].contiguous())
+        xl = x[rank * per:(rank + 1) * per].contiguous()
+        want_l = ep.torch_fwd(xl, wgu, wdn)
+        for it in range(2):
+            got = ep.dist_triton_fwd(xl)
+            torch.cuda.synchronize()
+            torch.testing.assert_close(got.float(), want_l.float(), rtol=0.12 if fp8 else 5e-2, atol=0.3 if fp8 else 0.15)
+        ep.finalize()
+
+
 def main() -> int:
     U.initialize_distributed(seed=0, heap_bytes=int(os.environ.get("B200DIST_TEST_HEAP", 3 << 30)))
     rank, world = _rank_world()

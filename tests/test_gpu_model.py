@@ -72,3 +72,25 @@ def test_safetensors_roundtrip_matches_random_source(dist1, tmp_path):
         kv = KV_Cache(arch.num_hidden_layers, 1, 128, arch.num_key_value_heads, arch.head_dim, torch.bfloat16, 1)
         outs.append(m.inference(ids, pos, kv))
     assert torch.equal(outs[0], outs[1])
+
+
+def test_moe_model_native_modes_match_torch(dist1):
+    from triton_distributed_b200.models import AutoLLM, KV_Cache, ModelConfig
+    cfg = ModelConfig(model_name="tiny-qwen3-moe", max_length=128, rank=0, world_size=1)
+    model = AutoLLM.from_pretrained(cfg, dist1)
+    a = model.arch
+    ids = torch.randint(0, a.vocab_size, (2, 24), device="cuda")
+    pos = torch.arange(24, device="cuda")[None, :].expand(2, 24).contiguous()
+    outs = {}
+    for mode in ("torch", "triton_dist_AR", "triton_dist"):
+        kv = KV_Cache(a.num_hidden_layers, 2, 128, a.num_key_value_heads, a.head_dim, torch.bfloat16, 1)
+        if mode == "triton_dist":
+            model.init_triton_dist_ctx(2 * 24)
+        if mode == "triton_dist_AR":
+            model.init_triton_dist_AR_ctx(2 * 24)
+        model.set_fwd(mode)
+        outs[mode] = torch.softmax(model.inference(ids, pos, kv), -1)
+        torch.cuda.synchronize()
+    for mode in ("triton_dist_AR", "triton_dist"):
+        torch.testing.assert_close(outs[mode], outs["torch"], rtol=3e-2, atol=3e-2)
+    model.finalize()

@@ -260,3 +260,78 @@ B200_API int b200_test_multimem(const void* symm_ctx, void* buf, uint32_t n4, vo
   B200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Stand-alone reduce-scatter: out[M / world, N] = rows of this rank of sum_r in_r[M, N].
+// CTA b of every rank pushes its share of each owner's rows into the owner's slot [src][row], meets CTA b of
+// the peers, then sums the slots of its own rows in fp32 (fixed order, so results are reproducible).
+// (python/triton_dist/kernels/nvidia/reduce_scatter.py:597-882: scatter by copy engine + ring_reduce kernel.)
+// ---------------------------------------------------------------------------------------------
+namespace b200 {
+struct RsParams {
+  const uint4* in;     // [world * per_rank_vecs]
+  uint4* out;          // [per_rank_vecs]
+  uint4* ws[2];        // symmetric [world][per_rank_vecs]
+  uint64_t per_rank_vecs;
+  uint32_t* flags;     // symmetric u32[2][kAgMaxCtas][kMaxRanks]
+  uint32_t* sync;
+  int bf16;            // 1 bf16, 0 f16, 2 f32
+};
+__device__ __forceinline__ void rs_acc(float* acc, uint4 v, int kind) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  if (kind == 2) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) acc[q] += __uint_as_float(w[q]);
+  } else {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 f = kind == 1 ? unpack_bf16x2(w[q]) : unpack_f16x2(w[q]);
+      acc[2 * q] += f.x;
+      acc[2 * q + 1] += f.y;
+    }
+  }
+}
+__global__ void __launch_bounds__(kAgThreads) reduce_scatter_kernel(const RsParams p, const SymmCtx ctx) {
+  const uint32_t epoch = epoch_begin(p.sync);
+  uint4* ws = p.ws[epoch & 1];
+  const uint64_t tid = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x, nthreads = (uint64_t)gridDim.x * blockDim.x;
+  for (int k = 0; k < ctx.world; ++k) {
+    const int owner = (ctx.rank + 1 + k) % ctx.world;
+    for (uint64_t i = tid; i < p.per_rank_vecs; i += nthreads)
+      st_v4(symm_at(ctx, ws + ctx.rank * p.per_rank_vecs + i, owner), p.in[owner * p.per_rank_vecs + i]);
+  }
+  if (ag_cta_barrier(ctx, p.flags, 0, epoch)) {
+    for (uint64_t i = tid; i < p.per_rank_vecs; i += nthreads) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int s = 0; s < ctx.world; ++s) rs_acc(acc, ld_v4_relaxed_sys(ws + s * p.per_rank_vecs + i), p.bf16);
+      uint4 o;
+      if (p.bf16 == 2) o = make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]));
+      else if (p.bf16 == 1) o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+      else o = make_uint4(pack_f16x2(acc[0], acc[1]), pack_f16x2(acc[2], acc[3]), pack_f16x2(acc[4], acc[5]), pack_f16x2(acc[6], acc[7]));
+      p.out[i] = o;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) epoch_end(p.sync, p.sync + 1, epoch, gridDim.x);
+}
+}  // namespace b200
+
+// in: [world * bytes_per_rank] (rows of owner r at r * bytes_per_rank); out: [bytes_per_rank]; ws0 / ws1: symmetric
+// [world * bytes_per_rank]; dtype 0 bf16, 1 f16, 2 f32.
+B200_API int b200_reduce_scatter(const void* symm_ctx, const void* in, void* out, uint64_t bytes_per_rank, int dtype, void* ws0,
+                                 void* ws1, uint32_t* flags, uint32_t* sync, int num_ctas, void* stream) {
+  LOAD_CTX(ctx);
+  B200_REQUIRE(bytes_per_rank % 16 == 0, "bytes per rank (%llu) must be a multiple of 16", (unsigned long long)bytes_per_rank);
+  B200_REQUIRE(dtype == kBF16 || dtype == kF16 || dtype == kF32, "reduce_scatter supports bf16/f16/f32");
+  RsParams p;
+  memset(&p, 0, sizeof(p));
+  p.in = static_cast<const uint4*>(in); p.out = static_cast<uint4*>(out);
+  p.ws[0] = static_cast<uint4*>(ws0); p.ws[1] = static_cast<uint4*>(ws1);
+  p.per_rank_vecs = bytes_per_rank / 16; p.flags = flags; p.sync = sync;
+  p.bf16 = dtype == kBF16 ? 1 : (dtype == kF16 ? 0 : 2);
+  int grid = num_ctas > 0 ? num_ctas : 8;
+  if (grid > kAgMaxCtas) grid = kAgMaxCtas;
+  reduce_scatter_kernel<<<grid, kAgThreads, 0, static_cast<cudaStream_t>(stream)>>>(p, ctx);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}

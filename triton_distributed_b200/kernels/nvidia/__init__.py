@@ -14,3 +14,6 @@ from .moe_reduce_rs import (create_moe_rs_context, create_moe_rs_context_colwise
                             moe_reduce_rs_rowise, select_experts)
 from .moe_utils import calc_gather_scatter_index, create_sort_plan, moe_sort, order_tiles, reduce_topk
 from .low_latency_all_to_all import all_to_all_post_process, create_all_to_all_context, fast_all_to_all
+from .allgather import (AllGatherMethod, cp_engine_producer_all_gather_inter_node, cp_engine_producer_all_gather_intra_node,
+                        get_auto_all_gather_method)
+from .reduce_scatter import create_reduce_scater_2d_ctx, reduce_scatter_2d_op, ring_reduce

@@ -45,14 +45,14 @@ class MoEAllGatherGroupGEMMTensorParallelContext:
 
     def weights_nk(self, b: torch.Tensor) -> torch.Tensor:
         """[E, N, K] view of the weights; a [E, K, N] tensor is transposed once and cached."""
-        if b.shape[2] == self.K and b.shape[1] == self.N_per_rank and self.K != self.N_per_rank:
-            return b
+        if b.shape[2] == self.K and b.shape[1] == self.N_per_rank:
+            return b  # already [E, N, K]; a square weight is always read this way
         if b.shape[1] == self.K and b.shape[2] == self.N_per_rank:
             key = (b.data_ptr(), b._version)
             if key not in self._weights_nk:
                 self._weights_nk = {key: b.transpose(1, 2).contiguous()}
             return self._weights_nk[key]
-        return b  # square: taken as [E, N, K]
+        raise ValueError(f"weights {tuple(b.shape)} match neither [E, {self.N_per_rank}, {self.K}] nor [E, {self.K}, {self.N_per_rank}]")
 
     def finalize(self) -> None:
         torch.cuda.synchronize()

@@ -23,7 +23,7 @@ from .. import ops
 from ..kernels.allreduce import AllReduceMethod
 from ..kernels.nvidia import (all_reduce_rmsnorm, create_ag_gemm_context, create_allreduce_ctx,
                               create_gemm_rs_context)
-from ..layers.nvidia import TP_MLP, TP_Attn, _set_cos_sin_cache, layer_norm
+from ..layers.nvidia import TP_MLP, TP_Attn, TP_MoE, _set_cos_sin_cache, layer_norm
 from .config import ArchConfig, ModelConfig
 from .kv_cache import KV_Cache
 from .utils import logger
@@ -53,8 +53,19 @@ class Qwen3Layer:
             q_norm=src.get(p + "self_attn.q_norm.weight") if src.has(p + "self_attn.q_norm.weight") else None,
             k_norm=src.get(p + "self_attn.k_norm.weight") if src.has(p + "self_attn.k_norm.weight") else None,
             num_heads=arch.num_attention_heads, num_kv_heads=arch.num_key_value_heads, eps=arch.rms_norm_eps)
-        self.mlp._init_parameters(gate=src.get(p + "mlp.gate_proj.weight", rows=Is), up=src.get(p + "mlp.up_proj.weight", rows=Is),
-                                  down=src.get(p + "mlp.down_proj.weight", cols=Is))
+        if arch.num_experts:
+            # MoE block: every expert's intermediate dimension is sharded over the ranks
+            Im = slice(rank * arch.moe_intermediate_size // world, (rank + 1) * arch.moe_intermediate_size // world)
+            self.mlp = TP_MoE(rank, world, self.attn.group, arch.num_experts_per_tok, arch.norm_topk_prob)
+            gu, dn = [], []
+            for e in range(arch.num_experts):
+                q = p + f"mlp.experts.{e}."
+                gu.append(torch.cat([src.get(q + "gate_proj.weight", rows=Im), src.get(q + "up_proj.weight", rows=Im)], dim=0))
+                dn.append(src.get(q + "down_proj.weight", cols=Im))
+            self.mlp._init_parameters(src.get(p + "mlp.gate.weight"), torch.stack(gu), torch.stack(dn))
+        else:
+            self.mlp._init_parameters(gate=src.get(p + "mlp.gate_proj.weight", rows=Is), up=src.get(p + "mlp.up_proj.weight", rows=Is),
+                                      down=src.get(p + "mlp.down_proj.weight", cols=Is))
         self.input_norm_w = src.get(p + "input_layernorm.weight")
         self.post_norm_w = src.get(p + "post_attention_layernorm.weight")
         self.eps = arch.rms_norm_eps
@@ -74,8 +85,9 @@ class Qwen3Layer:
         hidden = residual + x
         residual = hidden
         x = layer_norm(hidden, self.eps, self.post_norm_w)
-        x = self.mlp.torch_fwd(x) if self.mode == "torch" else self.mlp.dist_triton_fwd(x)
-        return residual + x
+        x2 = x.reshape(-1, x.shape[-1])
+        x2 = self.mlp.torch_fwd(x2) if self.mode == "torch" else self.mlp.dist_triton_fwd(x2)
+        return residual + x2.reshape(x.shape)
 
 
 class Qwen3:
@@ -87,11 +99,12 @@ class Qwen3:
         self.dtype = model_config.dtype
         self.arch = model_config.arch()
         a = self.arch
-        if a.num_attention_heads % self.world_size or a.intermediate_size % self.world_size:
+        if a.num_attention_heads % self.world_size or (a.num_experts == 0 and a.intermediate_size % self.world_size) or (
+                a.num_experts and a.moe_intermediate_size % self.world_size):
             raise ValueError("heads and intermediate size must be divisible by the world size")
         self.device = "cuda" if torch.cuda.is_available() else "cpu"
         self.mode = "torch"
-        self.ar_ctx = self.ag_ctx_qkv = self.ag_ctx_mlp = self.rs_ctx = None
+        self.ar_ctx = self.ag_ctx_qkv = self.ag_ctx_mlp = self.rs_ctx = self.moe_ctx = None
         self.ar_method = None
         self.max_length = model_config.max_length
         self.init_parameters(source)
@@ -143,9 +156,15 @@ class Qwen3:
             # one gather context serves both projections (same K); one scatter context serves o_proj and down
             self.ag_ctx_qkv = create_ag_gemm_context(dummy, l0.attn.wqkv, self.rank, self.world_size, max_M)
             self.rs_ctx = create_gemm_rs_context(max_M, H, self.rank, self.world_size, self.world_size, self.dtype)
+        if self.arch.num_experts and self.moe_ctx is None:
+            self.layers[0].mlp._init_ctx(max_M)  # one pair of MoE contexts serves every layer
+            self.moe_ctx = (self.layers[0].mlp.ag_ctx, self.layers[0].mlp.rs_ctx)
         for layer in self.layers:
             layer.attn._init_ctx(max_M, ag_ctx=self.ag_ctx_qkv, rs_ctx=self.rs_ctx)
-            layer.mlp._init_ctx(max_M, ag_ctx=self.ag_ctx_qkv, rs_ctx=self.rs_ctx)
+            if self.arch.num_experts:
+                layer.mlp.ag_ctx, layer.mlp.rs_ctx = self.moe_ctx
+            else:
+                layer.mlp._init_ctx(max_M, ag_ctx=self.ag_ctx_qkv, rs_ctx=self.rs_ctx)
 
     def init_triton_dist_AR_ctx(self, max_M: int, ar_method: AllReduceMethod | None = None) -> None:
         self.ar_method = ar_method
@@ -163,10 +182,10 @@ class Qwen3:
                                    (widest + 127) // 128)
 
     def finalize(self) -> None:
-        for c in (self.ar_ctx, self.ag_ctx_qkv, self.rs_ctx):
+        for c in (self.ar_ctx, self.ag_ctx_qkv, self.rs_ctx) + tuple(self.moe_ctx or ()):
             if c:
                 c.finalize()
-        self.ar_ctx = self.ag_ctx_qkv = self.rs_ctx = None
+        self.ar_ctx = self.ag_ctx_qkv = self.rs_ctx = self.moe_ctx = None
 
     # ------------------------------------------------------------------ forward
     def _reduce_norm(self, partial, residual, gamma):
