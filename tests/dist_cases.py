@@ -432,6 +432,34 @@ def reduce_scatter_op_and_moe_layers():
         ep.finalize()
 
 
+@case
+def sp_ag_attention_prefill():
+    from triton_distributed_b200.kernels.nvidia import create_sp_ag_attention_context_intra_node, fused_sp_ag_attn_intra_node
+    from triton_distributed_b200.kernels.nvidia.sp_ag_attention_intra_node import zigzag_positions
+    rank, world = _rank_world()
+    Hq, Hkv, D = 8, 2, 64
+    lens = [16 * world, 48 * world]
+    torch.manual_seed(21)
+    q = [torch.randn(L, Hq, D, device="cuda", dtype=torch.bfloat16) for L in lens]
+    k = [torch.randn(L, Hkv, D, device="cuda", dtype=torch.bfloat16) for L in lens]
+    v = [torch.randn(L, Hkv, D, device="cuda", dtype=torch.bfloat16) for L in lens]
+    ctx = create_sp_ag_attention_context_intra_node(len(lens), Hq, Hkv, sum(lens), max(lens) // world, D, torch.bfloat16,
+                                                    torch.bfloat16, rank, world)
+    pos = [zigzag_positions(L, rank, world, "cuda") for L in lens]
+    q_sh = torch.cat([qq[p] for qq, p in zip(q, pos)])
+    k_sh = torch.cat([kk[p] for kk, p in zip(k, pos)])
+    v_sh = torch.cat([vv[p] for vv, p in zip(v, pos)])
+    cu_q = torch.tensor([0] + [sum(l // world for l in lens[:i + 1]) for i in range(len(lens))], dtype=torch.int32)
+    cu_k = torch.tensor([0] + [sum(lens[:i + 1]) for i in range(len(lens))], dtype=torch.int32)
+    out = fused_sp_ag_attn_intra_node(ctx, q_sh, k_sh, v_sh, None, cu_q, cu_k, max(lens) // world, max(lens), rank, world)
+    torch.cuda.synchronize()
+    for i, L in enumerate(lens):
+        full = torch.nn.functional.scaled_dot_product_attention(q[i].float().transpose(0, 1)[None], k[i].float().transpose(0, 1)[None],
+                                                                v[i].float().transpose(0, 1)[None], is_causal=True, enable_gqa=True)[0].transpose(0, 1)
+        torch.testing.assert_close(out[cu_q[i]:cu_q[i + 1]].float(), full[pos[i]], rtol=3e-2, atol=3e-2)
+    ctx.finalize()
+
+
 def main() -> int:
     U.initialize_distributed(seed=0, heap_bytes=int(os.environ.get("B200DIST_TEST_HEAP", 3 << 30)))
     rank, world = _rank_world()

@@ -17,3 +17,4 @@ from .low_latency_all_to_all import all_to_all_post_process, create_all_to_all_c
 from .allgather import (AllGatherMethod, cp_engine_producer_all_gather_inter_node, cp_engine_producer_all_gather_intra_node,
                         get_auto_all_gather_method)
 from .reduce_scatter import create_reduce_scater_2d_ctx, reduce_scatter_2d_op, ring_reduce
+from .sp_ag_attention_intra_node import create_sp_ag_attention_context_intra_node, fused_sp_ag_attn_intra_node

@@ -52,7 +52,7 @@ def create_fast_allgather_context(rank: int, node: int, num_ranks: int, num_node
     heap = get_heap()
     lib = _lib.load()
     max_ctas = lib.b200_allgather_max_ctas()
-    ll = [heap.create_tensor((2 * max_buffer_size,), torch.uint8, align=1024) for _ in range(2)]
+    ll = [heap.create_tensor((max(2 * max_buffer_size, 16),), torch.uint8, align=1024) for _ in range(2)]
     flags = heap.create_tensor((2 * max_ctas * 8,), torch.int32)
     ctx = FastAllGatherContext(rank, node, num_ranks, num_nodes, max_buffer_size, heap, ll, flags,
                                torch.zeros(4, dtype=torch.int32, device="cuda"), max_ctas)
