@@ -416,7 +416,7 @@ def reduce_scatter_op_and_moe_layers():
     for it in range(2):
         got = tp.dist_triton_fwd(x[rank * per:(rank + 1) * per].contiguous())
         torch.cuda.synchronize()
-        torch.testing.assert_close(got.float(), want[rank * per:(rank + 1) * per].float(), rtol=5e-2, atol=0.15)
+        torch.testing.assert_close(got.float(), want[rank * per:(rank + 1) * per].float(), rtol=5e-2, atol=0.1 * world)
     tp.finalize()
     # EP-MoE layer: every rank owns E / world whole experts
     for fp8 in (False, True):
@@ -428,7 +428,7 @@ def reduce_scatter_op_and_moe_layers():
         for it in range(2):
             got = ep.dist_triton_fwd(xl)
             torch.cuda.synchronize()
-            torch.testing.assert_close(got.float(), want_l.float(), rtol=0.12 if fp8 else 5e-2, atol=0.3 if fp8 else 0.15)
+            torch.testing.assert_close(got.float(), want_l.float(), rtol=0.12 if fp8 else 5e-2, atol=(0.3 if fp8 else 0.1) * world)
         ep.finalize()
 
 
@@ -468,8 +468,17 @@ def main() -> int:
     if rank == 0:
         print(f"[dist_cases] world={world} heap mode={heap.mode} multicast={heap.has_multicast}", flush=True)
     failed = 0
+    # Verdicts travel over a gloo group so that a rank whose case failed early cannot collide with the NCCL
+    # collectives its peers are still issuing; a watchdog ends the process if a case stalls.
+    import datetime
+    import threading
+    verdict_group = dist.new_group(list(range(world)), backend="gloo", timeout=datetime.timedelta(seconds=120))
+    case_budget_s = int(os.environ.get("B200DIST_CASE_TIMEOUT_S", "120"))
     for name in names:
         ok, err = True, ""
+        dog = threading.Timer(case_budget_s, lambda n=name: (print(f"CASE {n} STALLED on rank {rank}: giving up", flush=True), os._exit(3)))
+        dog.daemon = True
+        dog.start()
         try:
             CASES[name]()
             torch.cuda.synchronize()
@@ -477,7 +486,13 @@ def main() -> int:
         except Exception:  # noqa: BLE001
             ok, err = False, traceback.format_exc()
         verdicts = [None] * world
-        dist.all_gather_object(verdicts, (ok, err))
+        try:
+            dist.all_gather_object(verdicts, (ok, err), group=verdict_group)
+        except Exception:  # noqa: BLE001
+            print(f"CASE {name} FAIL (rank {rank}: verdict exchange failed)\n{err}", flush=True)
+            os._exit(2)
+        finally:
+            dog.cancel()
         all_ok = all(v[0] for v in verdicts)
         if rank == 0:
             print(f"CASE {name} {'PASS' if all_ok else 'FAIL'}", flush=True)

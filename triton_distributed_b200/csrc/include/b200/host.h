@@ -102,4 +102,26 @@ int make_tma_3d(CUtensorMap* map, const void* base, int dtype, uint64_t d0, uint
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Whether kernels of the decode path are launched with programmatic stream serialization (on unless
+// B200DIST_PDL=0): the next kernel's CTAs may start their prologue while this one drains.
+bool pdl_enabled();
+
+// Launch with the programmatic-dependent-launch attribute. The kernel must execute griddep_wait() before it reads
+// anything an earlier kernel wrote or writes anything an earlier kernel may still read.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+  cudaLaunchConfig_t cfg;
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace b200

@@ -86,6 +86,12 @@ __device__ __forceinline__ int flat_tid() {
   return threadIdx.x + blockDim.x * (threadIdx.y + blockDim.y * threadIdx.z);
 }
 
+// Programmatic dependent launch. griddep_launch_dependents(): the next kernel of the stream may be scheduled once
+// every CTA of this grid has said so (or exited). griddep_wait(): block until the kernels this one depends on have
+// completed and their memory operations are visible; call it before touching anything they produce or still read.
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ----------------------------------------------------------------------------------------------
 // scoped loads / stores / atomics on 32- and 64-bit words
 // ----------------------------------------------------------------------------------------------

@@ -167,6 +167,8 @@ template <int DT>
 __global__ void __launch_bounds__(kArThreads) allreduce_kernel(const ArParams p, const SymmCtx ctx) {
   using V = Vec<DT>;
   __shared__ float red[32];
+  griddep_launch_dependents();
+  griddep_wait();
   const uint32_t epoch = epoch_begin(p.sync);
   const int par = epoch & 1;
   const int world = ctx.world, me = ctx.rank;
@@ -390,10 +392,9 @@ B200_API int b200_allreduce(const void* symm_ctx, const void* in, void* out, uin
   if (grid > kArMaxCtas) grid = kArMaxCtas;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (dtype) {
-    case kBF16: allreduce_kernel<kBF16><<<grid, kArThreads, 0, s>>>(p, ctx); break;
-    case kF16: allreduce_kernel<kF16><<<grid, kArThreads, 0, s>>>(p, ctx); break;
-    default: allreduce_kernel<kF32><<<grid, kArThreads, 0, s>>>(p, ctx); break;
+    case kBF16: B200_CHECK_CUDA(launch_pdl(allreduce_kernel<kBF16>, grid, kArThreads, 0, s, p, ctx)); break;
+    case kF16: B200_CHECK_CUDA(launch_pdl(allreduce_kernel<kF16>, grid, kArThreads, 0, s, p, ctx)); break;
+    default: B200_CHECK_CUDA(launch_pdl(allreduce_kernel<kF32>, grid, kArThreads, 0, s, p, ctx)); break;
   }
-  B200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }

@@ -69,6 +69,8 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
 template <bool BF16>
 __global__ void __launch_bounds__(kAttnThreads) decode_split_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
+  griddep_launch_dependents();
+  griddep_wait();
   const int split = blockIdx.x, b = blockIdx.z;
   const int G = p.Hq / p.Hkv;
   const int hgroups = (G + 15) / 16;
@@ -303,6 +305,8 @@ __global__ void __launch_bounds__(kD) decode_combine_kernel(const float* o_part,
                                                             long long lse_stride_s, int S, void* out, float* out_f32,
                                                             float* out_lse) {
   const int bh = blockIdx.x, c = threadIdx.x;
+  griddep_launch_dependents();
+  griddep_wait();
   float mg = -INFINITY;
   for (int s = 0; s < S; ++s) mg = fmaxf(mg, lse_part[bh * lse_stride_bh + s * lse_stride_s]);
   float lg = 0.f, og = 0.f;
@@ -356,9 +360,8 @@ B200_API int b200_decode_attn_split(const void* q, const void* k_cache, const vo
   const int G = Hq / Hkv;
   dim3 grid(num_splits, Hkv * ((G + 15) / 16), B);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == kBF16) decode_split_kernel<true><<<grid, kAttnThreads, kAttnSmem, s>>>(p);
-  else decode_split_kernel<false><<<grid, kAttnThreads, kAttnSmem, s>>>(p);
-  B200_CHECK_CUDA(cudaGetLastError());
+  if (dtype == kBF16) B200_CHECK_CUDA(launch_pdl(decode_split_kernel<true>, grid, kAttnThreads, kAttnSmem, s, p));
+  else B200_CHECK_CUDA(launch_pdl(decode_split_kernel<false>, grid, kAttnThreads, kAttnSmem, s, p));
   return kOk;
 }
 
@@ -368,11 +371,10 @@ B200_API int b200_decode_combine(const float* o_part, const float* lse_part, lon
   if (BH == 0) return kOk;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == kBF16)
-    decode_combine_kernel<true><<<BH, kD, 0, s>>>(o_part, lse_part, o_stride_bh, o_stride_s, lse_stride_bh, lse_stride_s,
-                                                  S, out, out_f32, out_lse);
+    B200_CHECK_CUDA(launch_pdl(decode_combine_kernel<true>, BH, kD, 0, s, o_part, lse_part, o_stride_bh, o_stride_s,
+                               lse_stride_bh, lse_stride_s, S, out, out_f32, out_lse));
   else
-    decode_combine_kernel<false><<<BH, kD, 0, s>>>(o_part, lse_part, o_stride_bh, o_stride_s, lse_stride_bh, lse_stride_s,
-                                                   S, out, out_f32, out_lse);
-  B200_CHECK_CUDA(cudaGetLastError());
+    B200_CHECK_CUDA(launch_pdl(decode_combine_kernel<false>, BH, kD, 0, s, o_part, lse_part, o_stride_bh, o_stride_s,
+                               lse_stride_bh, lse_stride_s, S, out, out_f32, out_lse));
   return kOk;
 }

@@ -38,6 +38,8 @@ __global__ void __launch_bounds__(512) rmsnorm_kernel(const uint4* __restrict__ 
                                                       uint4* __restrict__ y, int rows, int hidden, float eps) {
   __shared__ float red[32];
   const int nv = hidden / 8;
+  griddep_launch_dependents();
+  griddep_wait();
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     float v[4][8];
     float ss = 0.f;
@@ -97,6 +99,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const uint2* __restri
                                                            uint2* __restrict__ q_out, uint2* k_cache, uint2* v_cache,
                                                            int T, int Hq, int Hkv, float eps) {
   const int heads = Hq + 2 * Hkv;
+  griddep_launch_dependents();
+  griddep_wait();
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp_global >= T * heads) return;
@@ -155,6 +159,8 @@ template <bool BF16>
 __global__ void __launch_bounds__(256) silu_mul_kernel(const uint4* __restrict__ x, uint4* __restrict__ out, int T,
                                                        int inter, int ldx) {
   const int nv = inter / 8;
+  griddep_launch_dependents();
+  griddep_wait();
   const size_t total = static_cast<size_t>(T) * nv;
   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const int t = idx / nv, i = idx - static_cast<size_t>(t) * nv;
@@ -243,13 +249,13 @@ B200_API int b200_rmsnorm(const void* x, const void* residual_in, void* residual
   const int grid = rows < 4 * sm_count() ? rows : 4 * sm_count();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == kBF16)
-    rmsnorm_kernel<true><<<grid, threads, 0, s>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(residual_in),
-                                                  static_cast<uint4*>(residual_out), static_cast<const uint4*>(gamma),
-                                                  static_cast<uint4*>(y), rows, hidden, eps);
+    B200_CHECK_CUDA(launch_pdl(rmsnorm_kernel<true>, grid, threads, 0, s, static_cast<const uint4*>(x),
+                               static_cast<const uint4*>(residual_in), static_cast<uint4*>(residual_out),
+                               static_cast<const uint4*>(gamma), static_cast<uint4*>(y), rows, hidden, eps));
   else
-    rmsnorm_kernel<false><<<grid, threads, 0, s>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(residual_in),
-                                                   static_cast<uint4*>(residual_out), static_cast<const uint4*>(gamma),
-                                                   static_cast<uint4*>(y), rows, hidden, eps);
+    B200_CHECK_CUDA(launch_pdl(rmsnorm_kernel<false>, grid, threads, 0, s, static_cast<const uint4*>(x),
+                               static_cast<const uint4*>(residual_in), static_cast<uint4*>(residual_out),
+                               static_cast<const uint4*>(gamma), static_cast<uint4*>(y), rows, hidden, eps));
   B200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }
@@ -264,15 +270,15 @@ B200_API int b200_qk_norm_rope(const void* qkv, const int* positions, const int6
   const int grid = static_cast<int>((warps + 7) / 8);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == kBF16)
-    qk_norm_rope_kernel<true><<<grid, 256, 0, s>>>(static_cast<const uint2*>(qkv), positions, slots,
-                                                   static_cast<const uint2*>(q_gamma), static_cast<const uint2*>(k_gamma),
-                                                   cos_sin, static_cast<uint2*>(q_out), static_cast<uint2*>(k_cache),
-                                                   static_cast<uint2*>(v_cache), T, Hq, Hkv, eps);
+    B200_CHECK_CUDA(launch_pdl(qk_norm_rope_kernel<true>, grid, 256, 0, s, static_cast<const uint2*>(qkv), positions, slots,
+                               static_cast<const uint2*>(q_gamma), static_cast<const uint2*>(k_gamma), cos_sin,
+                               static_cast<uint2*>(q_out), static_cast<uint2*>(k_cache), static_cast<uint2*>(v_cache), T, Hq,
+                               Hkv, eps));
   else
-    qk_norm_rope_kernel<false><<<grid, 256, 0, s>>>(static_cast<const uint2*>(qkv), positions, slots,
-                                                    static_cast<const uint2*>(q_gamma), static_cast<const uint2*>(k_gamma),
-                                                    cos_sin, static_cast<uint2*>(q_out), static_cast<uint2*>(k_cache),
-                                                    static_cast<uint2*>(v_cache), T, Hq, Hkv, eps);
+    B200_CHECK_CUDA(launch_pdl(qk_norm_rope_kernel<false>, grid, 256, 0, s, static_cast<const uint2*>(qkv), positions, slots,
+                               static_cast<const uint2*>(q_gamma), static_cast<const uint2*>(k_gamma), cos_sin,
+                               static_cast<uint2*>(q_out), static_cast<uint2*>(k_cache), static_cast<uint2*>(v_cache), T, Hq,
+                               Hkv, eps));
   B200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }
@@ -286,9 +292,9 @@ B200_API int b200_silu_mul(const void* x, void* out, int T, int inter, int ldx, 
   const int grid = static_cast<int>(blocks < 8LL * sm_count() ? blocks : 8LL * sm_count());
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == kBF16)
-    silu_mul_kernel<true><<<grid, 256, 0, s>>>(static_cast<const uint4*>(x), static_cast<uint4*>(out), T, inter, ldx);
+    B200_CHECK_CUDA(launch_pdl(silu_mul_kernel<true>, grid, 256, 0, s, static_cast<const uint4*>(x), static_cast<uint4*>(out), T, inter, ldx));
   else
-    silu_mul_kernel<false><<<grid, 256, 0, s>>>(static_cast<const uint4*>(x), static_cast<uint4*>(out), T, inter, ldx);
+    B200_CHECK_CUDA(launch_pdl(silu_mul_kernel<false>, grid, 256, 0, s, static_cast<const uint4*>(x), static_cast<uint4*>(out), T, inter, ldx));
   B200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }

@@ -87,6 +87,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const uint64_t timeout_ns = 4000000000ull;
   const int u_begin = blockIdx.x * p.units_per_cta;
   const int u_end = min(p.units_total, u_begin + p.units_per_cta);
+  griddep_launch_dependents();  // the next kernel may set itself up while this one streams
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < p.stages; ++i) {
@@ -110,21 +111,35 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
   if (warp == 0) {
     if (elect_one()) {
+      // The weights do not depend on the previous kernel, the activations do: the first ring of weight tiles is
+      // requested before griddep_wait(), the matching activation tiles right after it.
       uint32_t stage = 0, phase = 0;
       int u = u_begin;
       Segment sg;
-      bool ok = true;
+      bool ok = true, waited = false;
+      int ndef = 0;
+      int def_kb[kSkMaxStages];
+      auto flush_deferred = [&]() {
+        griddep_wait();
+        fence_proxy_async();
+        waited = true;
+        for (int j = 0; j < ndef; ++j)
+          tma_load_2d(smem + j * p.stage_bytes + kW * kSkWBytes, &tmX, full_bar + j, def_kb[j] * kSkBK, 0);
+      };
       while (ok && next_segment(p, u, u_end, sg)) {
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+          if (!waited && ndef == p.stages) flush_deferred();
           if (!mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, timeout_ns)) { ok = false; break; }
           uint8_t* s = smem + stage * p.stage_bytes;
           mbar_expect_tx(full_bar + stage, p.stage_bytes);
           tma_load_2d(s, &tmW, full_bar + stage, kb * kSkBK, sg.tile * kSkBN);
           if (kDual) tma_load_2d(s + kSkWBytes, &tmW, full_bar + stage, kb * kSkBK, p.up_row0 + sg.tile * kSkBN);
-          tma_load_2d(s + kW * kSkWBytes, &tmX, full_bar + stage, kb * kSkBK, 0);
+          if (waited) tma_load_2d(s + kW * kSkWBytes, &tmX, full_bar + stage, kb * kSkBK, 0);
+          else def_kb[ndef++] = kb;
           if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
         }
       }
+      if (!waited) flush_deferred();
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -166,6 +181,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     uint32_t it = 0;
     int u = u_begin;
     Segment sg;
+    griddep_wait();  // the output, the scratch tile and the tickets may still be in use by the previous kernel
     while (next_segment(p, u, u_end, sg)) {
       const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
       ++it;
@@ -253,8 +269,7 @@ static int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const Ski
                                          kSkSmemBudget + 1024));
     configured[dev & 63] = true;
   }
-  gemm_skinny_kernel<kDual><<<grid, 256, smem, stream>>>(tw, tx, p);
-  B200_CHECK_CUDA(cudaGetLastError());
+  B200_CHECK_CUDA(launch_pdl(gemm_skinny_kernel<kDual>, grid, dim3(256), static_cast<size_t>(smem), stream, tw, tx, p));
   return kOk;
 }
 

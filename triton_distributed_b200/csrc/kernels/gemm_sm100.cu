@@ -27,6 +27,7 @@
 #include "b200/primitives.cuh"
 #include "b200/tcgen05.cuh"
 
+#include <cstdlib>
 #include <cstring>
 
 namespace b200 {
@@ -41,6 +42,11 @@ constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kEpiBytes = 4 * 32 * 128;  // 4 warps x 32 rows x 64 bf16
 constexpr int kGemmSmem = kStages * kStageBytes + kEpiBytes + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int kTmemCols = 512;
+// CTA-pair variant: each CTA stages 128 rows of A and 128 of the 256 rows of B per k-block (32 KB), six stages deep.
+constexpr int kPairBBytes = 128 * kBK * 2;
+constexpr int kPairStageBytes = kABytes + kPairBBytes;
+constexpr int kPairStages = 6;
+static_assert(kPairStages * kPairStageBytes == kStages * kStageBytes, "both variants use the same shared-memory budget");
 constexpr int kCommThreads = 64;
 constexpr int kCommRows = 8;  // rows per communication chunk
 
@@ -120,17 +126,20 @@ __device__ __forceinline__ void comm_copy(uint8_t* dst, const uint8_t* src, size
   for (; i < nvec; i += kCommThreads) st_v4(d + i, ld_v4_relaxed_sys(s + i));
 }
 
-template <int kMode>
+template <int kMode, int kCtas>
 __global__ void __launch_bounds__(256, 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                   const __grid_constant__ CUtensorMap tmB, const GemmParams p, const SymmCtx ctx) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr bool kPair = kCtas == 2;
+  constexpr int kNS = kPair ? kPairStages : kStages;              // pipeline depth
+  constexpr int kSB = kPair ? kPairStageBytes : kStageBytes;      // bytes per stage in this CTA
   uint8_t* epi_smem = smem + kStages * kStageBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + kEpiBytes);
-  uint64_t* full_bar = bars;                 // [kStages]
-  uint64_t* empty_bar = bars + kStages;      // [kStages]
-  uint64_t* tfull_bar = bars + 2 * kStages;  // [2]
+  uint64_t* full_bar = bars;                        // [kNS] (pair: only the leader's copy is used)
+  uint64_t* empty_bar = bars + kPairStages;         // [kNS]
+  uint64_t* tfull_bar = bars + 2 * kPairStages;     // [2]
   uint64_t* tempty_bar = tfull_bar + 2;      // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -138,8 +147,12 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_tiles = p.tiles_m * p.tiles_n;
+  const int total_tiles = p.tiles_m * p.tiles_n;  // pair: tiles are 256 rows high
   const int num_kb = (p.K + kBK - 1) / kBK;
+  const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
+  const int unit = blockIdx.x / kCtas, num_units = gridDim.x / kCtas;  // a unit = one CTA or one CTA pair
+  const int m_blocks = (p.M + kBM - 1) / kBM;
   const uint64_t pipe_timeout = ctx.timeout_ns;
 
   uint32_t epoch = 1;
@@ -147,22 +160,26 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
   const int par = epoch & 1;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kStages; ++i) {
+    for (int i = 0; i < kNS; ++i) {
       mbar_init(full_bar + i, 1);
       mbar_init(empty_bar + i, 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(tfull_bar + i, 1);
-      mbar_init(tempty_bar + i, 4);
+      mbar_init(tempty_bar + i, 4 * kCtas);  // pair: the epilogue warps of both CTAs release the leader's accumulator
     }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA0);
     tma_prefetch_desc(&tmB);
   }
-  if (warp == 2) tmem_alloc(tmem_slot, kTmemCols);
+  if (warp == 2) {
+    if (kPair) tmem_alloc_pair(tmem_slot, kTmemCols);
+    else tmem_alloc(tmem_slot, kTmemCols);
+  }
   tc_fence_before_sync();
   __syncthreads();
+  if (kPair) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -172,32 +189,40 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
       const CUtensorMap* tmA = (kMode == kAG && par) ? &tmA1 : &tmA0;
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < total_tiles && ok; t += num_units) {
         int m_blk, n_blk;
         tile_coords(p, t, m_blk, n_blk);
-        if (kMode == kAG) {
+        if (kPair) m_blk = 2 * m_blk + static_cast<int>(cta_rank);
+        if (kMode == kAG && m_blk < m_blocks) {
           ok = wait_flag<WaitCmp::EQ, false>(ctx, p.blk_flag + m_blk, epoch, m_blk, __LINE__);
           if (!ok) { *abort_flag = 1; break; }
           fence_proxy_async();
         }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, pipe_timeout)) { ok = false; break; }
-          uint8_t* sa = smem + stage * kStageBytes;
-          mbar_expect_tx(full_bar + stage, kStageBytes);
-          tma_load_2d(sa, tmA, full_bar + stage, kb * kBK, m_blk * kBM);
-          tma_load_2d(sa + kABytes, &tmB, full_bar + stage, kb * kBK, n_blk * kBN);
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          uint8_t* sa = smem + stage * kSB;
+          if (kPair) {
+            // both CTAs' loads credit the leader's barrier; the leader announces the bytes of the whole pair
+            if (leader) mbar_expect_tx(full_bar + stage, 2 * kSB);
+            tma_load_2d_pair(sa, tmA, full_bar + stage, kb * kBK, m_blk * kBM);
+            tma_load_2d_pair(sa + kABytes, &tmB, full_bar + stage, kb * kBK, n_blk * kBN + static_cast<int>(cta_rank) * 128);
+          } else {
+            mbar_expect_tx(full_bar + stage, kSB);
+            tma_load_2d(sa, tmA, full_bar + stage, kb * kBK, m_blk * kBM);
+            tma_load_2d(sa + kABytes, &tmB, full_bar + stage, kb * kBK, n_blk * kBN);
+          }
+          if (++stage == kNS) { stage = 0; phase ^= 1; }
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (elect_one()) {
-      const uint32_t idesc = umma_idesc_f16(kBM, kBN, p.bf16 != 0);
+    if (leader && elect_one()) {
+      const uint32_t idesc = umma_idesc_f16(kBM * kCtas, kBN, p.bf16 != 0);
       uint32_t stage = 0, phase = 0, it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      for (int t = unit; t < total_tiles && ok; t += num_units, ++it) {
         const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
         if (!mbar_wait(tempty_bar + acc, acc_phase ^ 1, abort_flag, pipe_timeout)) break;
         tc_fence_after_sync();
@@ -205,16 +230,30 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(full_bar + stage, phase, abort_flag, pipe_timeout)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + stage * kStageBytes);
+          const uint32_t sa = smem_u32(smem + stage * kSB);
           const uint64_t da = umma_desc_sw128_kmajor(sa);
           const uint64_t db = umma_desc_sw128_kmajor(sa + kABytes);
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k)
-            umma_f16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-          umma_commit(empty_bar + stage);
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          for (int k = 0; k < kBK / 16; ++k) {
+            if (kPair) umma_f16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_f16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          if (kPair) {  // free the stage in both CTAs
+            umma_commit_pair(mapa_u32(empty_bar + stage, 0));
+            umma_commit_pair(mapa_u32(empty_bar + stage, 1));
+          } else {
+            umma_commit(empty_bar + stage);
+          }
+          if (++stage == kNS) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(tfull_bar + acc);
+        if (ok) {
+          if (kPair) {
+            umma_commit_pair(mapa_u32(tfull_bar + acc, 0));
+            umma_commit_pair(mapa_u32(tfull_bar + acc, 1));
+          } else {
+            umma_commit(tfull_bar + acc);
+          }
+        }
       }
     }
     __syncwarp();
@@ -273,9 +312,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
     const int w = warp - 4;  // == warp % 4: the TMEM lane quarter this warp may read
     uint8_t* stg = epi_smem + w * (32 * 128);
     uint32_t it = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+    for (int t = unit; t < total_tiles; t += num_units, ++it) {
       int m_blk, n_blk;
       tile_coords(p, t, m_blk, n_blk);
+      if (kPair) m_blk = 2 * m_blk + static_cast<int>(cta_rank);
       const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
       if (!mbar_wait(tfull_bar + acc, acc_phase, abort_flag, pipe_timeout)) break;
       tc_fence_after_sync();
@@ -329,7 +369,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
       // accumulator fully read: hand it back to the MMA warp
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar + acc);
+      if (lane == 0) {
+        if (kPair && !leader) mbar_arrive_cluster(mapa_u32(tempty_bar + acc, 0));
+        else mbar_arrive(tempty_bar + acc);
+      }
       if (kMode == kRS) {
         // tell each owner how many of its rows this warp just delivered for this column block
         const int r_lo = row_base, r_hi = min(row_base + 32, p.M);
@@ -356,15 +399,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
     const int first_blk = seg0 / kBM;
     const int vec_per_row = p.N / 8;
     const uint8_t* slots = static_cast<const uint8_t*>(p.slots[par]);
+    // One work item = one row of this rank's segment; a thread owns up to four 16-byte vectors of the row and issues
+    // all of their loads over all slots (4 x world) before it adds anything, so the phase runs at HBM speed instead
+    // of one load latency per vector.
     int ready_blk = -1;
-    const int ngroups = (p.Mr + 7) / 8;
-    for (int g = blockIdx.x; g < ngroups && !failed; g += gridDim.x) {
-      const int lr0 = g * 8, lr1 = min(p.Mr, lr0 + 8);
-      // rows lr0..lr1 may straddle two 128-row blocks: wait for the later one (blocks complete in order
-      // of j only approximately, so both are checked)
-      const int jb0 = (seg0 + lr0) / kBM - first_blk, jb1 = (seg0 + lr1 - 1) / kBM - first_blk;
-      for (int j = jb0; j <= jb1; ++j) {
-        if (j <= ready_blk) continue;
+    for (int lrow = blockIdx.x; lrow < p.Mr && !failed; lrow += gridDim.x) {
+      const int j = (seg0 + lrow) / kBM - first_blk;
+      if (j > ready_blk) {
         bool ok = true;
         if (threadIdx.x < ctx.world) {
           const int blk = first_blk + j;
@@ -375,31 +416,46 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
         if (!__syncthreads_and(ok)) { failed = true; break; }
         ready_blk = j;
       }
-      if (failed) break;
-      const int nvec = (lr1 - lr0) * vec_per_row;
-      for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
-        const int lrow = lr0 + v / vec_per_row;
-        const int col = (v - (v / vec_per_row) * vec_per_row) * 8;
-        float accv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int s = 0; s < ctx.world; ++s) {
-          const uint4 x = ld_v4_relaxed_sys(slots + ((static_cast<size_t>(s) * p.Mr_cap + lrow) * p.N + col) * 2);
-          const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+      for (int v0 = threadIdx.x; v0 < vec_per_row; v0 += 4 * blockDim.x) {
+        uint4 x[4][kMaxRanks];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float2 f = p.bf16 ? unpack_bf16x2(xs[q]) : unpack_f16x2(xs[q]);
-            accv[2 * q] += f.x;
-            accv[2 * q + 1] += f.y;
+        for (int u = 0; u < 4; ++u) {
+          const int v = v0 + u * blockDim.x;
+          if (v < vec_per_row) {
+#pragma unroll
+            for (int s = 0; s < kMaxRanks; ++s)
+              if (s < ctx.world)
+                x[u][s] = ld_v4_relaxed_sys(slots + ((static_cast<size_t>(s) * p.Mr_cap + lrow) * p.N + v * 8) * 2);
           }
         }
-        uint4 o;
-        if (p.bf16) {
-          o.x = pack_bf16x2(accv[0], accv[1]); o.y = pack_bf16x2(accv[2], accv[3]);
-          o.z = pack_bf16x2(accv[4], accv[5]); o.w = pack_bf16x2(accv[6], accv[7]);
-        } else {
-          o.x = pack_f16x2(accv[0], accv[1]); o.y = pack_f16x2(accv[2], accv[3]);
-          o.z = pack_f16x2(accv[4], accv[5]); o.w = pack_f16x2(accv[6], accv[7]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int v = v0 + u * blockDim.x;
+          if (v < vec_per_row) {
+            float accv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+            for (int s = 0; s < kMaxRanks; ++s) {
+              if (s < ctx.world) {
+                const uint32_t xs[4] = {x[u][s].x, x[u][s].y, x[u][s].z, x[u][s].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const float2 f = p.bf16 ? unpack_bf16x2(xs[q]) : unpack_f16x2(xs[q]);
+                  accv[2 * q] += f.x;
+                  accv[2 * q + 1] += f.y;
+                }
+              }
+            }
+            uint4 o;
+            if (p.bf16) {
+              o.x = pack_bf16x2(accv[0], accv[1]); o.y = pack_bf16x2(accv[2], accv[3]);
+              o.z = pack_bf16x2(accv[4], accv[5]); o.w = pack_bf16x2(accv[6], accv[7]);
+            } else {
+              o.x = pack_f16x2(accv[0], accv[1]); o.y = pack_f16x2(accv[2], accv[3]);
+              o.z = pack_f16x2(accv[4], accv[5]); o.w = pack_f16x2(accv[6], accv[7]);
+            }
+            st_v4(static_cast<uint8_t*>(p.out) + (static_cast<size_t>(lrow) * p.N + v * 8) * 2, o);
+          }
         }
-        st_v4(static_cast<uint8_t*>(p.out) + (static_cast<size_t>(lrow) * p.N + col) * 2, o);
       }
     }
   }
@@ -407,7 +463,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
   // ---------------------------------------------------------------------- teardown
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 2) tmem_dealloc(tmem_base, kTmemCols);
+  if (kPair) cluster_sync_all();  // neither CTA's shared or tensor memory goes away while the pair may still use it
+  if (warp == 2) {
+    if (kPair) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
+  }
   if (threadIdx.x == 0) {
     if (*abort_flag != 0u) report_status(ctx, kStatusPipeTimeout, blockIdx.x, 0, 0, __LINE__);
     if (kMode != kPlain) {
@@ -431,19 +491,59 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
   }
 }
 
-template <int kMode>
-static int launch_gemm(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b, const GemmParams& p,
-                       const SymmCtx& ctx, int grid, cudaStream_t stream) {
+// Whether the tiled GEMMs run as CTA pairs (256x256 tiles, cta_group::2). -1 = decide from B200DIST_GEMM_2CTA (default on).
+static int g_two_cta = -1;
+static bool two_cta_enabled() {
+  if (g_two_cta < 0) {
+    const char* e = getenv("B200DIST_GEMM_2CTA");
+    g_two_cta = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_two_cta == 1;
+}
+
+template <int kMode, int kCtas>
+static int launch_gemm_impl(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b, const GemmParams& p,
+                            const SymmCtx& ctx, int grid, cudaStream_t stream) {
   static bool configured[64] = {false};
   int dev = 0;
   B200_CHECK_CUDA(cudaGetDevice(&dev));
   if (!configured[dev & 63]) {
-    B200_CHECK_CUDA(cudaFuncSetAttribute(gemm_sm100_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
+    B200_CHECK_CUDA(cudaFuncSetAttribute(gemm_sm100_kernel<kMode, kCtas>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
     configured[dev & 63] = true;
   }
-  gemm_sm100_kernel<kMode><<<grid, 256, kGemmSmem, stream>>>(a0, a1, b, p, ctx);
-  B200_CHECK_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = kGemmSmem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kCtas;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = kCtas > 1 ? 1 : 0;
+  B200_CHECK_CUDA(cudaLaunchKernelEx(&cfg, gemm_sm100_kernel<kMode, kCtas>, a0, a1, b, p, ctx));
   return kOk;
+}
+
+// B's TMA box is 256 rows for single CTAs and 128 rows for pairs, so the caller builds the map after this choice.
+static bool use_pair(int M) { return two_cta_enabled() && M > kBM; }
+
+template <int kMode>
+static int launch_gemm(bool pair, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b, const GemmParams& p,
+                       const SymmCtx& ctx, int grid, cudaStream_t stream) {
+  if (pair) return launch_gemm_impl<kMode, 2>(a0, a1, b, p, ctx, grid & ~1, stream);
+  return launch_gemm_impl<kMode, 1>(a0, a1, b, p, ctx, grid, stream);
+}
+
+// Tile geometry for the chosen variant: pairs tile M in 256-row steps (and rotate in those units).
+static void set_tiles(GemmParams& p, bool pair, int first_row) {
+  const int tm = pair ? 2 * kBM : kBM;
+  p.tiles_m = (p.M + tm - 1) / tm;
+  p.m_rot = first_row / tm;
+  if (pair && p.group_m > 1) p.group_m = (p.group_m + 1) / 2;
 }
 
 static int fill_common(GemmParams& p, int M, int N, int K, int dtype, int group_m) {
@@ -475,15 +575,18 @@ B200_API int b200_gemm(const void* A, const void* B, void* C, int M, int N, int 
   CUtensorMap ta, tb;
   rc = make_tma_2d(&ta, A, dtype, M, K, lda, kBM, kBK, true);
   if (rc != kOk) return rc;
-  rc = make_tma_2d(&tb, B, dtype, N, K, ldb, kBN, kBK, true);
+  const bool pair = use_pair(M);
+  set_tiles(p, pair, 0);
+  rc = make_tma_2d(&tb, B, dtype, N, K, ldb, pair ? 128 : kBN, kBK, true);
   if (rc != kOk) return rc;
   SymmCtx ctx;
   memset(&ctx, 0, sizeof(ctx));
   ctx.world = 1;
   ctx.timeout_ns = 4000000000ull;
-  int grid = min(p.tiles_m * p.tiles_n, sm_count());
+  int grid = min(p.tiles_m * p.tiles_n * (pair ? 2 : 1), sm_count());
   if (max_ctas > 0) grid = min(grid, max_ctas);
-  return launch_gemm<kPlain>(ta, ta, tb, p, ctx, grid, static_cast<cudaStream_t>(stream));
+  if (pair && grid < 2) grid = 2;
+  return launch_gemm<kPlain>(pair, ta, ta, tb, p, ctx, grid, static_cast<cudaStream_t>(stream));
 }
 
 // AG-GEMM. a_local [Mr, K] is this rank's shard; ag_buf0/1 are the two symmetric gather buffers
@@ -509,18 +612,19 @@ B200_API int b200_ag_gemm(const void* symm_ctx, const void* a_local, void* ag_bu
   p.blk_flag = blk_flag;
   p.sync = sync;
   p.Mr = Mr;
-  p.m_rot = (ctx.rank * Mr) / kBM;
+  const bool pair = use_pair(M);
+  set_tiles(p, pair, ctx.rank * Mr);
   B200_REQUIRE((reinterpret_cast<uint64_t>(a_local) & 15u) == 0, "a_local must be 16-byte aligned");
   CUtensorMap ta0, ta1, tb;
   rc = make_tma_2d(&ta0, ag_buf0, dtype, M, K, K, kBM, kBK, true);
   if (rc != kOk) return rc;
   rc = make_tma_2d(&ta1, ag_buf1, dtype, M, K, K, kBM, kBK, true);
   if (rc != kOk) return rc;
-  rc = make_tma_2d(&tb, B, dtype, N, K, ldb, kBN, kBK, true);
+  rc = make_tma_2d(&tb, B, dtype, N, K, ldb, pair ? 128 : kBN, kBK, true);
   if (rc != kOk) return rc;
   int grid = sm_count();
   if (max_ctas > 0) grid = min(grid, max_ctas);
-  return launch_gemm<kAG>(ta0, ta1, tb, p, ctx, grid, static_cast<cudaStream_t>(stream));
+  return launch_gemm<kAG>(pair, ta0, ta1, tb, p, ctx, grid, static_cast<cudaStream_t>(stream));
 }
 
 // GEMM-RS. A [M, K] (K is this rank's K shard), B [N, K], out [M / world, N].
@@ -547,13 +651,20 @@ B200_API int b200_gemm_rs(const void* symm_ctx, const void* A, const void* B, vo
   p.Mr_cap = Mr_cap;
   p.rs_blocks = rs_blocks;
   p.out = out;
-  p.m_rot = (((ctx.rank + 1) % ctx.world) * p.Mr) / kBM;
+  const bool pair = use_pair(M);
+  set_tiles(p, pair, ((ctx.rank + 1) % ctx.world) * p.Mr);
   CUtensorMap ta, tb;
   rc = make_tma_2d(&ta, A, dtype, M, K, lda, kBM, kBK, true);
   if (rc != kOk) return rc;
-  rc = make_tma_2d(&tb, B, dtype, N, K, ldb, kBN, kBK, true);
+  rc = make_tma_2d(&tb, B, dtype, N, K, ldb, pair ? 128 : kBN, kBK, true);
   if (rc != kOk) return rc;
   int grid = sm_count();
   if (max_ctas > 0) grid = min(grid, max_ctas);
-  return launch_gemm<kRS>(ta, ta, tb, p, ctx, grid, static_cast<cudaStream_t>(stream));
+  return launch_gemm<kRS>(pair, ta, ta, tb, p, ctx, grid, static_cast<cudaStream_t>(stream));
+}
+
+// 1 = CTA pairs (256x256 tiles, cta_group::2), 0 = single CTAs (128x256), -1 = follow B200DIST_GEMM_2CTA.
+B200_API int b200_set_gemm_two_cta(int mode) {
+  b200::g_two_cta = mode;
+  return kOk;
 }

@@ -54,12 +54,23 @@ __global__ void __launch_bounds__(kSortWarps * 32) moe_sort_kernel(const MoeSort
     const int seg = g / p.num_experts, e = g - seg * p.num_experts;
     const int p0 = seg * p.pairs_per_segment, p1 = p0 + p.pairs_per_segment;
     // ---- count ----
+    // 16-byte loads, two chunks of 128 ids in flight per warp: the scan is latency-bound otherwise
+    const bool vec_ok = (p0 % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.ids) & 15u) == 0);
     int count = 0;
-    for (int b0 = p0; b0 < p1; b0 += 32) {
-      const int i = b0 + lane;
-      const bool hit = i < p1 && p.ids[i] == e;
-      count += __popc(__ballot_sync(0xffffffffu, hit));
+    int b0 = p0;
+    if (vec_ok) {
+      for (; b0 + 256 <= p1; b0 += 256) {
+        const int4 a = *reinterpret_cast<const int4*>(p.ids + b0 + lane * 4);
+        const int4 c = *reinterpret_cast<const int4*>(p.ids + b0 + 128 + lane * 4);
+        count += (a.x == e) + (a.y == e) + (a.z == e) + (a.w == e) + (c.x == e) + (c.y == e) + (c.z == e) + (c.w == e);
+      }
     }
+    for (; b0 < p1; b0 += 32) {
+      const int i = b0 + lane;
+      count += (i < p1 && p.ids[i] == e) ? 1 : 0;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) count += __shfl_xor_sync(0xffffffffu, count, o);
     const int padded = (count + p.block_m - 1) / p.block_m * p.block_m;
     if (lane == 0) {
       p.group_count[g] = count;
@@ -95,22 +106,44 @@ __global__ void __launch_bounds__(kSortWarps * 32) moe_sort_kernel(const MoeSort
       // ---- compact in order ----
       int written = 0;
       const int first_tile = static_cast<int>(offset / p.block_m);
-      for (int b0 = p0; b0 < p1; b0 += 32) {
-        const int i = b0 + lane;
+      auto emit = [&](int i, int pos) {
+        p.sorted_ids[offset + pos] = i;
+        if (p.pair_pos) p.pair_pos[i] = static_cast<int32_t>(offset + pos);
+        // segment bounds of the tile this row falls into (only needed when sorting over all tokens)
+        if (p.segments == 1) {
+          const int src = (i / p.topk) / p.tokens_per_rank;
+          const int tile = first_tile + pos / p.block_m;
+          atomicMin(p.tile_seg_start + tile, src);
+          atomicMax(p.tile_seg_end + tile, src);
+        }
+      };
+      int b1 = p0;
+      if (vec_ok) {
+        // lane l holds ids [b1 + 4l, b1 + 4l + 4): order inside the chunk is (lane, j)
+        for (; b1 + 128 <= p1; b1 += 128) {
+          const int4 a = *reinterpret_cast<const int4*>(p.ids + b1 + lane * 4);
+          const int h0 = a.x == e, h1 = a.y == e, h2 = a.z == e, h3 = a.w == e;
+          const int mine_n = h0 + h1 + h2 + h3;
+          int incl = mine_n;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+          }
+          int pos = written + incl - mine_n;
+          const int i0 = b1 + lane * 4;
+          if (h0) emit(i0, pos++);
+          if (h1) emit(i0 + 1, pos++);
+          if (h2) emit(i0 + 2, pos++);
+          if (h3) emit(i0 + 3, pos++);
+          written += __shfl_sync(0xffffffffu, incl, 31);
+        }
+      }
+      for (; b1 < p1; b1 += 32) {
+        const int i = b1 + lane;
         const bool hit = i < p1 && p.ids[i] == e;
         const uint32_t m = __ballot_sync(0xffffffffu, hit);
-        if (hit) {
-          const int pos = written + __popc(m & ((1u << lane) - 1u));
-          p.sorted_ids[offset + pos] = i;
-          if (p.pair_pos) p.pair_pos[i] = static_cast<int32_t>(offset + pos);
-          // segment bounds of the tile this row falls into (only needed when sorting over all tokens)
-          if (p.segments == 1) {
-            const int src = (i / p.topk) / p.tokens_per_rank;
-            const int tile = first_tile + pos / p.block_m;
-            atomicMin(p.tile_seg_start + tile, src);
-            atomicMax(p.tile_seg_end + tile, src);
-          }
-        }
+        if (hit) emit(i, written + __popc(m & ((1u << lane) - 1u)));
         written += __popc(m);
       }
       for (int i = count + lane; i < padded; i += 32) p.sorted_ids[offset + i] = p.n_pairs;

@@ -2,7 +2,7 @@
 //
 // The nucleus of a row is {i : p_i >= t*} where t* is the largest threshold whose kept mass still reaches
 // top_p; that is the same set a descending sort + cumulative sum selects (up to ties), but it can be found
-// by bisection on t with one block reduction per step, so the 152K-entry vocabulary is never sorted or
+// from two shared-memory histograms of probability mass, so the 152K-entry vocabulary is never sorted or
 // scanned in global memory. The token is then drawn from the kept entries in index order with one uniform
 // random number per row supplied by the caller.
 //
@@ -42,78 +42,179 @@ __device__ __forceinline__ float block_reduce_max(float v, float* red) {
   return red[32];
 }
 
+// Strided pass over a row with eight independent 16-byte loads in flight per thread (one CTA streams a 600 KB row, so
+// memory-level parallelism per thread is what sets the speed). f(index, value) is called for every element.
+template <typename F>
+__device__ __forceinline__ void for_row(const float* __restrict__ row, int V, F f) {
+  const int tid = threadIdx.x;
+  const bool aligned = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
+  int done = 0;
+  if (aligned) {
+    const int nvec = V / 4;
+    const float4* r4 = reinterpret_cast<const float4*>(row);
+    int i = tid;
+    for (; i + 7 * kSampleThreads < nvec; i += 8 * kSampleThreads) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = r4[i + u * kSampleThreads];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int b = (i + u * kSampleThreads) * 4;
+        f(b, v[u].x); f(b + 1, v[u].y); f(b + 2, v[u].z); f(b + 3, v[u].w);
+      }
+    }
+    for (; i < nvec; i += kSampleThreads) {
+      const float4 v = r4[i];
+      f(i * 4, v.x); f(i * 4 + 1, v.y); f(i * 4 + 2, v.z); f(i * 4 + 3, v.w);
+    }
+    done = nvec * 4;
+  }
+  for (int i = done + tid; i < V; i += kSampleThreads) f(i, row[i]);
+}
+
+// Histogram cells are 64-bit fixed point (2^-40): integer shared-memory atomics are native and exact, float ones
+// are compare-and-swap loops that serialise when neighbouring logits fall into the same bin.
+typedef unsigned long long u64;
+__device__ __forceinline__ u64 to_fixed(float e) { return static_cast<u64>(e * 1099511627776.f); }
+
+// Inclusive scan of 1024 cells in shared memory (one per thread), Hillis-Steele.
+__device__ __forceinline__ void scan1024(u64* a) {
+  const int tid = threadIdx.x;
+  for (int off = 1; off < kSampleThreads; off <<= 1) {
+    const u64 add = tid >= off ? a[tid - off] : 0ull;
+    __syncthreads();
+    a[tid] += add;
+    __syncthreads();
+  }
+}
+// First index whose inclusive prefix reaches `target` (kSampleThreads - 1 when none does).
+__device__ __forceinline__ int first_reaching(const u64* incl, u64 target, int* slot) {
+  const int tid = threadIdx.x;
+  if (tid == 0) *slot = kSampleThreads - 1;
+  __syncthreads();
+  if (incl[tid] >= target && (tid == 0 || incl[tid - 1] < target)) *slot = tid;
+  __syncthreads();
+  return *slot;
+}
+
+// The nucleus threshold is found with two histograms over z = (max - logit) / T instead of a sort or a
+// bisection: 1024 bins of width 1/32 locate the bin in which the kept mass crosses top_p, 1024 sub-bins of that
+// bin pin the threshold to a relative probability error of e^(1/32768). Five passes over the row in total.
 __global__ void __launch_bounds__(kSampleThreads) top_p_sample_kernel(const float* __restrict__ logits, int ld, int V,
                                                                       float inv_temperature, float top_p,
                                                                       const float* __restrict__ uniform,
                                                                       long long* __restrict__ out) {
   __shared__ float red[33];
-  __shared__ float prefix[kSampleThreads];
-  __shared__ int chosen;
+  __shared__ u64 cells[kSampleThreads];
+  __shared__ float hist[32];
+  __shared__ int chosen, slot;
   const float* row = logits + static_cast<size_t>(blockIdx.x) * ld;
   const int tid = threadIdx.x;
+  griddep_launch_dependents();
+  griddep_wait();
 
   float mx = -INFINITY;
   int arg = 0;
-  for (int i = tid; i < V; i += kSampleThreads) {
-    const float v = row[i];
-    if (v > mx) { mx = v; arg = i; }
-  }
+  for_row(row, V, [&](int i, float v) {
+    if (v > mx || (v == mx && i < arg)) { mx = v; arg = i; }
+  });
   const float gmax = block_reduce_max(mx, red);
-  // lowest index attaining the maximum: the fallback choice
   if (tid == 0) chosen = 0x7fffffff;
+  cells[tid] = 0ull;
   __syncthreads();
-  if (mx == gmax) atomicMin(&chosen, arg);
-  float z = 0.f;
-  for (int i = tid; i < V; i += kSampleThreads) z += __expf((row[i] - gmax) * inv_temperature);
-  const float Z = block_reduce_sum(z, red);
-  const float inv_z = 1.f / Z;
+  if (mx == gmax) atomicMin(&chosen, arg);  // lowest index attaining the maximum: the fallback choice
 
-  // bisection on the probability threshold: mass(lo) >= top_p > mass(hi)
-  float lo = 0.f, hi = inv_z * 1.0001f;
+  float thr_z = INFINITY;  // keep entries with z < thr_z
   if (top_p < 1.f) {
-    for (int it = 0; it < 18; ++it) {
-      const float mid = 0.5f * (lo + hi);
-      float m = 0.f;
-      for (int i = tid; i < V; i += kSampleThreads) {
-        const float p = __expf((row[i] - gmax) * inv_temperature) * inv_z;
-        m += p >= mid ? p : 0.f;
-      }
-      const float mass = block_reduce_sum(m, red);
-      if (mass >= top_p) lo = mid; else hi = mid;
-    }
+    // pass 2: coarse histogram of probability mass over z
+    for_row(row, V, [&](int, float v) {
+      const float z = (gmax - v) * inv_temperature;  // >= 0
+      atomicAdd(cells + min(kSampleThreads - 1, static_cast<int>(z * 32.f)), to_fixed(__expf(-z)));
+    });
+    __syncthreads();
+    scan1024(cells);
+    const u64 target = static_cast<u64>(static_cast<double>(top_p) * static_cast<double>(cells[kSampleThreads - 1]));
+    const int b = first_reaching(cells, target, &slot);
+    const u64 before = b > 0 ? cells[b - 1] : 0ull;
+    __syncthreads();
+    cells[tid] = 0ull;
+    __syncthreads();
+    // pass 3: refine inside bin b
+    for_row(row, V, [&](int, float v) {
+      const float z = (gmax - v) * inv_temperature;
+      const float zb = z * 32.f;
+      if (min(kSampleThreads - 1, static_cast<int>(zb)) == b)
+        atomicAdd(cells + min(kSampleThreads - 1, max(0, static_cast<int>((zb - b) * 1024.f))), to_fixed(__expf(-z)));
+    });
+    __syncthreads();
+    scan1024(cells);
+    const int sb = first_reaching(cells, target > before ? target - before : 0ull, &slot);
+    thr_z = b == kSampleThreads - 1 ? INFINITY : (b + (sb + 1) * (1.f / 1024.f)) * (1.f / 32.f);
+    __syncthreads();
   }
-  // draw in index order among the kept entries: thread t owns the contiguous chunk [c0, c1)
-  const int per = (V + kSampleThreads - 1) / kSampleThreads;
-  const int c0 = min(V, tid * per), c1 = min(V, c0 + per);
+  // draw in index order among the kept entries. Warp w owns the contiguous range [w * R, (w + 1) * R) and reads it
+  // lane-strided (coalesced); the warp that contains the target then walks its range 32 entries at a time.
+  const int lane = tid & 31, warp = tid >> 5;
+  const int R = (V + 31) / 32;
+  const int r0 = min(V, warp * R), r1 = min(V, r0 + R);
   float mine = 0.f;
-  for (int i = c0; i < c1; ++i) {
-    const float p = __expf((row[i] - gmax) * inv_temperature) * inv_z;
-    mine += p >= lo ? p : 0.f;
-  }
-  prefix[tid] = mine;
-  __syncthreads();
-  // inclusive scan over 1024 chunk sums (Hillis-Steele in shared memory)
-  for (int off = 1; off < kSampleThreads; off <<= 1) {
-    const float add = tid >= off ? prefix[tid - off] : 0.f;
-    __syncthreads();
-    prefix[tid] += add;
-    __syncthreads();
-  }
-  const float total = prefix[kSampleThreads - 1];
-  const float target = uniform[blockIdx.x] * total;
-  const float before = prefix[tid] - mine;
-  if (mine > 0.f && target >= before && target < prefix[tid]) {
-    float acc = before;
-    int pick = -1;
-    for (int i = c0; i < c1; ++i) {
-      const float p = __expf((row[i] - gmax) * inv_temperature) * inv_z;
-      if (p >= lo) {
-        acc += p;
-        pick = i;
-        if (acc > target) break;
+  {
+    int i = r0 + lane;
+    for (; i + 7 * 32 < r1; i += 8 * 32) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = row[i + u * 32];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float z = (gmax - v[u]) * inv_temperature;
+        mine += z < thr_z ? __expf(-z) : 0.f;
       }
     }
-    if (pick >= 0) chosen = pick;
+    for (; i < r1; i += 32) {
+      const float z = (gmax - row[i]) * inv_temperature;
+      mine += z < thr_z ? __expf(-z) : 0.f;
+    }
+  }
+  mine = warp_sum(mine);
+  __syncthreads();
+  if (lane == 0) hist[warp] = mine;
+  __syncthreads();
+  float incl = hist[lane];  // every warp scans the 32 warp totals
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  const float total = __shfl_sync(0xffffffffu, incl, 31);
+  const float target = uniform[blockIdx.x] * total;
+  const float my_incl = __shfl_sync(0xffffffffu, incl, warp);
+  const float my_before = my_incl - mine;
+  if (mine > 0.f && target >= my_before && target < my_incl) {
+    float acc = my_before;
+    int pick = -1;
+    for (int b0 = r0; b0 < r1 && pick < 0; b0 += 32) {
+      const int i = b0 + lane;
+      float m = 0.f;
+      if (i < r1) {
+        const float z = (gmax - row[i]) * inv_temperature;
+        m = z < thr_z ? __expf(-z) : 0.f;
+      }
+      float sc = m;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float v = __shfl_up_sync(0xffffffffu, sc, o);
+        if (lane >= o) sc += v;
+      }
+      const uint32_t hit = __ballot_sync(0xffffffffu, m > 0.f && acc + sc > target);
+      if (hit) {
+        pick = b0 + __ffs(hit) - 1;
+      } else {
+        const uint32_t kept = __ballot_sync(0xffffffffu, m > 0.f);
+        if (kept && lane == 0) chosen = b0 + 31 - __clz(kept);  // rounding fallback: last kept entry seen
+        acc += __shfl_sync(0xffffffffu, sc, 31);
+      }
+    }
+    if (pick >= 0 && lane == 0) chosen = pick;
   }
   __syncthreads();
   if (tid == 0) out[blockIdx.x] = chosen;

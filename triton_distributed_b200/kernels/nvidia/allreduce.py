@@ -151,6 +151,9 @@ def all_reduce_rmsnorm(x: torch.Tensor, residual: torch.Tensor | None, gamma: to
     """
     rows, hidden = x.shape
     es = x.element_size()
+    if method is None and x.numel() * es <= 512 * 1024:
+        # latency-bound: one push, one meeting point, one pass (a two-shot costs two meetings and three passes)
+        method = AllReduceMethod.OneShot
     native = _resolve(method, x.numel() * es, ctx)
     if native in (1, 3) and rows % ctx.world_size != 0:
         native = 0 if native == 1 else 2  # row ownership needs rows divisible by the world size
