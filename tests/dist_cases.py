@@ -183,11 +183,13 @@ def allreduce_fused_rmsnorm():
     ctx.finalize()
 
 
-def _ag_gemm_case(Mr, N, K, dtype, iters=3, straggler=False):
+def _ag_gemm_case(Mr, N, K, dtype, iters=3, straggler=False, method=None):
     rank, world = _rank_world()
     torch.manual_seed(1234 + rank)
     b = (torch.randn(N, K, device="cuda", dtype=dtype) * 0.05)
     ctx = create_ag_gemm_context(torch.empty(Mr, K, device="cuda", dtype=dtype), b, rank, world, max_M=Mr * world)
+    if method is not None:
+        ctx.all_gather_method = method
     for it in range(iters):
         a = torch.randn(Mr, K, device="cuda", dtype=dtype)
         full = torch.empty(Mr * world, K, device="cuda", dtype=dtype)
@@ -207,6 +209,9 @@ def ag_gemm_shapes():
     _ag_gemm_case(999, 776, 520, torch.bfloat16)   # ragged: blocks straddle ranks
     _ag_gemm_case(64, 512, 1024, torch.float16)
     _ag_gemm_case(1024, 7168, 8192, torch.bfloat16, iters=2)
+    _ag_gemm_case(512, 1024, 2048, torch.bfloat16, method="sm_pull_fused")
+    _ag_gemm_case(999, 776, 520, torch.bfloat16, iters=4, method="sm_pull_fused")
+    _ag_gemm_case(999, 776, 520, torch.bfloat16, iters=5, method="sm_push_fused")  # odd and even parities reused
 
 
 @case

@@ -76,14 +76,16 @@ def test_grid_barrier_rounds(dist1):
     heap.check_status()
 
 
+@pytest.mark.parametrize("method", ["sm_push_fused", "sm_pull_fused"])
 @pytest.mark.parametrize("Mr,N,K", [(256, 512, 256), (1000, 776, 520), (64, 256, 128)])
-def test_ag_gemm_world1(dist1, Mr, N, K):
+def test_ag_gemm_world1(dist1, Mr, N, K, method):
     from triton_distributed_b200.kernels.nvidia import ag_gemm, create_ag_gemm_context
     from triton_distributed_b200.runtime.heap import get_heap
     torch.manual_seed(0)
     a = torch.randn(Mr, K, device="cuda", dtype=torch.bfloat16)
     b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
     ctx = create_ag_gemm_context(a, b, 0, 1, max_M=1024)
+    ctx.all_gather_method = method
     for it in range(3):  # epochs / parity buffers across calls
         a2 = a * (it + 1)
         c = ag_gemm(a2, b, ctx)

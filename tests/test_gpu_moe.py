@@ -40,7 +40,8 @@ def test_moe_sort_matches_reference(T, topk, E, bm, segments):
     assert int(plan.status[0]) == 0
 
 
-@pytest.mark.parametrize("T,topk,E,N,K", [(64, 2, 4, 128, 64), (300, 4, 16, 384, 512), (1024, 8, 32, 200, 1032)])
+@pytest.mark.parametrize("T,topk,E,N,K", [(64, 2, 4, 128, 64), (300, 4, 16, 384, 512), (1024, 8, 32, 200, 1032),
+                                             (256, 4, 8, 512, 256), (200, 2, 4, 1000, 192)])  # the last two: 256-wide tiles
 def test_grouped_gemm_matches_per_expert_matmul(T, topk, E, N, K):
     from triton_distributed_b200 import ref
     from triton_distributed_b200.kernels.nvidia import grouped_gemm

@@ -27,6 +27,7 @@ def main() -> None:
     ap.add_argument("--op", choices=OPS, required=True)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--m", type=int, default=4096, help="rows of the ag_gemm / gemm_rs problem")
     args = ap.parse_args()
     os.environ.setdefault("RANK", "0"), os.environ.setdefault("LOCAL_RANK", "0"), os.environ.setdefault("WORLD_SIZE", "1")
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1"), os.environ.setdefault("MASTER_PORT", "29571")
@@ -37,14 +38,14 @@ def main() -> None:
     dev = "cuda"
     info = {}
     if args.op == "ag_gemm":
-        M, N, K_ = 4096, 3584, 8192
+        M, N, K_ = args.m, 3584, 8192
         a = torch.randn(M, K_, device=dev, dtype=dt)
         b = torch.randn(N, K_, device=dev, dtype=dt) * 0.02
         ctx = K.create_ag_gemm_context(a, b, 0, 1, M)
         fn = lambda: K.ag_gemm(a, b, ctx)
         info = {"flops": 2.0 * M * N * K_}
     elif args.op == "gemm_rs":
-        M, N, K_ = 4096, 8192, 3584
+        M, N, K_ = args.m, 8192, 3584
         a = torch.randn(M, K_, device=dev, dtype=dt)
         b = torch.randn(N, K_, device=dev, dtype=dt) * 0.02
         ctx = K.create_gemm_rs_context(M, N, 0, 1, 1, dt)

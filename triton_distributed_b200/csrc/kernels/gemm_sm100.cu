@@ -10,14 +10,18 @@
 //   warp 0      TMA producer: 128x64 A tile + 256x64 B tile per stage, 128-byte swizzle, 4 stages
 //   warp 1      one elected thread issues tcgen05.mma (M128 N256 K16, bf16/f16 -> f32) into TMEM;
 //               two 256-column accumulators so the epilogue of tile i overlaps the mainloop of i+1
-//   warps 2-3   AG mode: communication warps. They copy this rank's shard into the symmetric
-//               gather buffer, publish it, and pull the peers' shards over NVLink with 16-byte
-//               loads in the order in which the tile schedule needs them; arrival is tracked per
-//               128-row block and the producer warp waits (bounded) on that block's flag before
-//               its first TMA load of the block. TMA only ever reads this GPU's own memory.
+//   warps 2-3   AG mode: communication warps. Push gather (default): they store this rank's shard into every
+//               peer's gather buffer, in the order in which the peers' tile schedules need it, and add the rows
+//               to the destination's per-128-row-block counters. Pull gather: they copy the local shard,
+//               publish it and pull the peers' shards with 16-byte loads. Either way the producer warp waits
+//               (bounded) on a block's arrival before its first TMA load of the block, and TMA only ever
+//               reads this GPU's own memory.
+//               RS mode: warp 2 is the signalling warp. It waits for the epilogue warps of each tile, issues
+//               the system-scope fence and bumps the owners' row counters, so the epilogue never waits for
+//               its remote stores to be acknowledged.
 //   warps 4-7   epilogue: tcgen05.ld -> convert -> swizzled smem staging -> 128-byte row segments.
 //               RS mode stores each row into the owner rank's slot [src][row][col] through its peer
-//               mapping and bumps the owner's per-(src, block) row counter with a release.
+//               mapping; the signalling warp then bumps the owner's per-(src, block) row counter.
 //   RS mode ends with a reduce phase in which all threads sum the `world` slots of this rank's
 //   rows (fp32) as the blocks complete.
 //
@@ -66,6 +70,12 @@ struct GemmParams {
   uint32_t* blk_flag;    // local u32[tiles_m cap]: == epoch once the block is complete
   uint32_t* sync;        // local u32[4]: [0] epoch, [1] done-CTA counter, [2] local-chunk counter
   int Mr;                // rows per rank (M / world)
+  // push variant of the gather: every rank stores its shard into all peers' buffers and adds the rows it
+  // delivered to the destination's per-block counters; a block is complete at base + rows_in_block
+  int push;
+  uint32_t* ag_cnt;      // symmetric u32[2][nblk_cap]: rows landed per 128-row block, by epoch parity (only ever grows)
+  uint32_t* ag_base;     // local u32[2][nblk_cap]: counter values before this call
+  int nblk_cap;
   // ---- RS ----
   void* slots[2];        // symmetric [world][Mr_cap][N], double-buffered by epoch parity
   uint32_t* rs_cnt;      // symmetric u32[world][rs_blocks]: rows received from src for block j
@@ -144,6 +154,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile uint32_t* bcast = tmem_slot + 2;
+  uint32_t* epi_done = tmem_slot + 3;  // RS: epilogue-warp completions, consumed by the signalling warp
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -169,6 +180,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
       mbar_init(tempty_bar + i, 4 * kCtas);  // pair: the epilogue warps of both CTAs release the leader's accumulator
     }
     *abort_flag = 0;
+    *epi_done = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA0);
     tma_prefetch_desc(&tmB);
@@ -194,7 +206,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
         tile_coords(p, t, m_blk, n_blk);
         if (kPair) m_blk = 2 * m_blk + static_cast<int>(cta_rank);
         if (kMode == kAG && m_blk < m_blocks) {
-          ok = wait_flag<WaitCmp::EQ, false>(ctx, p.blk_flag + m_blk, epoch, m_blk, __LINE__);
+          if (p.push) {
+            const uint32_t rows = static_cast<uint32_t>(min(kBM, p.M - m_blk * kBM));
+            const int idx = par * p.nblk_cap + m_blk;
+            ok = wait_flag<WaitCmp::GE, true>(ctx, p.ag_cnt + idx, p.ag_base[idx] + rows, m_blk, __LINE__);
+          } else {
+            ok = wait_flag<WaitCmp::EQ, false>(ctx, p.blk_flag + m_blk, epoch, m_blk, __LINE__);
+          }
           if (!ok) { *abort_flag = 1; break; }
           fence_proxy_async();
         }
@@ -258,6 +276,45 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
     }
     __syncwarp();
   } else if (warp < 4) {
+    // ------------------------------------------------------------------ signalling warp (RS)
+    if (kMode == kRS && warp == 2) {
+      // For every tile of this CTA, in issue order: wait until the four epilogue warps have stored their rows into
+      // the owners' slots, make those stores visible system-wide, and add the delivered rows to each owner's counter
+      // for (this source, 128-row block). The fence can take microseconds on a loaded link; here it delays nobody.
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = unit; t < total_tiles && ok; t += num_units, ++it) {
+        int m_blk, n_blk;
+        tile_coords(p, t, m_blk, n_blk);
+        if (kPair) m_blk = 2 * m_blk + static_cast<int>(cta_rank);
+        const uint32_t want = 4u * (it + 1u);
+        uint64_t t0 = 0;
+        uint32_t spins = 0;
+        while (true) {
+          uint32_t seen;
+          asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(seen) : "r"(smem_u32(epi_done)) : "memory");
+          if (seen >= want) break;
+          __nanosleep(64);
+          if ((++spins & 63u) == 0u) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            if (*abort_flag != 0u || now - t0 > pipe_timeout) { ok = false; break; }
+          }
+        }
+        if (!ok) break;
+        const int r_lo = m_blk * kBM, r_hi = min(r_lo + kBM, p.M);
+        if (r_lo < r_hi) {
+          const int o_lo = r_lo / p.Mr, o_hi = (r_hi - 1) / p.Mr;
+          for (int o = o_lo + lane; o <= o_hi; o += 32) {
+            fence_acq_rel_sys();
+            const int s0 = max(r_lo, o * p.Mr), s1 = min(r_hi, (o + 1) * p.Mr);
+            const int j = m_blk - (o * p.Mr) / kBM;
+            uint32_t* cnt = p.rs_cnt + ctx.rank * p.rs_blocks + j;
+            red_add_release_sys(symm_at(ctx, cnt, o), static_cast<uint32_t>(s1 - s0));
+          }
+        }
+      }
+    }
     // ------------------------------------------------------------------ communication warps (AG)
     if (kMode == kAG) {
       const int ct = threadIdx.x - 64;
@@ -265,6 +322,35 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
       uint8_t* buf = static_cast<uint8_t*>(p.ag_buf[par]);
       const int nch = (p.Mr + kCommRows - 1) / kCommRows;  // chunks per shard
       const int total_chunks = nch * ctx.world;            // local shard first, then peers in ring order
+      if (p.push) {
+        // Push: step s sends this rank's shard to rank - s, the peer whose tile schedule needs it s steps from now
+        // (step 0 is the local copy). Stores are posted, so the gather runs at link speed however small M is.
+        uint32_t* cnt = p.ag_cnt + par * p.nblk_cap;
+        for (int g = blockIdx.x; g < total_chunks; g += gridDim.x) {
+          const int step = g / nch;
+          const int c = g - step * nch;
+          int dst = ctx.rank - step;
+          if (dst < 0) dst += ctx.world;
+          const int r0 = c * kCommRows;
+          const int nrows = min(kCommRows, p.Mr - r0);
+          uint8_t* to = buf + (static_cast<size_t>(ctx.rank) * p.Mr + r0) * row_bytes;
+          if (step != 0) to = symm_at(ctx, to, dst);
+          comm_copy(to, static_cast<const uint8_t*>(p.a_local) + static_cast<size_t>(r0) * row_bytes, nrows * row_bytes, ct);
+          if (step == 0) fence_proxy_async();
+          comm_bar();
+          if (ct == 0) {
+            fence_acq_rel_sys();
+            int r = ctx.rank * p.Mr + r0;
+            const int end = r + nrows;
+            while (r < end) {
+              const int b = r / kBM;
+              const int bend = min(end, (b + 1) * kBM);
+              red_add_release_sys(symm_at(ctx, cnt + b, dst), static_cast<uint32_t>(bend - r));
+              r = bend;
+            }
+          }
+        }
+      } else
       for (int g = blockIdx.x; g < total_chunks; g += gridDim.x) {
         const int step = g / nch;
         const int c = g - step * nch;
@@ -373,24 +459,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
         if (kPair && !leader) mbar_arrive_cluster(mapa_u32(tempty_bar + acc, 0));
         else mbar_arrive(tempty_bar + acc);
       }
-      if (kMode == kRS) {
-        // tell each owner how many of its rows this warp just delivered for this column block
-        const int r_lo = row_base, r_hi = min(row_base + 32, p.M);
-        if (r_lo < r_hi) {
-          const int o_lo = r_lo / p.Mr, o_hi = (r_hi - 1) / p.Mr;
-          const int o = o_lo + lane;
-          fence_acq_rel_sys();
-          if (o <= o_hi) {
-            const int s0 = max(r_lo, o * p.Mr), s1 = min(r_hi, (o + 1) * p.Mr);
-            const int j = m_blk - (o * p.Mr) / kBM;
-            uint32_t* cnt = p.rs_cnt + ctx.rank * p.rs_blocks + j;
-            red_add_release_sys(symm_at(ctx, cnt, o), static_cast<uint32_t>(s1 - s0));
-          }
-        }
+      if (kMode == kRS && lane == 0) {
+        // the stores above are ordered before this release by the __syncwarp; the signalling warp fences and tells
+        // the owners, so that no epilogue warp ever waits for its remote stores to be acknowledged
+        asm volatile("red.release.cta.shared::cta.add.u32 [%0], 1;" ::"r"(smem_u32(epi_done)) : "memory");
       }
     }
   }
-
   // ---------------------------------------------------------------------- RS reduce phase
   __syncthreads();
   bool failed = *abort_flag != 0u;
@@ -402,8 +477,12 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
     // One work item = one row of this rank's segment; a thread owns up to four 16-byte vectors of the row and issues
     // all of their loads over all slots (4 x world) before it adds anything, so the phase runs at HBM speed instead
     // of one load latency per vector.
+    // A CTA owns a contiguous run of rows, so it waits for one or two 128-row blocks in all.
     int ready_blk = -1;
-    for (int lrow = blockIdx.x; lrow < p.Mr && !failed; lrow += gridDim.x) {
+    const int rows_per_cta = (p.Mr + gridDim.x - 1) / gridDim.x;
+    const int row_begin = min(p.Mr, static_cast<int>(blockIdx.x) * rows_per_cta);
+    const int row_end = min(p.Mr, row_begin + rows_per_cta);
+    for (int lrow = row_begin; lrow < row_end && !failed; ++lrow) {
       const int j = (seg0 + lrow) / kBM - first_blk;
       if (j > ready_blk) {
         bool ok = true;
@@ -474,6 +553,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
       __threadfence();
       if (atomicAdd(p.sync + 1, 1u) == gridDim.x - 1) {
         p.sync[1] = 0;
+        if (kMode == kAG && p.push) {
+          for (int b = 0; b < m_blocks; ++b)
+            p.ag_base[par * p.nblk_cap + b] += static_cast<uint32_t>(min(kBM, p.M - b * kBM));
+        }
         if (kMode == kRS) {
           // every rank delivered its rows of this call: advance the counter bases
           const int seg0 = ctx.rank * p.Mr, first_blk = seg0 / kBM, last_blk = (seg0 + p.Mr - 1) / kBM;
@@ -592,9 +675,12 @@ B200_API int b200_gemm(const void* A, const void* B, void* C, int M, int N, int 
 // AG-GEMM. a_local [Mr, K] is this rank's shard; ag_buf0/1 are the two symmetric gather buffers
 // [world * Mr, K] (rows of rank s at s * Mr); B is [N, K]; C is [world * Mr, N].
 // ready: symmetric u32[world]; blk_cnt/blk_flag: local u32[>= tiles_m]; sync: local u32[4]; all zero-initialised once.
+// push != 0 selects the push gather: ag_cnt symmetric u32[2 * nblk_cap], ag_base local u32[2 * nblk_cap] (zero-initialised
+// once); otherwise the communication warps pull and ag_cnt / ag_base are not touched.
 B200_API int b200_ag_gemm(const void* symm_ctx, const void* a_local, void* ag_buf0, void* ag_buf1, const void* B, void* C,
                           int Mr, int N, int K, int ldb, int ldc, int dtype, uint32_t* ready, uint32_t* blk_cnt,
-                          uint32_t* blk_flag, uint32_t* sync, int group_m, int max_ctas, void* stream) {
+                          uint32_t* blk_flag, uint32_t* sync, int group_m, int max_ctas, int push, uint32_t* ag_cnt,
+                          uint32_t* ag_base, int nblk_cap, void* stream) {
   SymmCtx ctx;
   memcpy(&ctx, symm_ctx, sizeof(ctx));
   const int M = Mr * ctx.world;
@@ -612,6 +698,14 @@ B200_API int b200_ag_gemm(const void* symm_ctx, const void* a_local, void* ag_bu
   p.blk_flag = blk_flag;
   p.sync = sync;
   p.Mr = Mr;
+  p.push = push;
+  p.ag_cnt = ag_cnt;
+  p.ag_base = ag_base;
+  p.nblk_cap = nblk_cap;
+  if (push) {
+    B200_REQUIRE(ag_cnt != nullptr && ag_base != nullptr, "the push gather needs its block counters");
+    B200_REQUIRE((M + kBM - 1) / kBM <= nblk_cap, "M (%d) needs more than %d block counters", M, nblk_cap);
+  }
   const bool pair = use_pair(M);
   set_tiles(p, pair, ctx.rank * Mr);
   B200_REQUIRE((reinterpret_cast<uint64_t>(a_local) & 15u) == 0, "a_local must be 16-byte aligned");

@@ -10,9 +10,10 @@
 //          reduces the slots of all ranks (moe_reduce_rs_rowise, kernels/nvidia/moe_reduce_rs.py:379-601, 816-926)
 //
 // Rows of a tile are scattered tokens, so A cannot be one TMA box: four producer warps gather it with 16-byte
-// cp.async copies, one row per thread, writing the same 128-byte XOR swizzle that TMA would produce, and hand
-// each stage to the MMA thread after cp.async.wait_group + fence.proxy.async. W[e] arrives by TMA from a 3-D
-// map [E, N, K], so a tile at the edge of N never reads the next expert. 384 threads:
+// cp.async copies (eight lanes per 128-byte row segment), writing the same 128-byte XOR swizzle that TMA would
+// produce; cp.async.mbarrier.arrive makes each stage's barrier complete when the copies land, and the MMA thread
+// issues fence.proxy.async before it reads the stage. W[e] arrives by TMA from a 3-D map [E, N, K], so a tile at
+// the edge of N never reads the next expert. 384 threads:
 //   warp 0 W producer | warp 1 MMA issuer | warps 2-3 communication (AG) | warps 4-7 epilogue | warps 8-11 A gather
 // Tile metadata (sorted pair ids, expert per tile, source-rank range per tile, issue order, tile count) is read
 // from device memory, so the grid is sized for the worst case and no host synchronisation is needed.
@@ -20,22 +21,30 @@
 #include "b200/primitives.cuh"
 #include "b200/tcgen05.cuh"
 
+#include <cstdlib>
 #include <cstring>
 
 namespace b200 {
 
-constexpr int kGM = 128, kGN = 128, kGK = 64;
-constexpr int kGStages = 6;
-constexpr int kGABytes = kGM * kGK * 2, kGWBytes = kGN * kGK * 2, kGStageBytes = kGABytes + kGWBytes;
+constexpr int kGM = 128, kGK = 64;
+constexpr int kGABytes = kGM * kGK * 2;
 constexpr int kGEpiBytes = 4 * 32 * 128;
-constexpr int kGSmem = kGStages * kGStageBytes + kGEpiBytes + 1024 + 512;
 constexpr int kGThreads = 384;
-constexpr int kGLag = 2;  // stages between issuing a gather and publishing it
+
+// Tile width: 128 columns (6 stages of 32 KB) or 256 columns (4 stages of 48 KB). The wide tile gathers A once per
+// 256 output columns and needs 96 instead of 128 bytes of shared-memory fill per tensor-core clock.
+template <int kBN>
+struct GTile {
+  static constexpr int kStages = kBN == 256 ? 4 : 6;
+  static constexpr int kWBytes = kBN * kGK * 2;
+  static constexpr int kStageBytes = kGABytes + kWBytes;
+  static constexpr int kSmem = kStages * kStageBytes + kGEpiBytes + 1024 + 512;
+};
 
 enum GroupedMode : int { kGPlain = 0, kGAG = 1, kGRS = 2 };
 
 struct GroupedParams {
-  int N, K, n_pairs, a_div, lda, ldo, tiles_n, bf16, max_tiles;
+  int N, K, n_pairs, a_div, lda, ldo, tiles_n, bf16, max_tiles, bn;
   const void* A;
   const int32_t* sorted_ids;
   const int32_t* tile_expert;
@@ -63,6 +72,9 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int by
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit_g() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 template <int N>
 __device__ __forceinline__ void cp_async_wait_g() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void gcomm_bar() { asm volatile("bar.sync 1, 64;" ::: "memory"); }
@@ -73,9 +85,10 @@ __device__ __forceinline__ int work_tile(const GroupedParams& p, int w, int& n_b
   return p.tile_order ? p.tile_order[slot] : slot;
 }
 
-template <int kMode>
+template <int kMode, int kGN>
 __global__ void __launch_bounds__(kGThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams p, const SymmCtx ctx) {
+  constexpr int kGStages = GTile<kGN>::kStages, kGWBytes = GTile<kGN>::kWBytes, kGStageBytes = GTile<kGN>::kStageBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_smem = smem + kGStages * kGStageBytes;
@@ -111,7 +124,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
     mbar_fence_init();
     tma_prefetch_desc(&tmW);
   }
-  if (warp == 2) tmem_alloc(tmem_slot, 256);
+  if (warp == 2) tmem_alloc(tmem_slot, 2 * kGN);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -148,6 +161,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
         const uint32_t d_tmem = tmem_base + acc * kGN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(full_bar + stage, phase, abort_flag, pipe_timeout)) { ok = false; break; }
+          fence_view_async_shared();  // the gathered A rows were written through the generic proxy (cp.async)
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * kGStageBytes);
           const uint64_t da = umma_desc_sw128_kmajor(sa);
@@ -265,50 +279,50 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
       if (lane == 0) mbar_arrive(tempty_bar + acc);
     }
   } else {
-    // ------------------------------------------------------------------ A gather producers (one row per thread)
-    const int row = threadIdx.x - 256;
-    uint32_t stage = 0, phase = 0, arr_stage = 0;
-    int issued = 0, arrived = 0;
+    // ------------------------------------------------------------------ A gather producers
+    // Eight consecutive lanes copy one 128-byte row segment (a whole line per row, four rows per warp instruction);
+    // thread t owns 16-byte chunk t & 7 of rows (t >> 3) + 16 i, i = 0..7.
+    const int t = threadIdx.x - 256;
+    const int chunk = t & 7, rbase = t >> 3;
+    const uint32_t sw_off = static_cast<uint32_t>(rbase * 128 + ((chunk ^ (rbase & 7)) * 16));
+    uint32_t stage = 0, phase = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
       int n_blk;
       const int tile = work_tile(p, w, n_blk);
-      const int pair = p.sorted_ids[tile * kGM + row];
-      const bool valid = pair < p.n_pairs;
-      const int src_row = valid ? pair / p.a_div : 0;
-      if (kMode == kGAG && valid) {
-        ok = wait_flag<WaitCmp::EQ, false>(ctx, p.rank_flag + src_row / p.Tr, epoch, src_row / p.Tr, __LINE__);
-        if (!ok) *abort_flag = 1;
+      const uint8_t* rp[8];
+      int last_src = -1;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int pair = p.sorted_ids[tile * kGM + rbase + 16 * i];
+        const bool valid = pair < p.n_pairs;
+        const int src_row = valid ? pair / p.a_div : 0;
+        if (kMode == kGAG && valid && ok) {
+          const int src = src_row / p.Tr;
+          if (src != last_src) {
+            ok = wait_flag<WaitCmp::EQ, false>(ctx, p.rank_flag + src, epoch, src, __LINE__);
+            last_src = src;
+          }
+        }
+        rp[i] = valid ? a_base + (static_cast<size_t>(src_row) * p.lda + chunk * 8) * 2 : nullptr;
       }
-      const uint8_t* rp = a_base + static_cast<size_t>(src_row) * p.lda * 2;
+      if (!ok) *abort_flag = 1;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
         if (!mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, pipe_timeout)) { ok = false; break; }
-        const uint32_t sa = smem_u32(smem + stage * kGStageBytes) + row * 128;
+        const uint32_t sa = smem_u32(smem + stage * kGStageBytes) + sw_off;
+        const int col = kb * kGK + chunk * 8;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const int col = kb * kGK + c * 8;
-          const bool in = valid && col < p.K;
-          cp_async16(sa + ((c ^ (row & 7)) * 16), in ? rp + static_cast<size_t>(col) * 2 : a_base, in ? 16 : 0);
+        for (int i = 0; i < 8; ++i) {
+          const bool in = rp[i] != nullptr && col < p.K;
+          cp_async16(sa + i * (16 * 128), in ? rp[i] + static_cast<size_t>(kb) * (kGK * 2) : a_base, in ? 16 : 0);
         }
-        cp_async_commit_g();
-        ++issued;
+        // the stage's barrier receives this thread's arrival when the copies above have landed: the producer never
+        // blocks on its own copies, so every free stage has a gather in flight
+        cp_async_arrive_noinc(full_bar + stage);
         if (++stage == kGStages) { stage = 0; phase ^= 1; }
-        if (issued - arrived > kGLag) {
-          cp_async_wait_g<kGLag>();
-          fence_view_async_shared();
-          mbar_arrive(full_bar + arr_stage);
-          ++arrived;
-          if (++arr_stage == kGStages) arr_stage = 0;
-        }
       }
     }
-    cp_async_wait_g<0>();
-    fence_view_async_shared();
-    while (arrived < issued) {
-      mbar_arrive(full_bar + arr_stage);
-      ++arrived;
-      if (++arr_stage == kGStages) arr_stage = 0;
-    }
+    cp_async_wait_g<0>();  // nothing of this thread is in flight when the CTA's shared memory goes away
   }
   // (continues below: RS phases and teardown)
 
@@ -333,14 +347,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
           uint8_t* rdst = symm_at(ctx, dst, owner);
           for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
             float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            for (int k = 0; k < p.topk; ++k) {
-              const uint4 x = ld_v4_relaxed_sys(out + ((static_cast<size_t>(t) * p.topk + k) * p.ldo + v * 8) * 2);
-              const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+            const uint8_t* src = out + (static_cast<size_t>(t) * p.topk * p.ldo + v * 8) * 2;
+            for (int k0 = 0; k0 < p.topk; k0 += 4) {  // four copies in flight before the first add
+              uint4 x[4];
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const float2 f = p.bf16 ? unpack_bf16x2(xs[q]) : unpack_f16x2(xs[q]);
-                acc[2 * q] += f.x;
-                acc[2 * q + 1] += f.y;
+              for (int u = 0; u < 4; ++u)
+                x[u] = k0 + u < p.topk ? ld_v4_relaxed_sys(src + static_cast<size_t>(k0 + u) * p.ldo * 2) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const uint32_t xs[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const float2 f = p.bf16 ? unpack_bf16x2(xs[q]) : unpack_f16x2(xs[q]);
+                  acc[2 * q] += f.x;
+                  acc[2 * q + 1] += f.y;
+                }
               }
             }
             uint4 o;
@@ -366,9 +387,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
         for (int lrow = blockIdx.x; lrow < p.Tr; lrow += gridDim.x) {
           for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
             float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            for (int s = 0; s < ctx.world; ++s) {
-              const uint4 x = ld_v4_relaxed_sys(slots + ((static_cast<size_t>(s) * p.Tr_cap + lrow) * p.N + v * 8) * 2);
-              const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+            uint4 x[kMaxRanks];
+#pragma unroll
+            for (int s = 0; s < kMaxRanks; ++s)
+              x[s] = s < ctx.world ? ld_v4_relaxed_sys(slots + ((static_cast<size_t>(s) * p.Tr_cap + lrow) * p.N + v * 8) * 2)
+                                   : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int s = 0; s < kMaxRanks; ++s) {
+              const uint32_t xs[4] = {x[s].x, x[s].y, x[s].z, x[s].w};
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 const float2 f = p.bf16 ? unpack_bf16x2(xs[q]) : unpack_f16x2(xs[q]);
@@ -389,7 +415,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
   // ---------------------------------------------------------------------- teardown
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 2) tmem_dealloc(tmem_base, 256);
+  if (warp == 2) tmem_dealloc(tmem_base, 2 * kGN);
   if (threadIdx.x == 0) {
     if (*abort_flag != 0u) report_status(ctx, kStatusPipeTimeout, blockIdx.x, 0, 0, __LINE__);
     if (kMode != kGPlain) {
@@ -405,18 +431,36 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
   }
 }
 
-template <int kMode>
-static int launch_grouped(const CUtensorMap& tw, const GroupedParams& p, const SymmCtx& ctx, int grid, cudaStream_t stream) {
+template <int kMode, int kBN>
+static int launch_grouped_bn(const CUtensorMap& tw, const GroupedParams& p, const SymmCtx& ctx, int grid, cudaStream_t stream) {
   static bool configured[64] = {false};
   int dev = 0;
   B200_CHECK_CUDA(cudaGetDevice(&dev));
   if (!configured[dev & 63]) {
-    B200_CHECK_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGSmem));
+    B200_CHECK_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<kMode, kBN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GTile<kBN>::kSmem));
     configured[dev & 63] = true;
   }
-  grouped_gemm_kernel<kMode><<<grid, kGThreads, kGSmem, stream>>>(tw, p, ctx);
+  grouped_gemm_kernel<kMode, kBN><<<grid, kGThreads, GTile<kBN>::kSmem, stream>>>(tw, p, ctx);
   B200_CHECK_CUDA(cudaGetLastError());
   return kOk;
+}
+template <int kMode>
+static int launch_grouped(const CUtensorMap& tw, const GroupedParams& p, const SymmCtx& ctx, int grid, cudaStream_t stream) {
+  return p.bn == 256 ? launch_grouped_bn<kMode, 256>(tw, p, ctx, grid, stream)
+                     : launch_grouped_bn<kMode, 128>(tw, p, ctx, grid, stream);
+}
+
+// Wide tiles when they waste no more columns than narrow ones would (N = 384 stays on 128-column tiles).
+static int pick_bn(int N) {
+  static int forced = -1;
+  if (forced < 0) {
+    const char* e = getenv("B200DIST_GROUPED_BN");
+    forced = e ? atoi(e) : 0;
+  }
+  if (forced == 128 || forced == 256) return forced;
+  const int waste256 = (N + 255) / 256 * 256 - N, waste128 = (N + 127) / 128 * 128 - N;
+  return (N >= 256 && waste256 <= waste128) ? 256 : 128;
 }
 
 static int fill_grouped(GroupedParams& p, CUtensorMap* tw, const void* W, int E, int N, int K, int n_pairs, int a_div,
@@ -426,12 +470,13 @@ static int fill_grouped(GroupedParams& p, CUtensorMap* tw, const void* W, int E,
   B200_REQUIRE(K % 8 == 0 && N % 8 == 0, "K (%d) and N (%d) must be multiples of 8", K, N);
   memset(&p, 0, sizeof(p));
   p.N = N; p.K = K; p.n_pairs = n_pairs; p.a_div = a_div; p.ldo = ldo;
-  p.tiles_n = (N + kGN - 1) / kGN;
+  p.bn = pick_bn(N);
+  p.tiles_n = (N + p.bn - 1) / p.bn;
   p.bf16 = dtype == kBF16;
   p.max_tiles = max_tiles;
   p.sorted_ids = sorted_ids; p.tile_expert = tile_expert; p.tile_order = tile_order; p.totals = totals;
   p.out = out; p.row_scale = row_scale;
-  return make_tma_3d(tw, W, dtype, K, N, E, K, static_cast<uint64_t>(N) * K, kGK, kGN, 1, true);
+  return make_tma_3d(tw, W, dtype, K, N, E, K, static_cast<uint64_t>(N) * K, kGK, p.bn, 1, true);
 }
 
 }  // namespace b200

@@ -1,13 +1,15 @@
-// MoE routing metadata in one launch (plus one tiny launch for the tile order), with no host sync, no
-// allocation and no device-wide synchronise, so it can sit inside a CUDA graph.
+// MoE routing metadata without a host sync, an allocation or a device-wide synchronise, so it can sit inside a
+// CUDA graph. Four short launches (no kernel waits on another CTA, so nothing has to be co-resident):
 //
 //   moe_sort     stable sort of the (token, k) pairs by (segment, expert), every run padded to BLOCK_M rows:
 //                  segments == 1      pairs sorted by expert over all tokens (AG + grouped GEMM, EP dispatch);
 //                                     each tile also records the first / last source rank of its rows
 //                  segments == ranks  every source-rank block of tokens sorted on its own (grouped GEMM + RS)
-//                One warp owns one (segment, expert) group: it counts its matches with ballots, publishes the
-//                padded count, obtains its offset by looking back at the groups before it (bounded spin on
-//                epoch-tagged counts), then compacts its matches in order. Stable, deterministic, E <= 1024.
+//                1. count    one CTA per chunk of 512 pairs: shared-memory histogram -> counts[chunk][expert]
+//                2. prefix   per (segment, expert): exclusive prefix of the counts over the chunks, group totals
+//                3. offsets  one CTA: padded group sizes scanned into group offsets; tile table and pad rows
+//                4. scatter  one CTA per chunk: position = group offset + chunk prefix + rank inside the chunk
+//                Stable, deterministic, E <= 1024.
 //   moe_tile_order  counting sort of the tiles by arrival stage ((seg_end - rank - shift) mod world), stable.
 //
 // Role in the reference: csrc/lib/moe_utils.cu:60-353 (moe_ag_scatter_align_block_size, grid 1 or ranks CTAs,
@@ -21,11 +23,14 @@
 
 namespace b200 {
 
+constexpr int kChunk = 512;  // pairs per CTA in the count and scatter kernels
+
 struct MoeSortParams {
   const int32_t* ids;      // [n_pairs] expert of pair p = t * topk + k
   int n_pairs, topk, num_experts, block_m;
   int segments;            // 1 or number of ranks
   int pairs_per_segment;   // n_pairs / segments
+  int chunks_per_segment;  // ceil(pairs_per_segment / kChunk)
   int tokens_per_rank;     // for the source rank of a row (segments == 1 mode)
   int32_t* sorted_ids;     // [cap] pair index per sorted row, pad = n_pairs
   int32_t* tile_expert;    // [tile cap]
@@ -33,148 +38,134 @@ struct MoeSortParams {
   int32_t* tile_seg_end;   // [tile cap]
   int32_t* pair_pos;       // nullable [n_pairs]: sorted position of every pair (inverse of sorted_ids)
   int32_t* group_count;    // [segments * experts] matches per group (unpadded)
-  int32_t* totals;         // [2 + segments]: m_pad, num_tiles, tiles per segment
-  uint64_t* lookback;      // [segments * experts]: (epoch << 32) | padded count
-  uint32_t* sync;          // [2] epoch, done counter
-  uint64_t timeout_ns;
-  uint32_t* status;
+  int32_t* totals;         // [2 + segments]: m_pad, num_tiles, cumulative tiles per segment
+  int32_t* chunk_cnt;      // scratch [segments * chunks_per_segment][experts]: counts, then exclusive prefixes
+  int32_t* group_off;      // scratch [segments * experts]: first sorted row of every group
 };
 
-constexpr int kSortWarps = 16;
-
-__global__ void __launch_bounds__(kSortWarps * 32) moe_sort_kernel(const MoeSortParams p) {
-  const uint32_t epoch = epoch_begin(p.sync);
-  const int lane = threadIdx.x & 31;
-  const int g = blockIdx.x * kSortWarps + (threadIdx.x >> 5);
-  const int G = p.segments * p.num_experts;
-  SymmCtx c;
-  c.status = p.status;
-  c.timeout_ns = p.timeout_ns;
-  if (g < G) {
-    const int seg = g / p.num_experts, e = g - seg * p.num_experts;
-    const int p0 = seg * p.pairs_per_segment, p1 = p0 + p.pairs_per_segment;
-    // ---- count ----
-    // 16-byte loads, two chunks of 128 ids in flight per warp: the scan is latency-bound otherwise
-    const bool vec_ok = (p0 % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.ids) & 15u) == 0);
-    int count = 0;
-    int b0 = p0;
-    if (vec_ok) {
-      for (; b0 + 256 <= p1; b0 += 256) {
-        const int4 a = *reinterpret_cast<const int4*>(p.ids + b0 + lane * 4);
-        const int4 c = *reinterpret_cast<const int4*>(p.ids + b0 + 128 + lane * 4);
-        count += (a.x == e) + (a.y == e) + (a.z == e) + (a.w == e) + (c.x == e) + (c.y == e) + (c.z == e) + (c.w == e);
-      }
-    }
-    for (; b0 < p1; b0 += 32) {
-      const int i = b0 + lane;
-      count += (i < p1 && p.ids[i] == e) ? 1 : 0;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) count += __shfl_xor_sync(0xffffffffu, count, o);
-    const int padded = (count + p.block_m - 1) / p.block_m * p.block_m;
-    if (lane == 0) {
-      p.group_count[g] = count;
-      const uint64_t v = (static_cast<uint64_t>(epoch) << 32) | static_cast<uint32_t>(padded);
-      asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p.lookback + g), "l"(v) : "memory");
-    }
-    // ---- offset = sum of padded counts of the groups before this one ----
-    long long offset = 0;
-    bool ok = true;
-    for (int j = lane; j < g; j += 32) {
-      uint64_t v;
-      uint64_t t0 = 0;
-      uint32_t spins = 0;
-      while (true) {
-        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p.lookback + j) : "memory");
-        if (static_cast<uint32_t>(v >> 32) == epoch) break;
-        if ((++spins & 63u) == 0u) {
-          const uint64_t now = globaltimer_ns();
-          if (t0 == 0) t0 = now;
-          if (now - t0 > p.timeout_ns) {
-            report_status(c, kStatusWaitTimeout, j, epoch, static_cast<uint32_t>(v >> 32), __LINE__);
-            ok = false;
-            break;
-          }
-        }
-      }
-      offset += static_cast<uint32_t>(v);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) offset += __shfl_xor_sync(0xffffffffu, offset, o);
-    ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
-      // ---- compact in order ----
-      int written = 0;
-      const int first_tile = static_cast<int>(offset / p.block_m);
-      auto emit = [&](int i, int pos) {
-        p.sorted_ids[offset + pos] = i;
-        if (p.pair_pos) p.pair_pos[i] = static_cast<int32_t>(offset + pos);
-        // segment bounds of the tile this row falls into (only needed when sorting over all tokens)
-        if (p.segments == 1) {
-          const int src = (i / p.topk) / p.tokens_per_rank;
-          const int tile = first_tile + pos / p.block_m;
-          atomicMin(p.tile_seg_start + tile, src);
-          atomicMax(p.tile_seg_end + tile, src);
-        }
-      };
-      int b1 = p0;
-      if (vec_ok) {
-        // lane l holds ids [b1 + 4l, b1 + 4l + 4): order inside the chunk is (lane, j)
-        for (; b1 + 128 <= p1; b1 += 128) {
-          const int4 a = *reinterpret_cast<const int4*>(p.ids + b1 + lane * 4);
-          const int h0 = a.x == e, h1 = a.y == e, h2 = a.z == e, h3 = a.w == e;
-          const int mine_n = h0 + h1 + h2 + h3;
-          int incl = mine_n;
-#pragma unroll
-          for (int o = 1; o < 32; o <<= 1) {
-            const int v = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += v;
-          }
-          int pos = written + incl - mine_n;
-          const int i0 = b1 + lane * 4;
-          if (h0) emit(i0, pos++);
-          if (h1) emit(i0 + 1, pos++);
-          if (h2) emit(i0 + 2, pos++);
-          if (h3) emit(i0 + 3, pos++);
-          written += __shfl_sync(0xffffffffu, incl, 31);
-        }
-      }
-      for (; b1 < p1; b1 += 32) {
-        const int i = b1 + lane;
-        const bool hit = i < p1 && p.ids[i] == e;
-        const uint32_t m = __ballot_sync(0xffffffffu, hit);
-        if (hit) emit(i, written + __popc(m & ((1u << lane) - 1u)));
-        written += __popc(m);
-      }
-      for (int i = count + lane; i < padded; i += 32) p.sorted_ids[offset + i] = p.n_pairs;
-      for (int t = lane; t < padded / p.block_m; t += 32) {
-        p.tile_expert[first_tile + t] = e;
-        if (p.segments > 1) {
-          p.tile_seg_start[first_tile + t] = seg;
-          p.tile_seg_end[first_tile + t] = seg;
-        }
-      }
-      if (lane == 0) {
-        if (p.segments > 1 && e == p.num_experts - 1) {
-          // cumulative: tiles of segments 0..seg
-          p.totals[2 + seg] = static_cast<int>((offset + padded) / p.block_m);
-        }
-        if (g == G - 1) {
-          p.totals[0] = static_cast<int>(offset + padded);
-          p.totals[1] = static_cast<int>((offset + padded) / p.block_m);
-        }
-      }
-    }
+// ---- 1. per-chunk histogram
+__global__ void __launch_bounds__(kChunk) moe_count_kernel(const MoeSortParams p) {
+  extern __shared__ int32_t hist[];
+  for (int e = threadIdx.x; e < p.num_experts; e += kChunk) hist[e] = 0;
+  __syncthreads();
+  const int seg = blockIdx.x / p.chunks_per_segment, c = blockIdx.x - seg * p.chunks_per_segment;
+  const int i = c * kChunk + threadIdx.x;
+  if (i < p.pairs_per_segment) {
+    const int e = p.ids[seg * p.pairs_per_segment + i];
+    if (e >= 0 && e < p.num_experts) atomicAdd(hist + e, 1);
   }
   __syncthreads();
-  if (threadIdx.x == 0) epoch_end(p.sync, p.sync + 1, epoch, gridDim.x);
+  int32_t* out = p.chunk_cnt + static_cast<size_t>(blockIdx.x) * p.num_experts;
+  for (int e = threadIdx.x; e < p.num_experts; e += kChunk) out[e] = hist[e];
 }
 
-// tile_seg_start / tile_seg_end must hold +inf / -1 before the sort in segments == 1 mode.
-__global__ void moe_sort_init_kernel(int32_t* seg_start, int32_t* seg_end, int n) {
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-    seg_start[i] = 0x7fffffff;
-    seg_end[i] = -1;
+// ---- 2. exclusive prefix over the chunks of a segment, 32 experts per CTA; thread (tx, ty) owns expert tx and the
+//         ty-th contiguous slice of the chunks
+__global__ void __launch_bounds__(1024) moe_chunk_prefix_kernel(const MoeSortParams p) {
+  __shared__ int32_t part[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int e = blockIdx.x * 32 + tx, seg = blockIdx.y;
+  const int per = (p.chunks_per_segment + 31) / 32;
+  const int c0 = min(p.chunks_per_segment, ty * per), c1 = min(p.chunks_per_segment, c0 + per);
+  int32_t* col = p.chunk_cnt + static_cast<size_t>(seg) * p.chunks_per_segment * p.num_experts + e;
+  int sum = 0;
+  if (e < p.num_experts)
+    for (int c = c0; c < c1; ++c) sum += col[static_cast<size_t>(c) * p.num_experts];
+  part[ty][tx] = sum;
+  __syncthreads();
+  int before = 0, total = 0;
+  for (int k = 0; k < 32; ++k) {
+    const int v = part[k][tx];
+    if (k < ty) before += v;
+    total += v;
+  }
+  if (e < p.num_experts) {
+    int run = before;
+    for (int c = c0; c < c1; ++c) {
+      const int v = col[static_cast<size_t>(c) * p.num_experts];
+      col[static_cast<size_t>(c) * p.num_experts] = run;
+      run += v;
+    }
+    if (ty == 0) p.group_count[seg * p.num_experts + e] = total;
+  }
+}
+
+// ---- 3. group offsets (scan of the padded group sizes), tile table, pad rows, totals; one CTA
+__global__ void __launch_bounds__(1024) moe_offsets_kernel(const MoeSortParams p) {
+  __shared__ int32_t warp_tot[32];
+  __shared__ int32_t carry;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int G = p.segments * p.num_experts;
+  if (tid == 0) carry = 0;
+  __syncthreads();
+  for (int g0 = 0; g0 < G; g0 += 1024) {
+    const int g = g0 + tid;
+    const int count = g < G ? p.group_count[g] : 0;
+    const int padded = (count + p.block_m - 1) / p.block_m * p.block_m;
+    int incl = padded;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    int before = carry;
+    for (int w = 0; w < warp; ++w) before += warp_tot[w];
+    const int off = before + incl - padded;
+    if (g < G) p.group_off[g] = off;
+    __syncthreads();
+    if (tid == 1023) carry = off + padded;
+    __syncthreads();
+  }
+  // tiles and pad rows, one warp per group
+  for (int g = warp; g < G; g += 32) {
+    const int seg = g / p.num_experts, e = g - seg * p.num_experts;
+    const int count = p.group_count[g], off = p.group_off[g];
+    const int padded = (count + p.block_m - 1) / p.block_m * p.block_m;
+    for (int i = count + lane; i < padded; i += 32) p.sorted_ids[off + i] = p.n_pairs;
+    const int first_tile = off / p.block_m;
+    for (int t = lane; t < padded / p.block_m; t += 32) {
+      p.tile_expert[first_tile + t] = e;
+      p.tile_seg_start[first_tile + t] = p.segments > 1 ? seg : 0x7fffffff;  // min / max of the source ranks follow
+      p.tile_seg_end[first_tile + t] = p.segments > 1 ? seg : -1;            // in the scatter kernel
+    }
+    if (lane == 0 && e == p.num_experts - 1) p.totals[2 + seg] = (off + padded) / p.block_m;  // cumulative
+  }
+  if (tid == 0) {
+    p.totals[0] = carry;
+    p.totals[1] = carry / p.block_m;
+  }
+}
+
+// ---- 4. scatter: stable rank of every pair among the pairs of its expert in the chunk
+__global__ void __launch_bounds__(kChunk) moe_scatter_kernel(const MoeSortParams p) {
+  __shared__ int32_t sid[kChunk];
+  const int seg = blockIdx.x / p.chunks_per_segment, c = blockIdx.x - seg * p.chunks_per_segment;
+  const int i = c * kChunk + threadIdx.x;
+  const int pair = seg * p.pairs_per_segment + i;
+  int e = -1;
+  if (i < p.pairs_per_segment) {
+    e = p.ids[pair];
+    if (e < 0 || e >= p.num_experts) e = -1;
+  }
+  sid[threadIdx.x] = e;
+  __syncthreads();
+  int rank = 0;
+  const int tid = threadIdx.x;
+  const int warp_first = tid & ~31;
+  for (int j = 0; j < warp_first; ++j) rank += sid[j] == e ? 1 : 0;   // uniform over the warp: broadcast reads
+  const uint32_t same = __match_any_sync(0xffffffffu, e);              // skipped lanes (e == -1) only match each other
+  rank += __popc(same & ((1u << (tid & 31)) - 1u));
+  if (e < 0) return;
+  const int pos = p.group_off[seg * p.num_experts + e] + p.chunk_cnt[static_cast<size_t>(blockIdx.x) * p.num_experts + e] + rank;
+  p.sorted_ids[pos] = pair;
+  if (p.pair_pos) p.pair_pos[pair] = pos;
+  if (p.segments == 1) {
+    const int src = (pair / p.topk) / p.tokens_per_rank;
+    const int tile = pos / p.block_m;
+    atomicMin(p.tile_seg_start + tile, src);
+    atomicMax(p.tile_seg_end + tile, src);
   }
 }
 
@@ -223,31 +214,40 @@ B200_API long long b200_moe_sorted_capacity(int n_pairs, int num_experts, int bl
   return (static_cast<long long>(n_pairs) + groups * (block_m - 1) + block_m - 1) / block_m * block_m;
 }
 
+// Scratch (int32 elements) that b200_moe_sort needs for a problem of this size.
+B200_API long long b200_moe_sort_scratch_ints(int n_pairs, int num_experts, int segments) {
+  const long long pps = n_pairs / (segments > 0 ? segments : 1);
+  const long long chunks = (pps + kChunk - 1) / kChunk;
+  return (chunks * segments + 1) * num_experts + static_cast<long long>(segments) * num_experts;
+}
+
 // ids int32 [n_pairs]; outputs sized by b200_moe_sorted_capacity (rows) and capacity / block_m (tiles).
-// group_count int32 [segments * E]; totals int32 [2 + segments]; lookback u64 [segments * E] and sync u32 [2] are
-// zero-initialised once and owned by the caller (one pair per concurrent user). pair_pos (nullable) int32 [n_pairs].
+// group_count int32 [segments * E]; totals int32 [2 + segments]; scratch int32 [b200_moe_sort_scratch_ints(...)]
+// (no initialisation needed); pair_pos (nullable) int32 [n_pairs]. Ids outside [0, E) are skipped.
 B200_API int b200_moe_sort(const int32_t* ids, int n_pairs, int topk, int num_experts, int block_m, int segments,
                            int tokens_per_rank, int32_t* sorted_ids, int32_t* tile_expert, int32_t* tile_seg_start,
-                           int32_t* tile_seg_end, int32_t* group_count, int32_t* totals, uint64_t* lookback,
-                           uint32_t* sync, uint32_t* status, int32_t* pair_pos, void* stream) {
+                           int32_t* tile_seg_end, int32_t* group_count, int32_t* totals, int32_t* scratch,
+                           int32_t* pair_pos, void* stream) {
   B200_REQUIRE(num_experts >= 1 && num_experts <= 1024, "number of experts (%d) must be in [1, 1024]", num_experts);
   B200_REQUIRE(segments >= 1 && n_pairs % segments == 0, "pairs (%d) must divide into %d segments", n_pairs, segments);
   B200_REQUIRE(block_m >= 1 && topk >= 1 && tokens_per_rank >= 1, "bad block_m / topk / tokens_per_rank");
-  const int G = num_experts * segments;
-  const int ctas = (G + kSortWarps - 1) / kSortWarps;
-  B200_REQUIRE(ctas <= 2 * sm_count(), "too many (segment, expert) groups (%d) for a co-resident grid", G);
+  B200_REQUIRE(n_pairs >= 1, "no pairs to sort");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int tile_cap = static_cast<int>(b200_moe_sorted_capacity(n_pairs, num_experts, block_m, segments) / block_m);
-  if (segments == 1) moe_sort_init_kernel<<<(tile_cap + 255) / 256, 256, 0, s>>>(tile_seg_start, tile_seg_end, tile_cap);
   MoeSortParams p;
   memset(&p, 0, sizeof(p));
   p.ids = ids; p.n_pairs = n_pairs; p.topk = topk; p.num_experts = num_experts; p.block_m = block_m;
   p.segments = segments; p.pairs_per_segment = n_pairs / segments; p.tokens_per_rank = tokens_per_rank;
+  p.chunks_per_segment = (p.pairs_per_segment + kChunk - 1) / kChunk;
   p.sorted_ids = sorted_ids; p.tile_expert = tile_expert; p.tile_seg_start = tile_seg_start; p.tile_seg_end = tile_seg_end;
   p.pair_pos = pair_pos;
-  p.group_count = group_count; p.totals = totals; p.lookback = lookback; p.sync = sync;
-  p.timeout_ns = 2000000000ull; p.status = status;
-  moe_sort_kernel<<<ctas, kSortWarps * 32, 0, s>>>(p);
+  p.group_count = group_count; p.totals = totals;
+  p.chunk_cnt = scratch;
+  p.group_off = scratch + static_cast<size_t>(p.chunks_per_segment) * segments * num_experts;
+  const int chunks = p.chunks_per_segment * segments;
+  moe_count_kernel<<<chunks, kChunk, num_experts * sizeof(int32_t), s>>>(p);
+  moe_chunk_prefix_kernel<<<dim3((num_experts + 31) / 32, segments), 1024, 0, s>>>(p);
+  moe_offsets_kernel<<<1, 1024, 0, s>>>(p);
+  moe_scatter_kernel<<<chunks, kChunk, 0, s>>>(p);
   B200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }

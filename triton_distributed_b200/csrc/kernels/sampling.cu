@@ -152,30 +152,40 @@ __global__ void __launch_bounds__(kSampleThreads) top_p_sample_kernel(const floa
     thr_z = b == kSampleThreads - 1 ? INFINITY : (b + (sb + 1) * (1.f / 1024.f)) * (1.f / 32.f);
     __syncthreads();
   }
-  // draw in index order among the kept entries. Warp w owns the contiguous range [w * R, (w + 1) * R) and reads it
-  // lane-strided (coalesced); the warp that contains the target then walks its range 32 entries at a time.
+  // draw in index order among the kept entries. Warp w owns the contiguous range [w * R, (w + 1) * R), cut into 32
+  // sub-blocks of S entries; lane j ends up with the kept mass of sub-block j (coalesced reads, two sub-blocks = up
+  // to 2 * S / 32 loads in flight). The target is then located by warp, by sub-block, and by a walk of S / 32 steps.
   const int lane = tid & 31, warp = tid >> 5;
-  const int R = (V + 31) / 32;
+  const int S = ((V + 1023) / 1024 + 31) / 32 * 32;  // multiple of 32, 32 * 32 * S >= V
+  const int R = 32 * S;
   const int r0 = min(V, warp * R), r1 = min(V, r0 + R);
-  float mine = 0.f;
-  {
-    int i = r0 + lane;
-    for (; i + 7 * 32 < r1; i += 8 * 32) {
-      float v[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = row[i + u * 32];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const float z = (gmax - v[u]) * inv_temperature;
-        mine += z < thr_z ? __expf(-z) : 0.f;
+  auto kept_mass = [&](int i) -> float {
+    if (i >= r1) return 0.f;
+    const float z = (gmax - row[i]) * inv_temperature;
+    return z < thr_z ? __expf(-z) : 0.f;
+  };
+  float sub = 0.f;  // lane j: mass of sub-block j
+  for (int j = 0; j < 32; j += 2) {
+    float m0 = 0.f, m1 = 0.f;
+    const int b0 = r0 + j * S, b1 = b0 + S;
+    if (b0 < r1) {
+      for (int k = lane; k < S; k += 32) {
+        m0 += kept_mass(b0 + k);
+        m1 += kept_mass(b1 + k);
       }
     }
-    for (; i < r1; i += 32) {
-      const float z = (gmax - row[i]) * inv_temperature;
-      mine += z < thr_z ? __expf(-z) : 0.f;
-    }
+    m0 = warp_sum(m0);
+    m1 = warp_sum(m1);
+    if (lane == j) sub = m0;
+    if (lane == j + 1) sub = m1;
   }
-  mine = warp_sum(mine);
+  float sub_incl = sub;  // inclusive scan of the sub-block masses over the lanes
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float v = __shfl_up_sync(0xffffffffu, sub_incl, o);
+    if (lane >= o) sub_incl += v;
+  }
+  const float mine = __shfl_sync(0xffffffffu, sub_incl, 31);
   __syncthreads();
   if (lane == 0) hist[warp] = mine;
   __syncthreads();
@@ -190,15 +200,15 @@ __global__ void __launch_bounds__(kSampleThreads) top_p_sample_kernel(const floa
   const float my_incl = __shfl_sync(0xffffffffu, incl, warp);
   const float my_before = my_incl - mine;
   if (mine > 0.f && target >= my_before && target < my_incl) {
-    float acc = my_before;
-    int pick = -1;
-    for (int b0 = r0; b0 < r1 && pick < 0; b0 += 32) {
-      const int i = b0 + lane;
-      float m = 0.f;
-      if (i < r1) {
-        const float z = (gmax - row[i]) * inv_temperature;
-        m = z < thr_z ? __expf(-z) : 0.f;
-      }
+    // first sub-block whose inclusive mass passes the target (the last non-empty one if rounding leaves none)
+    const uint32_t pass = __ballot_sync(0xffffffffu, sub > 0.f && my_before + sub_incl > target);
+    const uint32_t nonempty = __ballot_sync(0xffffffffu, sub > 0.f);
+    const int jsel = pass ? __ffs(pass) - 1 : 31 - __clz(nonempty);
+    float acc = my_before + __shfl_sync(0xffffffffu, sub_incl - sub, jsel);
+    int pick = -1, last_kept = -1;
+    const int s0 = r0 + jsel * S, s1 = min(r1, s0 + S);
+    for (int b0 = s0; b0 < s1 && pick < 0; b0 += 32) {
+      const float m = kept_mass(b0 + lane);
       float sc = m;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -206,14 +216,12 @@ __global__ void __launch_bounds__(kSampleThreads) top_p_sample_kernel(const floa
         if (lane >= o) sc += v;
       }
       const uint32_t hit = __ballot_sync(0xffffffffu, m > 0.f && acc + sc > target);
-      if (hit) {
-        pick = b0 + __ffs(hit) - 1;
-      } else {
-        const uint32_t kept = __ballot_sync(0xffffffffu, m > 0.f);
-        if (kept && lane == 0) chosen = b0 + 31 - __clz(kept);  // rounding fallback: last kept entry seen
-        acc += __shfl_sync(0xffffffffu, sc, 31);
-      }
+      const uint32_t kept = __ballot_sync(0xffffffffu, m > 0.f);
+      if (hit) pick = b0 + __ffs(hit) - 1;
+      else if (kept) last_kept = b0 + 31 - __clz(kept);
+      acc += __shfl_sync(0xffffffffu, sc, 31);
     }
+    if (pick < 0) pick = last_kept;  // rounding: the last kept entry of the sub-block
     if (pick >= 0 && lane == 0) chosen = pick;
   }
   __syncthreads();

@@ -3,13 +3,19 @@
 API parity with ``python/triton_dist/kernels/nvidia/allgather_gemm.py`` (``create_ag_gemm_context``
 :489, ``ag_gemm`` :534, ``gemm_persistent`` :660, ``gemm_non_persistent`` :707). The reference runs a
 copy-engine all-gather on a side stream and a consumer GEMM that spins on per-rank flags; here the
-communication warps of the GEMM kernel itself pull the peers' shards over NVLink into the local
-gather buffer while the tcgen05 mainloop consumes row blocks as they land
-(``csrc/kernels/gemm_sm100.cu``). No side stream, no flag reset, no barrier: flags are epochs.
+communication warps of the GEMM kernel itself move the shards over NVLink while the tcgen05 mainloop
+consumes row blocks as they land (``csrc/kernels/gemm_sm100.cu``). No side stream, no flag reset, no
+barrier: flags are epochs and counters only grow.
+
+Two gathers: ``sm_push_fused`` (default) stores this rank's shard into every peer's buffer in the order
+in which the peers' tile schedules need it and bumps the destination's per-block row counters, so the
+transfer runs at link speed even for small M; ``sm_pull_fused`` (``B200DIST_AG_PUSH=0``) pulls the peers'
+shards with 16-byte loads after a "shard published" flag.
 """
 from __future__ import annotations
 
 import dataclasses
+import os
 
 import torch
 
@@ -33,6 +39,8 @@ class AllGatherGEMMTensorParallelContext:
     blk_cnt: torch.Tensor                 # local row-arrival counters per 128-row block
     blk_flag: torch.Tensor                # local block epochs
     sync: torch.Tensor                    # local [epoch, done counter, local chunk counter, -]
+    symm_blk_cnt: torch.Tensor | None = None   # push gather: u32[2, nblk] rows landed per block and parity (remote-added)
+    blk_base: torch.Tensor | None = None       # push gather: local u32[2, nblk] counter values before the next call
     BLOCK_M: int = 128
     BLOCK_N: int = 256
     BLOCK_K: int = 64
@@ -41,7 +49,7 @@ class AllGatherGEMMTensorParallelContext:
     max_ctas: int = 0
     for_correctness: bool = False
     is_multinode: bool = False
-    all_gather_method: str = "sm_pull_fused"
+    all_gather_method: str = "sm_push_fused"
 
     @property
     def symm_workspace(self) -> torch.Tensor:
@@ -54,9 +62,10 @@ class AllGatherGEMMTensorParallelContext:
 
     def finalize(self) -> None:
         torch.cuda.synchronize()
-        for t in self.symm_workspaces + [self.symm_ready]:
+        for t in self.symm_workspaces + [self.symm_ready] + ([self.symm_blk_cnt] if self.symm_blk_cnt is not None else []):
             self.heap.free(t)
         self.symm_workspaces = []
+        self.symm_blk_cnt = None
 
     finailize = finalize  # the reference spells it this way (allgather_gemm.py:483)
 
@@ -83,6 +92,11 @@ def create_ag_gemm_context(tensor_A: torch.Tensor, tensor_B: torch.Tensor, rank:
         dtype=tensor_A.dtype, heap=heap, symm_workspaces=ws, symm_ready=ready,
         blk_cnt=torch.zeros(nblk, dtype=torch.int32, device=dev), blk_flag=torch.zeros(nblk, dtype=torch.int32, device=dev),
         sync=torch.zeros(4, dtype=torch.int32, device=dev), for_correctness=for_correctness)
+    ctx.symm_blk_cnt = heap.create_tensor((2, nblk), torch.int32)
+    ctx.symm_blk_cnt.zero_()
+    ctx.blk_base = torch.zeros((2, nblk), dtype=torch.int32, device=dev)
+    if os.environ.get("B200DIST_AG_PUSH", "1") == "0":
+        ctx.all_gather_method = "sm_pull_fused"
     heap.barrier_all()
     torch.cuda.synchronize()
     return ctx
@@ -107,7 +121,8 @@ def ag_gemm(a: torch.Tensor, b: torch.Tensor, ctx: AllGatherGEMMTensorParallelCo
         torch.cuda._sleep(int(straggler_option[1]))
     _lib.call("b200_ag_gemm", ctx.heap.ctx, ptr(a), ptr(ctx.symm_workspaces[0]), ptr(ctx.symm_workspaces[1]), ptr(b),
               ptr(out), Mr, N, K, b.stride(0), out.stride(0), dtype_code(a.dtype), ptr(ctx.symm_ready), ptr(ctx.blk_cnt),
-              ptr(ctx.blk_flag), ptr(ctx.sync), ctx.group_m, ctx.max_ctas, stream_ptr())
+              ptr(ctx.blk_flag), ptr(ctx.sync), ctx.group_m, ctx.max_ctas, 1 if ctx.all_gather_method == "sm_push_fused" else 0,
+              ptr(ctx.symm_blk_cnt), ptr(ctx.blk_base), ctx.symm_blk_cnt.shape[1], stream_ptr())
     ops._count()
     return out
 

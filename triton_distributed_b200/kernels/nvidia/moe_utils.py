@@ -33,9 +33,8 @@ class MoeSortPlan:
     tile_order: torch.Tensor      # int32 [tiles]: issue order (filled by order_tiles)
     group_count: torch.Tensor     # int32 [segments * E]
     totals: torch.Tensor          # int32 [2 + segments]: m_pad, tiles, cumulative tiles per segment
-    lookback: torch.Tensor
-    sync: torch.Tensor
-    status: torch.Tensor
+    scratch: torch.Tensor         # int32: per-chunk expert counts / prefixes and group offsets
+    status: torch.Tensor          # int32 [16], stays zero: the sort has no device-side waits that could expire
     pair_pos: torch.Tensor | None = None  # int32 [n_pairs]: sorted position of every pair (when requested)
 
     @property
@@ -49,12 +48,13 @@ def create_sort_plan(n_pairs: int, topk: int, num_experts: int, block_m: int = 1
     lib.b200_moe_sorted_capacity.restype = ctypes.c_longlong
     cap = int(lib.b200_moe_sorted_capacity(n_pairs, num_experts, block_m, segments))
     tiles = cap // block_m
+    lib.b200_moe_sort_scratch_ints.restype = ctypes.c_longlong
+    scratch = int(lib.b200_moe_sort_scratch_ints(n_pairs, num_experts, segments))
     i32 = dict(dtype=torch.int32, device=device)
     return MoeSortPlan(n_pairs, topk, num_experts, block_m, segments, cap,
                        torch.empty(cap, **i32), torch.empty(tiles, **i32), torch.empty(tiles, **i32),
                        torch.empty(tiles, **i32), torch.empty(tiles, **i32), torch.zeros(segments * num_experts, **i32),
-                       torch.zeros(2 + segments, **i32), torch.zeros(segments * num_experts, dtype=torch.int64, device=device),
-                       torch.zeros(4, **i32), torch.zeros(16, **i32),
+                       torch.zeros(2 + segments, **i32), torch.empty(scratch, **i32), torch.zeros(16, **i32),
                        torch.empty(n_pairs, **i32) if with_positions else None)
 
 
@@ -68,8 +68,8 @@ def moe_sort(topk_ids: torch.Tensor, plan: MoeSortPlan, tokens_per_rank: int | N
         tokens_per_rank = max(1, plan.n_pairs // plan.topk)
     _lib.call("b200_moe_sort", ptr(ids), plan.n_pairs, plan.topk, plan.num_experts, plan.block_m, plan.segments,
               tokens_per_rank, ptr(plan.sorted_ids), ptr(plan.tile_expert), ptr(plan.tile_seg_start), ptr(plan.tile_seg_end),
-              ptr(plan.group_count), ptr(plan.totals), ptr(plan.lookback), ptr(plan.sync), ptr(plan.status), ptr(plan.pair_pos), stream_ptr())
-    ops._count(2 if plan.segments == 1 else 1)
+              ptr(plan.group_count), ptr(plan.totals), ptr(plan.scratch), ptr(plan.pair_pos), stream_ptr())
+    ops._count(4)
     return plan
 
 
