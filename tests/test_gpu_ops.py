@@ -198,3 +198,13 @@ def test_top_p_sampling_matches_sorted_reference():
     peaked[1, 999] = 10.0
     ids = ops.top_p_sample(peaked, 1.0, 0.9)
     assert ids.flatten().tolist() == [123, 999]
+    # odd vocabulary: rows that are not 16-byte aligned take the scalar path; tiny rows leave some CTAs without work
+    odd = torch.full((3, 1001), -30.0, device="cuda")
+    odd[0, 1000] = 10.0
+    odd[1, 5] = 10.0
+    odd[2, 500] = 10.0
+    assert ops.top_p_sample(odd, 1.0, 0.9).flatten().tolist() == [1000, 5, 500]
+    tiny = torch.full((2, 10), -30.0, device="cuda")
+    tiny[0, 9] = 5.0
+    tiny[1, 0] = 5.0
+    assert ops.top_p_sample(tiny, 0.7, 0.5).flatten().tolist() == [9, 0]

@@ -28,6 +28,8 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--m", type=int, default=4096, help="rows of the ag_gemm / gemm_rs problem")
+    ap.add_argument("--kv-len", type=int, default=16384, help="KV length of the decode_attn / sp_decode problem")
+    ap.add_argument("--splits", type=int, default=0, help="decode_attn: KV splits (0 = the library's choice)")
     args = ap.parse_args()
     os.environ.setdefault("RANK", "0"), os.environ.setdefault("LOCAL_RANK", "0"), os.environ.setdefault("WORLD_SIZE", "1")
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1"), os.environ.setdefault("MASTER_PORT", "29571")
@@ -91,7 +93,7 @@ def main() -> None:
             return layer.combine(back, wt)
         info = {"bytes": T * H * 2.0 + T * topk * H * 1.0 + T * topk * H * 2.0 * 2 + T * H * 2.0}
     elif args.op in ("decode_attn", "sp_decode"):
-        B, Hq, Hkv, D, page, L = 8, 64, 8, 128, 64, 16384
+        B, Hq, Hkv, D, page, L = 8, 64, 8, 128, 64, args.kv_len
         nb = L // page
         kc = torch.randn(B * nb, page, Hkv, D, device=dev, dtype=dt)
         vc = torch.randn_like(kc)
@@ -100,7 +102,8 @@ def main() -> None:
         q = torch.randn(B, Hq, D, device=dev, dtype=dt)
         info = {"bytes": 2.0 * kc.numel() * 2}
         if args.op == "decode_attn":
-            S = ops.choose_kv_splits(B, Hkv, Hq // Hkv, L)
+            S = args.splits or ops.choose_kv_splits(B, Hkv, Hq // Hkv, L)
+            info["splits"] = S
             fn = lambda: ops.decode_attention(q, kc, vc, lens, bt, 1 / math.sqrt(D), 0.0, S)
         else:
             layer = SpGQAFlashDecodeAttention(0, 0, 1, 1, Hq, Hkv, D, D, page_size=page, scale=1 / math.sqrt(D), max_allowed_batch=B)
@@ -137,6 +140,8 @@ def main() -> None:
         out["tflops"] = info["flops"] / min(ts) / 1e9
     if "bytes" in info:
         out["gbs"] = info["bytes"] / min(ts) / 1e6
+    if "splits" in info:
+        out["splits"] = info["splits"]
     print(json.dumps(out), flush=True)
     os._exit(0)
 

@@ -245,7 +245,10 @@ __device__ __forceinline__ bool wait_flag(const SymmCtx& c, const uint32_t* flag
     uint32_t seen = SYS ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
     bool ok = (CMP == WaitCmp::EQ) ? (seen == value) : (static_cast<int32_t>(seen - value) >= 0);
     if (ok) return true;
-    if ((++spins & 63u) == 0u) {
+    // back off once the flag is clearly not about to flip: thousands of threads polling one line would otherwise
+    // saturate its L2 slice and delay the very stores and atomics that the waiters are waiting for
+    if (++spins > 8u) __nanosleep(spins > 64u ? 256u : 64u);
+    if ((spins & 63u) == 0u) {
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
       if (now - t0 > c.timeout_ns) {

@@ -56,14 +56,30 @@ struct EpParams {
   void* out;                // [T, H] bf16
 };
 
-// cum[e] = pairs of experts < e; every CTA computes it for itself (E <= 1024)
+// cum[e] = pairs of experts < e; every CTA computes it for itself (E <= 1024): coalesced load, then warp 0 scans
+// 32 experts per step.
 __device__ __forceinline__ void build_cum(const int32_t* counts, const int32_t* cum_in, int E, int* cum) {
   if (cum_in) {
     for (int e = threadIdx.x; e <= E; e += blockDim.x) cum[e] = cum_in[e];
-  } else if (threadIdx.x == 0) {
-    int run = 0;
-    for (int e = 0; e < E; ++e) { cum[e] = run; run += counts[e]; }
-    cum[E] = run;
+  } else {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cum[e + 1] = counts[e];
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      const int lane = threadIdx.x;
+      int carry = 0;
+      for (int base = 0; base < E; base += 32) {
+        const int v = base + lane < E ? cum[base + lane + 1] : 0;
+        int incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int u = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += u;
+        }
+        if (base + lane < E) cum[base + lane + 1] = carry + incl;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) cum[0] = 0;
+    }
   }
   __syncthreads();
 }
@@ -86,8 +102,24 @@ __device__ __forceinline__ bool signal_and_wait(const SymmCtx& ctx, uint32_t* fl
   return __syncthreads_and(ok);
 }
 
+// One warp copies one row; eight (then four) independent 16-byte loads in flight per lane.
 __device__ __forceinline__ void copy_row_warp(uint8_t* dst, const uint8_t* src, int bytes, int lane) {
-  for (int i = lane * 16; i < bytes; i += 32 * 16) st_v4(dst + i, *reinterpret_cast<const uint4*>(src + i));
+  int i = lane * 16;
+  for (; i + 7 * 512 < bytes; i += 8 * 512) {
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = ld_v4_relaxed_sys(src + i + u * 512);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) st_v4(dst + i + u * 512, v[u]);
+  }
+  for (; i + 3 * 512 < bytes; i += 4 * 512) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = ld_v4_relaxed_sys(src + i + u * 512);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) st_v4(dst + i + u * 512, v[u]);
+  }
+  for (; i < bytes; i += 512) st_v4(dst + i, ld_v4_relaxed_sys(src + i));
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -143,51 +175,64 @@ __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const EpParams 
     }
     const uint8_t* row = x + static_cast<size_t>(t) * p.H * 2;
     if (!p.quant) {
-      for (int i = lane * 16; i < p.H * 2; i += 512) {
-        const uint4 v = *reinterpret_cast<const uint4*>(row + i);
+      for (int i0 = lane * 16; i0 < p.H * 2; i0 += 4 * 512) {  // four loads in flight, then k stores each
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          v[u] = i0 + u * 512 < p.H * 2 ? *reinterpret_cast<const uint4*>(row + i0 + u * 512) : make_uint4(0, 0, 0, 0);
         for (int k = 0; k < p.topk; ++k) {
           uint8_t* dst = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_dst), k));
-          st_v4(dst + i, v);
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (i0 + u * 512 < p.H * 2) st_v4(dst + i0 + u * 512, v[u]);
         }
       }
     } else {
-      // each half-warp owns one 128-channel block per iteration: lane holds 8 channels
+      // each half-warp owns one 128-channel block per step (a lane holds 8 channels); four steps are loaded at once
       const int half = lane >> 4, hl = lane & 15;
-      for (int b0 = 0; b0 < p.H / 128; b0 += 2) {
-        const int blk = b0 + half;
-        const bool in = blk < p.H / 128;
-        float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (in) {
-          const uint4 v = *reinterpret_cast<const uint4*>(row + (static_cast<size_t>(blk) * 128 + hl * 8) * 2);
-          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      const int nblk = p.H / 128;
+      for (int b0 = 0; b0 < nblk; b0 += 8) {
+        uint4 raw[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int blk = b0 + 2 * u + half;
+          raw[u] = blk < nblk ? *reinterpret_cast<const uint4*>(row + (static_cast<size_t>(blk) * 128 + hl * 8) * 2)
+                              : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int blk = b0 + 2 * u + half;
+          const bool in = blk < nblk;
+          float f[8];
+          const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            const float2 u = unpack_bf16x2(w[q]);
-            f[2 * q] = u.x;
-            f[2 * q + 1] = u.y;
+            const float2 x2 = unpack_bf16x2(w[q]);
+            f[2 * q] = x2.x;
+            f[2 * q + 1] = x2.y;
           }
-        }
-        float amax = 0.f;
+          float amax = 0.f;
 #pragma unroll
-        for (int q = 0; q < 8; ++q) amax = fmaxf(amax, fabsf(f[q]));
+          for (int q = 0; q < 8; ++q) amax = fmaxf(amax, fabsf(f[q]));
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        const float scale = amax / 448.f;
-        const float den = scale > 0.f ? scale : 1.f;  // exact division, so that rounding ties fall as in x / scale
-        uint32_t lo = 0, hi = 0;
+          for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+          const float scale = amax / 448.f;
+          const float den = scale > 0.f ? scale : 1.f;  // exact division, so that rounding ties fall as in x / scale
+          uint32_t lo = 0, hi = 0;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t a = __nv_cvt_float_to_fp8(__fdiv_rn(f[q], den), __NV_SATFINITE, __NV_E4M3);
-          const uint32_t c = __nv_cvt_float_to_fp8(__fdiv_rn(f[4 + q], den), __NV_SATFINITE, __NV_E4M3);
-          lo |= a << (8 * q);
-          hi |= c << (8 * q);
-        }
-        for (int k = 0; k < p.topk; ++k) {
-          uint8_t* dst = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_dst), k));
-          float* sdst = reinterpret_cast<float*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_sdst), k));
-          if (in) {
-            *reinterpret_cast<uint2*>(dst + blk * 128 + hl * 8) = make_uint2(lo, hi);
-            if (hl == 0) sdst[blk] = scale;
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t a = __nv_cvt_float_to_fp8(__fdiv_rn(f[q], den), __NV_SATFINITE, __NV_E4M3);
+            const uint32_t c = __nv_cvt_float_to_fp8(__fdiv_rn(f[4 + q], den), __NV_SATFINITE, __NV_E4M3);
+            lo |= a << (8 * q);
+            hi |= c << (8 * q);
+          }
+          for (int k = 0; k < p.topk; ++k) {
+            uint8_t* dst = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_dst), k));
+            float* sdst = reinterpret_cast<float*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_sdst), k));
+            if (in) {
+              *reinterpret_cast<uint2*>(dst + blk * 128 + hl * 8) = make_uint2(lo, hi);
+              if (hl == 0) sdst[blk] = scale;
+            }
           }
         }
       }
@@ -238,16 +283,25 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const EpParams p
       }
       for (int i = lane * 16; i < row_bytes; i += 512) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int k = 0; k < p.topk; ++k) {
-          const uint8_t* src = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_src), k));
-          const float wk = __shfl_sync(0xffffffffu, my_w, k);
-          const uint4 v = ld_v4_relaxed_sys(src + i);
-          const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+        for (int k0 = 0; k0 < p.topk; k0 += 8) {  // up to eight copies in flight before the first add
+          uint4 v[8];
+          float wk[8];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float2 u = unpack_bf16x2(w4[q]);
-            acc[2 * q] += wk * u.x;
-            acc[2 * q + 1] += wk * u.y;
+          for (int u = 0; u < 8; ++u) {
+            const int k = k0 + u < p.topk ? k0 + u : k0;
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_src), k));
+            wk[u] = k0 + u < p.topk ? __shfl_sync(0xffffffffu, my_w, k) : 0.f;
+            v[u] = k0 + u < p.topk ? ld_v4_relaxed_sys(src + i) : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const uint32_t w4[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 f = unpack_bf16x2(w4[q]);
+              acc[2 * q] += wk[u] * f.x;
+              acc[2 * q + 1] += wk[u] * f.y;
+            }
           }
         }
         st_v4(static_cast<uint8_t*>(p.out) + static_cast<size_t>(t) * row_bytes + i,
@@ -264,23 +318,45 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const EpParams p
 __global__ void __launch_bounds__(1024) ep_recv_plan_kernel(const int32_t* splits, int world, int E_local, int max_m, int block_m,
                                                             int32_t* sorted_ids, int32_t* tile_expert, int32_t* totals,
                                                             int32_t* rows_per_expert, int cap_rows) {
-  __shared__ int estart[kEpMaxExperts + 1];         // padded start row of every local expert
-  __shared__ int src_off[kMaxRanks][kEpMaxExperts]; // offset of (s, e) inside source s's area
-  if (threadIdx.x == 0) {
-    int run = 0;
-    for (int e = 0; e < E_local; ++e) {
-      estart[e] = run;
-      int c = 0;
-      for (int s = 0; s < world; ++s) c += splits[s * E_local + e];
-      rows_per_expert[e] = c;
-      run += (c + block_m - 1) / block_m * block_m;
+  __shared__ int estart[kEpMaxExperts + 1];              // padded start row of every local expert
+  __shared__ int src_off[kMaxRanks][kEpMaxExperts + 1];  // offset of (s, e) inside source s's area; [E_local] = total
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // warp 0: padded expert starts; warps 1..world: offsets inside each source's area (32 experts per step)
+  if (warp <= world) {
+    int carry = 0;
+    for (int base = 0; base < E_local; base += 32) {
+      const int e = base + lane;
+      int v = 0;
+      if (e < E_local) {
+        if (warp == 0) {
+          int c = 0;
+          for (int s = 0; s < world; ++s) c += splits[s * E_local + e];
+          rows_per_expert[e] = c;
+          v = (c + block_m - 1) / block_m * block_m;
+        } else {
+          v = splits[(warp - 1) * E_local + e];
+        }
+      }
+      int incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += u;
+      }
+      if (e < E_local) {
+        if (warp == 0) estart[e] = carry + incl - v;
+        else src_off[warp - 1][e] = carry + incl - v;
+      }
+      carry += __shfl_sync(0xffffffffu, incl, 31);
     }
-    estart[E_local] = run;
-    totals[0] = run;
-    totals[1] = run / block_m;
-    for (int s = 0; s < world; ++s) {
-      int o = 0;
-      for (int e = 0; e < E_local; ++e) { src_off[s][e] = o; o += splits[s * E_local + e]; }
+    if (lane == 0) {
+      if (warp == 0) {
+        estart[E_local] = carry;
+        totals[0] = carry;
+        totals[1] = carry / block_m;
+      } else {
+        src_off[warp - 1][E_local] = carry;
+      }
     }
   }
   __syncthreads();
@@ -290,7 +366,7 @@ __global__ void __launch_bounds__(1024) ep_recv_plan_kernel(const int32_t* split
   for (int e = 0; e < E_local; ++e) {
     int dst = estart[e];
     for (int s = 0; s < world; ++s) {
-      const int n = splits[s * E_local + e];
+      const int n = src_off[s][e + 1] - src_off[s][e];
       for (int i = threadIdx.x; i < n; i += blockDim.x)
         if (dst + i < cap_rows) sorted_ids[dst + i] = s * max_m + src_off[s][e] + i;
       dst += n;

@@ -100,6 +100,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile uint32_t* bcast = tmem_slot + 2;
+  uint32_t* ready_cache = tmem_slot + 4;  // AG: [kMaxRanks] epoch of the last shard seen complete, per source rank
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = min(p.totals[1], p.max_tiles);
@@ -121,6 +122,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
       mbar_init(tempty_bar + i, 4);
     }
     *abort_flag = 0;
+    for (int i = 0; i < kMaxRanks; ++i) ready_cache[i] = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmW);
   }
@@ -300,7 +302,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
         if (kMode == kGAG && valid && ok) {
           const int src = src_row / p.Tr;
           if (src != last_src) {
-            ok = wait_flag<WaitCmp::EQ, false>(ctx, p.rank_flag + src, epoch, src, __LINE__);
+            // a shard that any thread of this CTA has seen complete is not polled in global memory again
+            uint32_t seen;
+            asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(seen) : "r"(smem_u32(ready_cache + src)) : "memory");
+            if (seen != epoch) {
+              ok = wait_flag<WaitCmp::EQ, false>(ctx, p.rank_flag + src, epoch, src, __LINE__);
+              if (ok) asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(ready_cache + src)), "r"(epoch) : "memory");
+            }
             last_src = src;
           }
         }

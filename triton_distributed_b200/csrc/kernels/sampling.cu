@@ -1,4 +1,4 @@
-// Top-p (nucleus) sampling in one kernel, one CTA per row, without sorting.
+// Top-p (nucleus) sampling in one kernel, one cluster of eight CTAs per row, without sorting.
 //
 // The nucleus of a row is {i : p_i >= t*} where t* is the largest threshold whose kept mass still reaches
 // top_p; that is the same set a descending sort + cumulative sum selects (up to ties), but it can be found
@@ -11,9 +11,12 @@
 #include "b200/host.h"
 #include "b200/primitives.cuh"
 
+#include <cooperative_groups.h>
+
 namespace b200 {
 
 constexpr int kSampleThreads = 1024;
+constexpr int kSampleCtas = 8;  // CTAs (one cluster) per row
 
 __device__ __forceinline__ float block_reduce_sum(float v, float* red) {
   v = warp_sum(v);
@@ -42,34 +45,34 @@ __device__ __forceinline__ float block_reduce_max(float v, float* red) {
   return red[32];
 }
 
-// Strided pass over a row with eight independent 16-byte loads in flight per thread (one CTA streams a 600 KB row, so
-// memory-level parallelism per thread is what sets the speed). f(index, value) is called for every element.
+// Strided pass over the slice [lo, hi) of a row (lo a multiple of 4) with four independent 16-byte loads in flight
+// per thread. f(index, value) is called for every element.
 template <typename F>
-__device__ __forceinline__ void for_row(const float* __restrict__ row, int V, F f) {
+__device__ __forceinline__ void for_range(const float* __restrict__ row, int lo, int hi, F f) {
   const int tid = threadIdx.x;
-  const bool aligned = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
-  int done = 0;
-  if (aligned) {
-    const int nvec = V / 4;
-    const float4* r4 = reinterpret_cast<const float4*>(row);
+  int done = lo;
+  if ((reinterpret_cast<uintptr_t>(row + lo) & 15u) == 0) {
+    const int nvec = (hi - lo) / 4;
+    const float4* r4 = reinterpret_cast<const float4*>(row + lo);
     int i = tid;
-    for (; i + 7 * kSampleThreads < nvec; i += 8 * kSampleThreads) {
-      float4 v[8];
+    for (; i + 3 * kSampleThreads < nvec; i += 4 * kSampleThreads) {
+      float4 v[4];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = r4[i + u * kSampleThreads];
+      for (int u = 0; u < 4; ++u) v[u] = r4[i + u * kSampleThreads];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int b = (i + u * kSampleThreads) * 4;
+      for (int u = 0; u < 4; ++u) {
+        const int b = lo + (i + u * kSampleThreads) * 4;
         f(b, v[u].x); f(b + 1, v[u].y); f(b + 2, v[u].z); f(b + 3, v[u].w);
       }
     }
     for (; i < nvec; i += kSampleThreads) {
       const float4 v = r4[i];
-      f(i * 4, v.x); f(i * 4 + 1, v.y); f(i * 4 + 2, v.z); f(i * 4 + 3, v.w);
+      const int b = lo + i * 4;
+      f(b, v.x); f(b + 1, v.y); f(b + 2, v.z); f(b + 3, v.w);
     }
-    done = nvec * 4;
+    done = lo + nvec * 4;
   }
-  for (int i = done + tid; i < V; i += kSampleThreads) f(i, row[i]);
+  for (int i = done + tid; i < hi; i += kSampleThreads) f(i, row[i]);
 }
 
 // Histogram cells are 64-bit fixed point (2^-40): integer shared-memory atomics are native and exact, float ones
@@ -99,66 +102,105 @@ __device__ __forceinline__ int first_reaching(const u64* incl, u64 target, int* 
 
 // The nucleus threshold is found with two histograms over z = (max - logit) / T instead of a sort or a
 // bisection: 1024 bins of width 1/32 locate the bin in which the kept mass crosses top_p, 1024 sub-bins of that
-// bin pin the threshold to a relative probability error of e^(1/32768). Five passes over the row in total.
-__global__ void __launch_bounds__(kSampleThreads) top_p_sample_kernel(const float* __restrict__ logits, int ld, int V,
-                                                                      float inv_temperature, float top_p,
-                                                                      const float* __restrict__ uniform,
-                                                                      long long* __restrict__ out) {
+// bin pin the threshold to a relative probability error of e^(1/32768).
+//
+// A row is spread over a cluster of eight CTAs (a decode batch has few rows, and one SM cannot stream a 600 KB row
+// fast enough): every CTA works on an eighth of the vocabulary and the CTAs exchange their maxima, histograms and
+// kept masses through distributed shared memory. Four passes over the slice in total.
+__global__ void __cluster_dims__(kSampleCtas, 1, 1) __launch_bounds__(kSampleThreads)
+top_p_sample_kernel(const float* __restrict__ logits, int ld, int V, float inv_temperature, float top_p,
+                    const float* __restrict__ uniform, long long* __restrict__ out) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
   __shared__ float red[33];
-  __shared__ u64 cells[kSampleThreads];
+  __shared__ u64 cells_a[kSampleThreads], cells_b[kSampleThreads], merged[kSampleThreads];
   __shared__ float hist[32];
   __shared__ int chosen, slot;
-  const float* row = logits + static_cast<size_t>(blockIdx.x) * ld;
+  __shared__ float x_max, x_mass;          // read by the other CTAs of the cluster
+  __shared__ int x_arg;
+  __shared__ float all_max[kSampleCtas], all_mass[kSampleCtas];
+  __shared__ int all_arg[kSampleCtas];
+  const int crank = static_cast<int>(cluster.block_rank());
+  const int row_id = blockIdx.x / kSampleCtas;
+  const float* row = logits + static_cast<size_t>(row_id) * ld;
   const int tid = threadIdx.x;
+  const int per = ((V + kSampleCtas - 1) / kSampleCtas + 3) & ~3;
+  const int lo = min(V, crank * per), hi = min(V, lo + per);
   griddep_launch_dependents();
   griddep_wait();
 
+  // ---- pass 1: maximum and the lowest index attaining it
   float mx = -INFINITY;
-  int arg = 0;
-  for_row(row, V, [&](int i, float v) {
+  int arg = 0x7fffffff;
+  for_range(row, lo, hi, [&](int i, float v) {
     if (v > mx || (v == mx && i < arg)) { mx = v; arg = i; }
   });
-  const float gmax = block_reduce_max(mx, red);
+  const float lmax = block_reduce_max(mx, red);
   if (tid == 0) chosen = 0x7fffffff;
-  cells[tid] = 0ull;
+  cells_a[tid] = 0ull;
+  cells_b[tid] = 0ull;
   __syncthreads();
-  if (mx == gmax) atomicMin(&chosen, arg);  // lowest index attaining the maximum: the fallback choice
+  if (mx == lmax && arg != 0x7fffffff) atomicMin(&chosen, arg);
+  __syncthreads();
+  if (tid == 0) { x_max = lmax; x_arg = chosen; }
+  cluster.sync();
+  if (tid < kSampleCtas) {
+    all_max[tid] = *cluster.map_shared_rank(&x_max, tid);
+    all_arg[tid] = *cluster.map_shared_rank(&x_arg, tid);
+  }
+  __syncthreads();
+  float gmax = -INFINITY;
+  int garg = 0x7fffffff;
+#pragma unroll
+  for (int c = 0; c < kSampleCtas; ++c) {
+    if (all_max[c] > gmax || (all_max[c] == gmax && all_arg[c] < garg)) { gmax = all_max[c]; garg = all_arg[c]; }
+  }
+  __syncthreads();
+  if (tid == 0) chosen = garg;  // the fallback choice
 
   float thr_z = INFINITY;  // keep entries with z < thr_z
   if (top_p < 1.f) {
-    // pass 2: coarse histogram of probability mass over z
-    for_row(row, V, [&](int, float v) {
+    // ---- pass 2: coarse histogram of probability mass over z
+    for_range(row, lo, hi, [&](int, float v) {
       const float z = (gmax - v) * inv_temperature;  // >= 0
-      atomicAdd(cells + min(kSampleThreads - 1, static_cast<int>(z * 32.f)), to_fixed(__expf(-z)));
+      atomicAdd(cells_a + min(kSampleThreads - 1, static_cast<int>(z * 32.f)), to_fixed(__expf(-z)));
     });
+    cluster.sync();
+    u64 sum = 0ull;
+#pragma unroll
+    for (int c = 0; c < kSampleCtas; ++c) sum += cluster.map_shared_rank(cells_a, c)[tid];
+    merged[tid] = sum;
     __syncthreads();
-    scan1024(cells);
-    const u64 target = static_cast<u64>(static_cast<double>(top_p) * static_cast<double>(cells[kSampleThreads - 1]));
-    const int b = first_reaching(cells, target, &slot);
-    const u64 before = b > 0 ? cells[b - 1] : 0ull;
+    scan1024(merged);
+    const u64 target = static_cast<u64>(static_cast<double>(top_p) * static_cast<double>(merged[kSampleThreads - 1]));
+    const int b = first_reaching(merged, target, &slot);
+    const u64 before = b > 0 ? merged[b - 1] : 0ull;
     __syncthreads();
-    cells[tid] = 0ull;
-    __syncthreads();
-    // pass 3: refine inside bin b
-    for_row(row, V, [&](int, float v) {
+    // ---- pass 3: refine inside bin b
+    for_range(row, lo, hi, [&](int, float v) {
       const float z = (gmax - v) * inv_temperature;
       const float zb = z * 32.f;
       if (min(kSampleThreads - 1, static_cast<int>(zb)) == b)
-        atomicAdd(cells + min(kSampleThreads - 1, max(0, static_cast<int>((zb - b) * 1024.f))), to_fixed(__expf(-z)));
+        atomicAdd(cells_b + min(kSampleThreads - 1, max(0, static_cast<int>((zb - b) * 1024.f))), to_fixed(__expf(-z)));
     });
+    cluster.sync();
+    sum = 0ull;
+#pragma unroll
+    for (int c = 0; c < kSampleCtas; ++c) sum += cluster.map_shared_rank(cells_b, c)[tid];
+    merged[tid] = sum;
     __syncthreads();
-    scan1024(cells);
-    const int sb = first_reaching(cells, target > before ? target - before : 0ull, &slot);
+    scan1024(merged);
+    const int sb = first_reaching(merged, target > before ? target - before : 0ull, &slot);
     thr_z = b == kSampleThreads - 1 ? INFINITY : (b + (sb + 1) * (1.f / 1024.f)) * (1.f / 32.f);
     __syncthreads();
   }
-  // draw in index order among the kept entries. Warp w owns the contiguous range [w * R, (w + 1) * R), cut into 32
-  // sub-blocks of S entries; lane j ends up with the kept mass of sub-block j (coalesced reads, two sub-blocks = up
-  // to 2 * S / 32 loads in flight). The target is then located by warp, by sub-block, and by a walk of S / 32 steps.
+  // ---- pass 4: draw in index order among the kept entries. Inside the CTA's slice, warp w owns the contiguous
+  // range [lo + w * R, lo + (w + 1) * R), cut into 32 sub-blocks of S entries; lane j ends up with the kept mass of
+  // sub-block j (coalesced reads). The target is located by CTA, by warp, by sub-block, then by a walk of S / 32 steps.
   const int lane = tid & 31, warp = tid >> 5;
-  const int S = ((V + 1023) / 1024 + 31) / 32 * 32;  // multiple of 32, 32 * 32 * S >= V
+  const int S = ((per + 1023) / 1024 + 31) / 32 * 32;  // multiple of 32, 32 * 32 * S >= per
   const int R = 32 * S;
-  const int r0 = min(V, warp * R), r1 = min(V, r0 + R);
+  const int r0 = min(hi, lo + warp * R), r1 = min(hi, r0 + R);
   auto kept_mass = [&](int i) -> float {
     if (i >= r1) return 0.f;
     const float z = (gmax - row[i]) * inv_temperature;
@@ -195,37 +237,68 @@ __global__ void __launch_bounds__(kSampleThreads) top_p_sample_kernel(const floa
     const float v = __shfl_up_sync(0xffffffffu, incl, o);
     if (lane >= o) incl += v;
   }
-  const float total = __shfl_sync(0xffffffffu, incl, 31);
-  const float target = uniform[blockIdx.x] * total;
-  const float my_incl = __shfl_sync(0xffffffffu, incl, warp);
-  const float my_before = my_incl - mine;
-  if (mine > 0.f && target >= my_before && target < my_incl) {
-    // first sub-block whose inclusive mass passes the target (the last non-empty one if rounding leaves none)
-    const uint32_t pass = __ballot_sync(0xffffffffu, sub > 0.f && my_before + sub_incl > target);
-    const uint32_t nonempty = __ballot_sync(0xffffffffu, sub > 0.f);
-    const int jsel = pass ? __ffs(pass) - 1 : 31 - __clz(nonempty);
-    float acc = my_before + __shfl_sync(0xffffffffu, sub_incl - sub, jsel);
-    int pick = -1, last_kept = -1;
-    const int s0 = r0 + jsel * S, s1 = min(r1, s0 + S);
-    for (int b0 = s0; b0 < s1 && pick < 0; b0 += 32) {
-      const float m = kept_mass(b0 + lane);
-      float sc = m;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const float v = __shfl_up_sync(0xffffffffu, sc, o);
-        if (lane >= o) sc += v;
-      }
-      const uint32_t hit = __ballot_sync(0xffffffffu, m > 0.f && acc + sc > target);
-      const uint32_t kept = __ballot_sync(0xffffffffu, m > 0.f);
-      if (hit) pick = b0 + __ffs(hit) - 1;
-      else if (kept) last_kept = b0 + 31 - __clz(kept);
-      acc += __shfl_sync(0xffffffffu, sc, 31);
-    }
-    if (pick < 0) pick = last_kept;  // rounding: the last kept entry of the sub-block
-    if (pick >= 0 && lane == 0) chosen = pick;
-  }
+  const float cta_mass = __shfl_sync(0xffffffffu, incl, 31);
+  if (tid == 0) x_mass = cta_mass;
+  cluster.sync();
+  if (tid < kSampleCtas) all_mass[tid] = *cluster.map_shared_rank(&x_mass, tid);
   __syncthreads();
-  if (tid == 0) out[blockIdx.x] = chosen;
+  float cta_before = 0.f, total = 0.f;
+#pragma unroll
+  for (int c = 0; c < kSampleCtas; ++c) {
+    if (c < crank) cta_before += all_mass[c];
+    total += all_mass[c];
+  }
+  const float target = uniform[row_id] * total;
+  // the CTA whose interval holds the target; rounding at the upper end goes to the last CTA that kept anything
+  int sel = -1, last_nonempty = 0;
+  {
+    float run = 0.f;
+#pragma unroll
+    for (int c = 0; c < kSampleCtas; ++c) {
+      if (all_mass[c] > 0.f) {
+        last_nonempty = c;
+        if (sel < 0 && target < run + all_mass[c]) sel = c;
+      }
+      run += all_mass[c];
+    }
+    if (sel < 0) sel = last_nonempty;
+  }
+  if (crank == sel) {
+    const float my_incl = cta_before + __shfl_sync(0xffffffffu, incl, warp);
+    const float my_before = my_incl - mine;
+    // warp whose interval holds the target (rounding: the last warp that kept anything)
+    const float w_incl = cta_before + incl;  // lane l: inclusive mass up to warp l
+    const uint32_t wpass = __ballot_sync(0xffffffffu, hist[lane] > 0.f && target < w_incl);
+    const uint32_t wnonempty = __ballot_sync(0xffffffffu, hist[lane] > 0.f);
+    const int wsel = wpass ? __ffs(wpass) - 1 : 31 - __clz(wnonempty | 1u);
+    if (warp == wsel && mine > 0.f) {
+      const uint32_t pass = __ballot_sync(0xffffffffu, sub > 0.f && my_before + sub_incl > target);
+      const uint32_t nonempty = __ballot_sync(0xffffffffu, sub > 0.f);
+      const int jsel = pass ? __ffs(pass) - 1 : 31 - __clz(nonempty);
+      float acc = my_before + __shfl_sync(0xffffffffu, sub_incl - sub, jsel);
+      int pick = -1, last_kept = -1;
+      const int s0 = r0 + jsel * S, s1 = min(r1, s0 + S);
+      for (int b0 = s0; b0 < s1 && pick < 0; b0 += 32) {
+        const float m = kept_mass(b0 + lane);
+        float sc = m;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float v = __shfl_up_sync(0xffffffffu, sc, o);
+          if (lane >= o) sc += v;
+        }
+        const uint32_t hit = __ballot_sync(0xffffffffu, m > 0.f && acc + sc > target);
+        const uint32_t kept = __ballot_sync(0xffffffffu, m > 0.f);
+        if (hit) pick = b0 + __ffs(hit) - 1;
+        else if (kept) last_kept = b0 + 31 - __clz(kept);
+        acc += __shfl_sync(0xffffffffu, sc, 31);
+      }
+      if (pick < 0) pick = last_kept;  // rounding: the last kept entry of the sub-block
+      if (pick >= 0 && lane == 0) chosen = pick;
+    }
+    __syncthreads();
+    if (tid == 0) out[row_id] = chosen;
+  }
+  cluster.sync();  // no CTA's shared memory goes away while a peer may still read it
 }
 
 }  // namespace b200
@@ -238,7 +311,7 @@ B200_API int b200_top_p_sample(const float* logits, int ld, int B, int V, float 
   B200_REQUIRE(temperature > 0.f, "temperature must be positive (use argmax for greedy decoding)");
   B200_REQUIRE(top_p > 0.f, "top_p must be positive");
   if (B == 0) return kOk;
-  top_p_sample_kernel<<<B, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(logits, ld, V, 1.f / temperature,
+  top_p_sample_kernel<<<B * kSampleCtas, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(logits, ld, V, 1.f / temperature,
                                                                                    top_p, uniform, out);
   B200_CHECK_CUDA(cudaGetLastError());
   return kOk;

@@ -33,10 +33,11 @@ class AllToAllContext:
     split_recv_bufs: list[torch.Tensor]
     flags: torch.Tensor
     sync: torch.Tensor
+    calls: int = 0   # host mirror of the device-resident epoch (one per fast_all_to_all), so no call reads it back
 
     @property
     def call_count(self) -> int:
-        return int(self.sync[0].item()) + 1
+        return self.calls + 1
 
     def finalize(self) -> None:
         torch.cuda.synchronize()
@@ -71,7 +72,8 @@ def fast_all_to_all(ctx: AllToAllContext, send_tensor: torch.Tensor, send_split_
     if not send_tensor.is_contiguous() or send_tensor.dtype != ctx.dtype or send_tensor.shape[1] != ctx.hidden:
         raise ValueError("send_tensor must be contiguous [n, hidden] in the context dtype")
     cum = send_split_cumsum.to(torch.int32).contiguous()
-    par = (int(ctx.sync[0].item()) + 1) & 1
+    ctx.calls += 1
+    par = ctx.calls & 1
     sc = None
     if send_scale is not None:
         sc = send_scale.reshape(send_tensor.shape[0], -1).float().contiguous()

@@ -44,6 +44,7 @@ class EPAll2AllLayer:
         self.recv_totals, self.recv_rows_per_expert = z(4), z(self.experts_per_rank)
         self.recv_cap = cap
         self._last = None
+        self._dispatch_calls = 0
         heap.barrier_all()
         torch.cuda.synchronize()
 
@@ -63,7 +64,8 @@ class EPAll2AllLayer:
         ids = exp_indices.to(torch.int32).contiguous()
         plan = self._plan(T)
         moe_sort(ids, plan)
-        par = (int(self.dsync[0].item()) + 1) & 1
+        self._dispatch_calls += 1  # mirrors the device-resident epoch without reading it back
+        par = self._dispatch_calls & 1
         _lib.call("b200_ep_dispatch", self.heap.ctx, ptr(input.contiguous()), T, self.hidden, self.topk, ptr(ids),
                   ptr(plan.pair_pos), ptr(plan.group_count), self.num_tot_experts, self.experts_per_rank, self.max_m,
                   1 if self.fp8 else 0, ptr(self.recv[0]), ptr(self.recv[1]), ptr(self.recv_scale[0]), ptr(self.recv_scale[1]),
