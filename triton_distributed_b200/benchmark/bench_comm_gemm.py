@@ -65,13 +65,21 @@ def main() -> None:
                 torch.matmul(a, w1.t(), out=c)
 
         t_ours = _time(lambda: ag_gemm(a, w1, ag_ctx, out=c), args.iters, args.warmup, group)
+        chosen = ag_ctx.method_for(M // world)
+        by_method = {}
+        if world > 1:  # both gathers, so that the automatic choice can be checked against the data
+            for m in ("sm_push_fused", "sm_pull_fused"):
+                ag_ctx.all_gather_method = m
+                by_method[m] = _time(lambda: ag_gemm(a, w1, ag_ctx, out=c), args.iters, args.warmup, group) * 1e3
+            ag_ctx.all_gather_method = "auto"
         t_base = _time(base_ag, args.iters, args.warmup, group)
         flops = 2.0 * M * n_ag * H
         nv_bytes = (world - 1) * (M // world) * H * 2
         roof = max(flops / (PEAK_TFLOPS * 1e9), nv_bytes / (LINK_GBS * 1e6))
         rows.append({"op": "ag_gemm", "world": world, "M": M, "N": n_ag, "K": H, "ours_us": t_ours * 1e3,
                      "nccl_cublas_us": t_base * 1e3, "speedup": t_base / t_ours, "roofline_us": roof * 1e3,
-                     "frac_of_roofline": roof / t_ours, "tflops": flops / t_ours / 1e9})
+                     "frac_of_roofline": roof / t_ours, "tflops": flops / t_ours / 1e9, "gather": chosen,
+                     "push_us": by_method.get("sm_push_fused"), "pull_us": by_method.get("sm_pull_fused")})
         x = torch.randn(M, k_rs, device="cuda", dtype=dt) * 0.1
         part = torch.empty(M, H, device="cuda", dtype=dt)
         out = torch.empty(M // world, H, device="cuda", dtype=dt)

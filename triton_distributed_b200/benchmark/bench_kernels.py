@@ -28,6 +28,8 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--m", type=int, default=4096, help="rows of the ag_gemm / gemm_rs problem")
+    ap.add_argument("--n", type=int, default=0, help="ag_gemm / gemm_rs: N (0 = the Llama-3-70B TP8 default)")
+    ap.add_argument("--k", type=int, default=0, help="ag_gemm / gemm_rs: K (0 = the Llama-3-70B TP8 default)")
     ap.add_argument("--kv-len", type=int, default=16384, help="KV length of the decode_attn / sp_decode problem")
     ap.add_argument("--splits", type=int, default=0, help="decode_attn: KV splits (0 = the library's choice)")
     args = ap.parse_args()
@@ -40,14 +42,14 @@ def main() -> None:
     dev = "cuda"
     info = {}
     if args.op == "ag_gemm":
-        M, N, K_ = args.m, 3584, 8192
+        M, N, K_ = args.m, args.n or 3584, args.k or 8192
         a = torch.randn(M, K_, device=dev, dtype=dt)
         b = torch.randn(N, K_, device=dev, dtype=dt) * 0.02
         ctx = K.create_ag_gemm_context(a, b, 0, 1, M)
         fn = lambda: K.ag_gemm(a, b, ctx)
         info = {"flops": 2.0 * M * N * K_}
     elif args.op == "gemm_rs":
-        M, N, K_ = args.m, 8192, 3584
+        M, N, K_ = args.m, args.n or 8192, args.k or 3584
         a = torch.randn(M, K_, device=dev, dtype=dt)
         b = torch.randn(N, K_, device=dev, dtype=dt) * 0.02
         ctx = K.create_gemm_rs_context(M, N, 0, 1, 1, dt)

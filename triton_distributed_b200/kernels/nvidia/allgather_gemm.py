@@ -7,10 +7,13 @@ communication warps of the GEMM kernel itself move the shards over NVLink while 
 consumes row blocks as they land (``csrc/kernels/gemm_sm100.cu``). No side stream, no flag reset, no
 barrier: flags are epochs and counters only grow.
 
-Two gathers: ``sm_push_fused`` (default) stores this rank's shard into every peer's buffer in the order
-in which the peers' tile schedules need it and bumps the destination's per-block row counters, so the
-transfer runs at link speed even for small M; ``sm_pull_fused`` (``B200DIST_AG_PUSH=0``) pulls the peers'
-shards with 16-byte loads after a "shard published" flag.
+Two gathers. ``sm_push_fused`` stores this rank's shard into every peer's buffer in the order in which the
+peers' tile schedules need it and bumps the destination's per-block row counters: posted stores run at link
+speed however small M is, but while they drain they compete with the epilogue's stores. ``sm_pull_fused``
+pulls the peers' shards with 16-byte loads after a "shard published" flag: free when one rank's share of the
+GEMM is long enough to cover the first pull, latency-bound when it is not. ``auto`` (default) picks per call
+from the world size and the bytes to move; ``B200DIST_AG_PUSH=1`` / ``0`` forces one. Calls of both kinds can
+share a context (separate flags and counters, common epoch).
 """
 from __future__ import annotations
 
@@ -22,6 +25,9 @@ import torch
 from ... import _lib, ops
 from ..._lib import dtype_code, ptr, stream_ptr
 from ...runtime.heap import SymmHeap, get_heap
+
+
+PUSH_MAX_OUTGOING_BYTES = 64 << 20
 
 
 @dataclasses.dataclass
@@ -49,7 +55,15 @@ class AllGatherGEMMTensorParallelContext:
     max_ctas: int = 0
     for_correctness: bool = False
     is_multinode: bool = False
-    all_gather_method: str = "sm_push_fused"
+    all_gather_method: str = "auto"
+
+    def method_for(self, Mr: int) -> str:
+        """The gather used for a call with Mr rows per rank."""
+        if self.all_gather_method != "auto":
+            return self.all_gather_method
+        outgoing = (self.num_ranks - 1) * Mr * self.K * self.dtype.itemsize
+        # with few ranks a rank's own tiles always cover the first pull; with many, small problems are latency-bound
+        return "sm_push_fused" if self.num_ranks >= 4 and outgoing <= PUSH_MAX_OUTGOING_BYTES else "sm_pull_fused"
 
     @property
     def symm_workspace(self) -> torch.Tensor:
@@ -95,8 +109,9 @@ def create_ag_gemm_context(tensor_A: torch.Tensor, tensor_B: torch.Tensor, rank:
     ctx.symm_blk_cnt = heap.create_tensor((2, nblk), torch.int32)
     ctx.symm_blk_cnt.zero_()
     ctx.blk_base = torch.zeros((2, nblk), dtype=torch.int32, device=dev)
-    if os.environ.get("B200DIST_AG_PUSH", "1") == "0":
-        ctx.all_gather_method = "sm_pull_fused"
+    forced = os.environ.get("B200DIST_AG_PUSH")
+    if forced is not None:
+        ctx.all_gather_method = "sm_pull_fused" if forced == "0" else "sm_push_fused"
     heap.barrier_all()
     torch.cuda.synchronize()
     return ctx
@@ -121,7 +136,7 @@ def ag_gemm(a: torch.Tensor, b: torch.Tensor, ctx: AllGatherGEMMTensorParallelCo
         torch.cuda._sleep(int(straggler_option[1]))
     _lib.call("b200_ag_gemm", ctx.heap.ctx, ptr(a), ptr(ctx.symm_workspaces[0]), ptr(ctx.symm_workspaces[1]), ptr(b),
               ptr(out), Mr, N, K, b.stride(0), out.stride(0), dtype_code(a.dtype), ptr(ctx.symm_ready), ptr(ctx.blk_cnt),
-              ptr(ctx.blk_flag), ptr(ctx.sync), ctx.group_m, ctx.max_ctas, 1 if ctx.all_gather_method == "sm_push_fused" else 0,
+              ptr(ctx.blk_flag), ptr(ctx.sync), ctx.group_m, ctx.max_ctas, 1 if ctx.method_for(Mr) == "sm_push_fused" else 0,
               ptr(ctx.symm_blk_cnt), ptr(ctx.blk_base), ctx.symm_blk_cnt.shape[1], stream_ptr())
     ops._count()
     return out

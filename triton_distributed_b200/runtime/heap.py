@@ -102,8 +102,19 @@ class SymmHeap:
         # 64 KiB of the heap is reserved for runtime flags (barrier epochs etc.)
         self._barrier_flags = self.create_tensor((64,), torch.int32)
         self._barrier_sync = torch.zeros(4, dtype=torch.int32, device="cuda")
+        # The first device barrier also pays for every rank's first kernel launch out of the native library (module
+        # load on a cold machine can take many seconds and differs between ranks): meet on the host first and give
+        # this one barrier a generous budget, then restore the configured one.
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        self._lib.b200_heap_set_timeout_ms(self._h, ctypes.c_uint64(max(timeout_ms, 120000)))
+        self._refresh_ctx()
         self.barrier_all()
         torch.cuda.synchronize()
+        self._lib.b200_heap_set_timeout_ms(self._h, ctypes.c_uint64(timeout_ms))
+        self._refresh_ctx()
+        self.check_status("heap bootstrap barrier")
 
     # ------------------------------------------------------------------ bootstrap pieces
     def _sock_name(self, rank: int) -> bytes:
@@ -197,9 +208,12 @@ class SymmHeap:
         self._refresh_ctx()
 
     # ------------------------------------------------------------------ tensors
-    def create_tensor(self, shape: Sequence[int] | int, dtype: torch.dtype, align: int = 256) -> torch.Tensor:
-        """Allocate a zero-filled symmetric tensor. Collective by convention: every rank must issue the
-        same sequence of create/free calls so that offsets agree."""
+    def create_tensor(self, shape: Sequence[int] | int, dtype: torch.dtype, align: int = 256,
+                      sync: bool = True) -> torch.Tensor:
+        """Allocate a zero-filled symmetric tensor. Collective: every rank must issue the same sequence of
+        create/free calls so that offsets agree. With ``sync`` (default) a device barrier is enqueued behind the
+        zero-fill on the current stream, so that work enqueued after this call can never have its remote writes
+        wiped by a slower peer's zero-fill (the role of the barrier inside ``nvshmem_malloc``)."""
         if isinstance(shape, int):
             shape = (shape,)
         nbytes = max(1, math.prod(shape)) * torch.empty((), dtype=dtype).element_size()
@@ -211,6 +225,8 @@ class SymmHeap:
         t = t[: math.prod(shape)].view(*shape)
         t.zero_()
         self._tensors[t.data_ptr()] = off.value
+        if sync and self.world > 1 and getattr(self, "_barrier_flags", None) is not None:
+            self.barrier_all()
         return t
 
     def offset_of(self, t: torch.Tensor) -> int:
