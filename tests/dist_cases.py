@@ -424,8 +424,8 @@ def reduce_scatter_op_and_moe_layers():
         torch.testing.assert_close(got.float(), want[rank * per:(rank + 1) * per].float(), rtol=5e-2, atol=0.1 * world)
     tp.finalize()
     # EP-MoE layer: every rank owns E / world whole experts
-    for fp8 in (False, True):
-        ep = EP_MoE(rank, world, group, E, topk, H, per, torch.bfloat16, True, fp8_dispatch=fp8)
+    for fp8, fp8_experts in ((False, False), (True, False), (True, True)):
+        ep = EP_MoE(rank, world, group, E, topk, H, per, torch.bfloat16, True, fp8_dispatch=fp8, fp8_experts=fp8_experts)
         el = E // world
         ep._init_parameters(gate, wgu[rank * el:(rank + 1) * el].contiguous(), wdn[rank * el:(rank + 1) * el].contiguous())
         xl = x[rank * per:(rank + 1) * per].contiguous()

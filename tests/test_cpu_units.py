@@ -167,3 +167,25 @@ def test_native_library_builds_and_reports_errors():
         from triton_distributed_b200 import ops
         with pytest.raises(RuntimeError, match="CUDA"):
             ops.gemm(torch.zeros(2, 8), torch.zeros(2, 8))
+
+
+def test_fp8_block_quantisers_round_trip_and_reference():
+    """1x128 activation scales and 128x128 weight scales: amax / 448 without epsilon, zero blocks stay zero, and the
+    dequantised grouped product stays within fp8's precision of the exact one."""
+    import torch
+    from triton_distributed_b200 import ref
+    from triton_distributed_b200.kernels.nvidia.grouped_gemm_fp8 import quantize_fp8_rows, quantize_fp8_weight_blocks
+    torch.manual_seed(0)
+    a = torch.randn(12, 256)
+    a[3] = 0
+    w = torch.randn(3, 200, 256) * 0.05
+    a8, sa = quantize_fp8_rows(a)
+    w8, sw = quantize_fp8_weight_blocks(w)
+    assert a8.dtype == torch.float8_e4m3fn and sa.shape == (12, 2) and sw.shape == (3, 2, 2)
+    assert torch.all(sa[3] == 0) and torch.all(ref.dequant_fp8_rows(a8, sa)[3] == 0)
+    torch.testing.assert_close(sa[0, 0], a[0, :128].abs().max() / 448.0)
+    assert (ref.dequant_fp8_rows(a8, sa) - a).abs().max() <= a.abs().max() * 0.07
+    e = torch.randint(0, 3, (12,))
+    got = ref.grouped_gemm_fp8_ref(a8, sa, w8, sw, e)
+    exact = ref.grouped_gemm_ref(a, w, e)
+    assert (got - exact).norm() / exact.norm() < 0.06

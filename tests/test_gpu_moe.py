@@ -124,3 +124,54 @@ def test_ep_dispatch_combine_world1(dist1):
             torch.testing.assert_close(out.float(), x.float() * wt.sum(-1, keepdim=True), rtol=0.1 if fp8 else 2e-2,
                                        atol=0.1 if fp8 else 2e-2)
         layer.finalize()
+
+
+@pytest.mark.parametrize("T,topk,E,N,K", [(64, 2, 4, 128, 128), (300, 4, 16, 384, 512), (1024, 8, 32, 200, 1024)])
+def test_grouped_gemm_fp8_block_scaled(T, topk, E, N, K):
+    """e4m3 operands, 1x128 activation scales and 128x128 weight scales, against the dequantised fp32 product."""
+    from triton_distributed_b200 import ref
+    from triton_distributed_b200.kernels.nvidia import grouped_gemm_fp8, quantize_fp8_rows, quantize_fp8_weight_blocks
+    torch.manual_seed(3)
+    a = torch.randn(T, K, device="cuda") * torch.rand(T, 1, device="cuda") * 4   # rows of very different magnitude
+    w = torch.randn(E, N, K, device="cuda") * 0.05
+    a8, sa = quantize_fp8_rows(a)
+    w8, sw = quantize_fp8_weight_blocks(w)
+    ids = torch.stack([torch.randperm(E)[:topk] for _ in range(T)]).to(torch.int32).cuda()
+    out = grouped_gemm_fp8(a8, sa, w8, sw, ids)
+    torch.cuda.synchronize()
+    want = ref.grouped_gemm_fp8_ref(a8.repeat_interleave(topk, 0), sa.repeat_interleave(topk, 0), w8, sw, ids.reshape(-1).long())
+    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
+    # and it is close to the unquantised product (fp8 has 3 mantissa bits: a few percent of the row norm)
+    exact = ref.grouped_gemm_ref(a.repeat_interleave(topk, 0), w, ids.reshape(-1).long())
+    err = (out.float() - exact).norm() / exact.norm()
+    assert err < 0.06, f"relative error {err:.3f} against the bf16 product"
+    # per-pair rows with routing weights (the down-projection form)
+    x = torch.randn(T * topk, K, device="cuda")
+    x8, sx = quantize_fp8_rows(x)
+    sc = torch.rand(T, topk, device="cuda")
+    out2 = grouped_gemm_fp8(x8, sx, w8, sw, ids, a_per_pair=True, row_scale=sc)
+    want2 = ref.grouped_gemm_fp8_ref(x8, sx, w8, sw, ids.reshape(-1).long()) * sc.reshape(-1, 1)
+    torch.testing.assert_close(out2.float(), want2, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("fp8,fp8_experts", [(False, False), (True, False), (True, True)])
+def test_ep_moe_layer_world1(dist1, fp8, fp8_experts):
+    """Expert-parallel MoE layer with the GPU as its own only peer: dispatch -> grouped GEMMs -> weighted combine,
+    in bf16, with fp8 dispatch, and with the block-scaled fp8 up-projection on the dispatched bytes."""
+    from triton_distributed_b200.layers.nvidia import EP_MoE
+    from triton_distributed_b200.runtime.heap import get_heap
+    E, topk, H, I, T = 8, 2, 256, 384, 64
+    torch.manual_seed(11)
+    gate = torch.randn(E, H, device="cuda", dtype=torch.bfloat16)  # wide logits: no near-ties between experts
+    wgu = torch.randn(E, 2 * I, H, device="cuda", dtype=torch.bfloat16) * 0.05
+    wdn = torch.randn(E, H, I, device="cuda", dtype=torch.bfloat16) * 0.05
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    ep = EP_MoE(0, 1, dist1, E, topk, H, T, torch.bfloat16, True, fp8_dispatch=fp8, fp8_experts=fp8_experts)
+    ep._init_parameters(gate, wgu, wdn)
+    want = ep.torch_fwd(x, wgu, wdn)
+    for _ in range(2):
+        got = ep.dist_triton_fwd(x)
+        torch.cuda.synchronize()
+        get_heap().check_status("ep_moe")
+        torch.testing.assert_close(got.float(), want.float(), rtol=0.12 if fp8 else 5e-2, atol=0.3 if fp8 else 0.1)
+    ep.finalize()

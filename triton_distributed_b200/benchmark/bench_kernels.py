@@ -18,7 +18,7 @@ import torch
 from .. import ops, utils
 from ..utils import perf_func_cold
 
-OPS = ["ag_gemm", "gemm_rs", "grouped_gemm", "ag_group_gemm", "moe_reduce_rs", "allreduce_rmsnorm", "ep_dispatch_combine",
+OPS = ["ag_gemm", "gemm_rs", "grouped_gemm", "grouped_gemm_fp8", "ag_group_gemm", "moe_reduce_rs", "allreduce_rmsnorm", "ep_dispatch_combine",
        "decode_attn", "sp_decode", "moe_sort", "sampling", "rmsnorm", "qk_norm_rope"]
 
 
@@ -55,6 +55,14 @@ def main() -> None:
         ctx = K.create_gemm_rs_context(M, N, 0, 1, 1, dt)
         fn = lambda: K.gemm_rs(a, b, ctx)
         info = {"flops": 2.0 * M * N * K_}
+    elif args.op == "grouped_gemm_fp8":
+        T, topk, E, H, I = 4096, 8, 128, 4096, 384
+        ids = torch.stack([torch.randperm(E, device=dev)[:topk] for _ in range(T)]).to(torch.int32)
+        a8, sa = K.quantize_fp8_rows(torch.randn(T, H, device=dev))
+        w8, sw = K.quantize_fp8_weight_blocks(torch.randn(E, I, H, device=dev) * 0.02)
+        plan = K.create_sort_plan(T * topk, topk, E, 128, 1)
+        fn = lambda: K.grouped_gemm_fp8(a8, sa, w8, sw, ids, plan=plan)
+        info = {"flops": 2.0 * T * topk * I * H}
     elif args.op in ("grouped_gemm", "ag_group_gemm", "moe_reduce_rs"):
         T, topk, E, H, I = 4096, 8, 128, 4096, 384
         ids = torch.stack([torch.randperm(E, device=dev)[:topk] for _ in range(T)]).to(torch.int32)

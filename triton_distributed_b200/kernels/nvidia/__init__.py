@@ -10,6 +10,8 @@ from .flash_decode import (get_triton_combine_kv_algo_info, gqa_fwd_batch_decode
 from .gemm_reduce_scatter import create_gemm_rs_context, gemm_rs
 from .low_latency_allgather import create_fast_allgather_context, fast_allgather
 from .allgather_group_gemm import ag_group_gemm, create_ag_group_gemm_context, grouped_gemm
+from .grouped_gemm_fp8 import (grouped_gemm_fp8, grouped_gemm_fp8_planned, quantize_fp8_rows,
+                               quantize_fp8_weight_blocks)
 from .moe_reduce_rs import (create_moe_rs_context, create_moe_rs_context_colwise, moe_reduce_rs, moe_reduce_rs_colwise,
                             moe_reduce_rs_rowise, select_experts)
 from .moe_utils import calc_gather_scatter_index, create_sort_plan, moe_sort, order_tiles, reduce_topk

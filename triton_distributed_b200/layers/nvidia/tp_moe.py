@@ -125,7 +125,12 @@ class EP_MoE:
     """Experts partitioned over ranks; tokens travel by the fused dispatch / combine kernels."""
 
     def __init__(self, rank: int, world_size: int, group, num_experts: int, topk: int, hidden: int, max_tokens: int,
-                 dtype=torch.bfloat16, norm_topk_prob: bool = True, fp8_dispatch: bool = False):
+                 dtype=torch.bfloat16, norm_topk_prob: bool = True, fp8_dispatch: bool = False, fp8_experts: bool = False):
+        """fp8_dispatch: tokens travel as e4m3 + one fp32 scale per 128 channels. fp8_experts (needs fp8_dispatch):
+        the up-projection runs on those bytes with block-quantised weights instead of dequantising the rows first."""
+        if fp8_experts and not fp8_dispatch:
+            raise ValueError("fp8_experts needs fp8_dispatch")
+        self.fp8_experts = fp8_experts
         self.rank, self.world_size, self.group = rank, world_size, group
         self.num_experts, self.topk, self.hidden, self.dtype = num_experts, topk, hidden, dtype
         self.norm_topk_prob = norm_topk_prob
@@ -137,6 +142,9 @@ class EP_MoE:
     def _init_parameters(self, gate: torch.Tensor, w_gate_up_local: torch.Tensor, w_down_local: torch.Tensor):
         """gate [E, H]; w_gate_up_local [E / world, 2 * I, H]; w_down_local [E / world, H, I] (this rank's experts)."""
         self.gate, self.w_gate_up, self.w_down = gate.contiguous(), w_gate_up_local.contiguous(), w_down_local.contiguous()
+        if self.fp8_experts:
+            from ...kernels.nvidia.grouped_gemm_fp8 import quantize_fp8_weight_blocks
+            self.w_gate_up8, self.w_gate_up_scale = quantize_fp8_weight_blocks(self.w_gate_up)
 
     def _grouped(self, a: torch.Tensor, w: torch.Tensor, n_rows: int) -> torch.Tensor:
         sorted_ids, tile_expert, totals, _ = self.a2a.recv_plan()
@@ -152,13 +160,22 @@ class EP_MoE:
         """x_local [T_local, H] (this rank's tokens) -> [T_local, H]."""
         ids, w = ops.topk_softmax(ops.linear(x_local, self.gate), self.topk, self.norm_topk_prob)
         res = self.a2a.dispatch(x_local, ids)
-        if self.fp8_dispatch:
+        if self.fp8_experts:
+            from ...kernels.nvidia.grouped_gemm_fp8 import grouped_gemm_fp8_planned
             q, sc = res
-            rows = (q.float().view(q.shape[0], -1, 128) * sc[:, :, None]).view(q.shape[0], -1).to(self.dtype)
+            n_rows = q.shape[0]
+            sorted_ids, tile_expert, totals, _ = self.a2a.recv_plan()
+            up = torch.zeros((n_rows, self.w_gate_up8.shape[1]), dtype=self.dtype, device=q.device)
+            grouped_gemm_fp8_planned(q, sc, self.w_gate_up8, self.w_gate_up_scale, sorted_ids, tile_expert, totals,
+                                     self.a2a.recv_cap // 128, n_rows, 1, None, up)
         else:
-            rows = res
-        n_rows = rows.shape[0]
-        up = self._grouped(rows, self.w_gate_up, n_rows)
+            if self.fp8_dispatch:
+                q, sc = res
+                rows = (q.float().view(q.shape[0], -1, 128) * sc[:, :, None]).view(q.shape[0], -1).to(self.dtype)
+            else:
+                rows = res
+            n_rows = rows.shape[0]
+            up = self._grouped(rows, self.w_gate_up, n_rows)
         act = ops.silu_mul(up)
         down = self._grouped(act, self.w_down, n_rows)
         return self.a2a.combine(down, w)

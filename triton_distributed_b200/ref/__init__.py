@@ -7,7 +7,7 @@ the same compositions the reference uses as goldens (``test/nvidia/test_ag_gemm.
 ``test_moe_reduce_rs.py:76-152``, ``test_sp_decode_attn.py:82-133``).
 """
 from .collectives import (ag_gemm_ref, all_reduce_ref, all_reduce_rmsnorm_ref, fast_allgather_ref, gemm_rs_ref)
-from .moe import (ag_group_gemm_ref, grouped_gemm_ref, all_to_all_post_process_ref, ep_combine_ref, ep_dispatch_ref, fast_all_to_all_ref,
+from .moe import (ag_group_gemm_ref, grouped_gemm_ref, grouped_gemm_fp8_ref, dequant_fp8_rows, dequant_fp8_weight_blocks, all_to_all_post_process_ref, ep_combine_ref, ep_dispatch_ref, fast_all_to_all_ref,
                   fp8_dequant_ref, fp8_quant_ref, moe_align_block_size_ref, moe_reduce_rs_ref, select_experts_ref,
                   ag_moe_tile_schedule_ref, calc_gather_scatter_index_ref)
 from .attention import paged_decode_attention_ref, combine_partials_ref, sp_flash_decode_ref

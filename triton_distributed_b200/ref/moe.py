@@ -120,6 +120,25 @@ def grouped_gemm_ref(a_rows: torch.Tensor, w: torch.Tensor, expert_of_row: torch
     return out
 
 
+def dequant_fp8_rows(a8: torch.Tensor, a_scale: torch.Tensor) -> torch.Tensor:
+    """e4m3 [T, K] with fp32 scales [T, K / 128] -> fp32 [T, K]."""
+    T, K = a8.shape
+    return (a8.float().view(T, K // 128, 128) * a_scale[:, :, None]).view(T, K)
+
+
+def dequant_fp8_weight_blocks(w8: torch.Tensor, w_scale: torch.Tensor) -> torch.Tensor:
+    """e4m3 [E, N, K] with fp32 scales [E, ceil(N / 128), K / 128] (one per 128 x 128 block) -> fp32 [E, N, K]."""
+    E, N, K = w8.shape
+    s = w_scale.repeat_interleave(128, dim=1)[:, :N].repeat_interleave(128, dim=2)
+    return w8.float() * s
+
+
+def grouped_gemm_fp8_ref(a8_rows: torch.Tensor, a_scale_rows: torch.Tensor, w8: torch.Tensor, w_scale: torch.Tensor,
+                         expert_of_row: torch.Tensor) -> torch.Tensor:
+    """Block-scaled fp8 grouped GEMM in fp32: out[i] = dequant(a8_rows[i]) @ dequant(w8[expert_of_row[i]]).T."""
+    return grouped_gemm_ref(dequant_fp8_rows(a8_rows, a_scale_rows), dequant_fp8_weight_blocks(w8, w_scale), expert_of_row)
+
+
 def ag_group_gemm_ref(a_local: torch.Tensor, w: torch.Tensor, full_topk_ids: torch.Tensor, group=None) -> torch.Tensor:
     """TP-MoE up-projection: tokens all-gathered, every (token, k) pair multiplied by its expert's weight shard.
     a_local [T / world, K]; w [E, N_local, K]; returns [T * topk, N_local] with row t * topk + k."""
