@@ -22,6 +22,7 @@
 #include "b200/primitives.cuh"
 #include "b200/tcgen05.cuh"
 
+#include <cstdlib>
 #include <cstring>
 
 namespace b200 {
@@ -258,6 +259,19 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   if (warp == 2) tmem_dealloc(tmem_base, tmem_cols);
 }
 
+// Shared memory per CTA for the weight ring. At about half of an SM's shared memory the first CTAs of the next
+// kernel of a programmatic-dependent-launch chain become resident (and prefetch their weights) while this kernel's
+// last tiles are still streaming. B200DIST_SKINNY_SMEM_KB overrides it.
+static int skinny_smem_budget() {
+  static int budget = -1;
+  if (budget < 0) {
+    const char* e = getenv("B200DIST_SKINNY_SMEM_KB");
+    int kb = e ? atoi(e) : 0;
+    budget = (kb >= 16 && kb * 1024 <= kSkSmemBudget) ? kb * 1024 : kSkSmemBudget;
+  }
+  return budget;
+}
+
 template <bool kDual>
 static int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const SkinnyParams& p, dim3 grid, int smem,
                          cudaStream_t stream) {
@@ -300,8 +314,9 @@ B200_API int b200_gemm_skinny(const void* X, const void* W, void* C, int M, int 
   B200_REQUIRE(!dual || p.MB <= 128, "fused SwiGLU handles at most 128 tokens");
   const int kw = dual ? 2 : 1;
   p.stage_bytes = kw * kSkWBytes + p.MB * 128;
-  p.stages = kSkSmemBudget / p.stage_bytes;
+  p.stages = skinny_smem_budget() / p.stage_bytes;
   if (p.stages > kSkMaxStages) p.stages = kSkMaxStages;
+  if (p.stages < 2) p.stages = kSkSmemBudget / p.stage_bytes < 2 ? 0 : 2;
   B200_REQUIRE(p.stages >= 2, "tile does not fit in shared memory");
   p.up_row0 = N;
   p.bf16 = dtype == kBF16;
