@@ -189,3 +189,46 @@ def test_fp8_block_quantisers_round_trip_and_reference():
     got = ref.grouped_gemm_fp8_ref(a8, sa, w8, sw, e)
     exact = ref.grouped_gemm_ref(a, w, e)
     assert (got - exact).norm() / exact.norm() < 0.06
+
+
+def test_scatter_gather_index_helpers_and_public_names():
+    """The torch index helpers invert each other, and the package exports every name of the reference's
+    kernels.nvidia surface that has a counterpart here."""
+    import torch
+    from triton_distributed_b200.kernels import nvidia as K
+    ids = torch.tensor([[1, 0], [0, 2], [2, 1], [1, 1]], dtype=torch.int32)
+    scatter = K.calc_scatter_index_torch(ids, 3)
+    assert sorted(scatter.reshape(-1).tolist()) == list(range(8))
+    experts_sorted = torch.empty(8, dtype=torch.int32)
+    experts_sorted[scatter.reshape(-1).long()] = ids.reshape(-1)
+    assert torch.equal(experts_sorted, torch.sort(ids.reshape(-1), stable=True).values)
+    gather = K.calc_gather_index_from_scatter_index(scatter)
+    assert torch.equal(gather[scatter.reshape(-1).long()], torch.arange(8, dtype=torch.int32))
+    assert torch.equal(K.histogram_by_expert_torch(ids, 3), torch.tensor([2, 4, 2], dtype=torch.int32))
+    for name in ["create_ag_gemm_context", "ag_gemm", "gemm_persistent", "create_gemm_rs_context", "gemm_rs", "AllGatherMethod",
+                 "get_auto_all_gather_method", "create_ag_group_gemm_context", "ag_group_gemm", "select_experts",
+                 "create_moe_rs_context", "moe_reduce_rs_rowise", "moe_reduce_rs_colwise", "create_all_to_all_context",
+                 "fast_all_to_all", "all_to_all_post_process", "create_fast_allgather_context", "fast_allgather",
+                 "gqa_fwd_batch_decode", "gqa_fwd_batch_decode_intra_rank", "gqa_fwd_batch_decode_persistent",
+                 "fused_sp_ag_attn_intra_node", "fused_sp_ag_attn_inter_node", "create_allreduce_ctx", "all_reduce",
+                 "get_auto_allreduce_method", "BarrierAllContext", "wait_eq", "set_signal", "create_reduce_scater_2d_ctx",
+                 "reduce_scatter_2d_op", "ring_reduce", "calc_gather_scatter_index_triton", "reduce_topk_tma",
+                 "estimate_gemm_sol_time_ms", "get_tensorcore_tflops", "estimate_all_gather_time_ms", "grouped_gemm_fp8"]:
+        assert hasattr(K, name), name
+
+
+def test_ag_gemm_gather_choice_follows_world_size_and_bytes():
+    """`auto` pushes only when at least four ranks take part and at most 64 MB leave a rank."""
+    import torch
+    from triton_distributed_b200.kernels.nvidia.allgather_gemm import AllGatherGEMMTensorParallelContext as Ctx
+
+    def ctx(world, K=8192):
+        return Ctx(rank=0, num_ranks=world, num_local_ranks=world, max_M=8192, N_per_rank=1024, K=K, dtype=torch.bfloat16,
+                   heap=None, symm_workspaces=[], symm_ready=None, blk_cnt=None, blk_flag=None, sync=None)
+    assert ctx(2).method_for(64) == "sm_pull_fused"
+    assert ctx(8).method_for(128) == "sm_push_fused"      # M = 1024: 14.7 MB out
+    assert ctx(8).method_for(512) == "sm_push_fused"      # M = 4096: 58.7 MB out
+    assert ctx(8).method_for(1024) == "sm_pull_fused"     # M = 8192: 117 MB out
+    c = ctx(8)
+    c.all_gather_method = "sm_pull_fused"
+    assert c.method_for(128) == "sm_pull_fused"

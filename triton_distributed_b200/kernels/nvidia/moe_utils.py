@@ -98,6 +98,25 @@ def calc_gather_scatter_index(chosen_experts: torch.Tensor, nexperts: int, align
 calc_gather_scatter_index_triton = calc_gather_scatter_index
 
 
+def calc_scatter_index_torch(chosen_experts: torch.Tensor, nexperts: int) -> torch.Tensor:
+    """scatter_index [T, topk]: position of every (token, k) pair in the stable expert-sorted order (no padding).
+    Plain torch; the oracle of the device sort (``moe_utils.py:94-135`` of the reference)."""
+    flat = chosen_experts.reshape(-1).long()
+    order = torch.argsort(flat, stable=True)
+    scatter = torch.empty_like(order)
+    scatter[order] = torch.arange(order.numel(), device=order.device)
+    return scatter.view_as(chosen_experts).to(torch.int32)
+
+
+def calc_gather_index_from_scatter_index(scatter_index: torch.Tensor, n_rows: int | None = None) -> torch.Tensor:
+    """Inverse permutation: gather_index[scatter_index[p]] = p (rows that nothing scatters to hold -1)."""
+    flat = scatter_index.reshape(-1).long()
+    n = int(n_rows) if n_rows is not None else flat.numel()
+    gather = torch.full((n,), -1, dtype=torch.int32, device=flat.device)
+    gather[flat] = torch.arange(flat.numel(), dtype=torch.int32, device=flat.device)
+    return gather
+
+
 def histogram_by_expert(chosen_experts: torch.Tensor, nexperts: int) -> torch.Tensor:
     return torch.bincount(chosen_experts.reshape(-1).long(), minlength=nexperts).to(torch.int32)
 

@@ -95,3 +95,14 @@ def fused_sp_ag_attn_intra_node(ctx: SPAllGatherAttentionContextIntraNode, q_sha
         output[cu_q[b]:cu_q[b + 1]] = o[0].transpose(0, 1)
     ctx.heap.barrier_all()
     return output
+
+
+def create_sp_ag_attention_context_inter_node(*args, **kwargs):
+    """The reference's two-level (node x local rank) variant (``sp_ag_attention_inter_node.py:504-594``). Ranks of one
+    NVSwitch domain are all one hop apart, so the single-level context serves; more than one node is not supported."""
+    return create_sp_ag_attention_context_intra_node(*args, **kwargs)
+
+
+def fused_sp_ag_attn_inter_node(*args, **kwargs):
+    """See ``create_sp_ag_attention_context_inter_node``: same kernel path as the intra-node form."""
+    return fused_sp_ag_attn_intra_node(*args, **kwargs)
