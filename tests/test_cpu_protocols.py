@@ -1,0 +1,187 @@
+"""Protocol models of the cross-rank handshakes, run under random schedules on the CPU.
+
+The fused kernels never reset a flag: buffers and counters that peers write are double-buffered by the parity of a
+device-resident epoch, counters only grow, and the value a waiter expects is `base + rows` with `base` advanced at the
+end of every call. Whether that is enough (no waiter passes early, no buffer is overwritten while it is still read)
+is a property of the protocol, not of the CUDA code, so it is checked here by executing a small model of every rank's
+producer and consumer threads under thousands of random interleavings. The same model with the parity removed must
+fail, which shows that the checker can see the hazard it is guarding against.
+
+What is modelled: the push gather of AG-GEMM (`csrc/kernels/gemm_sm100.cu`, communication warps and TMA producer) and
+the slot / counter scheme of GEMM-RS (epilogue stores, signalling warp, reduce phase).
+"""
+from __future__ import annotations
+
+import random
+
+import pytest
+
+
+class Violation(Exception):
+    pass
+
+
+def _run(threads, rng, max_steps=200000):
+    """threads: list of generators; each `yield` is a point where another thread may run. A generator yields False while
+    it is blocked on a condition (so that a schedule in which everybody is blocked is reported as a deadlock)."""
+    live = list(threads)
+    blocked_streak = 0
+    for _ in range(max_steps):
+        if not live:
+            return
+        t = rng.choice(live)
+        try:
+            progressed = next(t)
+        except StopIteration:
+            live.remove(t)
+            blocked_streak = 0
+            continue
+        blocked_streak = 0 if progressed is not False else blocked_streak + 1
+        if blocked_streak > 50 * len(live) + 50:
+            raise Violation("deadlock: every live thread is blocked")
+    raise Violation("schedule did not finish")
+
+
+# ---------------------------------------------------------------------------------------------- AG push gather
+def _ag_push_model(world, rows_per_rank, block, calls, rng, use_parity=True):
+    M = world * rows_per_rank
+    nblk = (M + block - 1) // block
+    npar = 2 if use_parity else 1
+    data = [[[None] * M for _ in range(npar)] for _ in range(world)]       # data[rank][parity][row] = (epoch, source)
+    cnt = [[[0] * nblk for _ in range(npar)] for _ in range(world)]        # symmetric counters, only ever grow
+    base = [[[0] * nblk for _ in range(npar)] for _ in range(world)]       # local
+    done_epoch = [0] * world                                              # device-resident epoch of each rank
+    finished = [[0, 0] for _ in range(world)]                             # [pusher, consumer] progress per rank
+
+    def rows_in_block(b):
+        return min(block, M - b * block)
+
+    def pusher(r):
+        for e in range(1, calls + 1):
+            while not (finished[r][0] == e - 1 and finished[r][1] == e - 1 and done_epoch[r] == e - 1):
+                yield False                                              # kernel e starts when kernel e - 1 has retired
+            par = e % npar
+            for step in range(world):                                    # step s goes to rank r - s
+                dst = (r - step) % world
+                for row in range(r * rows_per_rank, (r + 1) * rows_per_rank):
+                    data[dst][par][row] = (e, r)
+                    yield True
+                    cnt[dst][par][row // block] += 1                     # fence + red.release after the stores
+                    yield True
+            finished[r][0] = e
+            yield True
+
+    def consumer(r):
+        for e in range(1, calls + 1):
+            while not (finished[r][1] == e - 1 and done_epoch[r] == e - 1):
+                yield False
+            par = e % npar
+            first = (r * rows_per_rank) // block
+            for k in range(nblk):                                        # own rows first, then the ring order
+                b = (first + k) % nblk
+                want = base[r][par][b] + rows_in_block(b)
+                while cnt[r][par][b] < want:
+                    yield False
+                for row in range(b * block, b * block + rows_in_block(b)):
+                    got = data[r][par][row]
+                    if got != (e, row // rows_per_rank):
+                        raise Violation(f"rank {r} call {e} block {b} row {row}: read {got}")
+                    yield True
+            finished[r][1] = e
+            while finished[r][0] != e:                                   # last CTA out: both roles are done
+                yield False
+            for b in range(nblk):
+                base[r][par][b] += rows_in_block(b)
+            done_epoch[r] = e
+            yield True
+
+    _run([pusher(r) for r in range(world)] + [consumer(r) for r in range(world)], rng)
+
+
+@pytest.mark.parametrize("world,rows,block", [(2, 2, 2), (3, 3, 2), (4, 2, 3), (2, 5, 4)])
+def test_ag_push_gather_protocol_is_safe_under_random_schedules(world, rows, block):
+    for seed in range(150):
+        _ag_push_model(world, rows, block, calls=5, rng=random.Random(seed))
+
+
+def test_ag_push_gather_without_parity_is_caught():
+    """One buffer and one counter set: a fast rank's next call overwrites rows (or inflates counters of blocks that
+    straddle two sources) while a slow rank is still in the previous call. The checker must find it."""
+    failures = 0
+    for seed in range(150):
+        try:
+            _ag_push_model(3, 3, 2, calls=5, rng=random.Random(seed), use_parity=False)
+        except Violation:
+            failures += 1
+    assert failures > 0
+
+
+# ---------------------------------------------------------------------------------------------- GEMM-RS slots + counters
+def _gemm_rs_model(world, rows_per_rank, tiles_n, calls, rng, use_parity=True):
+    """Every rank computes a partial of every row and column tile, stores it into the owner's slot [source][row][tile],
+    and adds the delivered rows to the owner's counter for that source; the owner sums the slots of a row block once
+    every source has delivered `rows * tiles_n`."""
+    npar = 2 if use_parity else 1
+    slots = [[[[[None] * tiles_n for _ in range(rows_per_rank)] for _ in range(world)] for _ in range(npar)] for _ in range(world)]
+    cnt = [[0] * world for _ in range(world)]        # cnt[owner][source], only ever grows (not parity-split: see below)
+    base = [[0] * world for _ in range(world)]
+    done_epoch = [0] * world
+    finished = [[0, 0] for _ in range(world)]
+
+    def producer(r):
+        for e in range(1, calls + 1):
+            while not (finished[r][0] == e - 1 and finished[r][1] == e - 1 and done_epoch[r] == e - 1):
+                yield False
+            par = e % npar
+            for step in range(1, world + 1):          # the segment after this rank's first, its own last
+                owner = (r + step) % world
+                for t in range(tiles_n):
+                    for row in range(rows_per_rank):
+                        slots[owner][par][r][row][t] = (e, r)
+                        yield True
+                    cnt[owner][r] += rows_per_rank    # signalling warp: fence, then red.release
+                    yield True
+            finished[r][0] = e
+            yield True
+
+    def reducer(r):
+        for e in range(1, calls + 1):
+            while not (finished[r][0] == e and done_epoch[r] == e - 1):   # the reduce phase follows the GEMM tiles
+                yield False
+            par = e % npar
+            for s in range(world):
+                while cnt[r][s] < base[r][s] + rows_per_rank * tiles_n:
+                    yield False
+            for s in range(world):
+                for row in range(rows_per_rank):
+                    for t in range(tiles_n):
+                        got = slots[r][par][s][row][t]
+                        if got != (e, s):
+                            raise Violation(f"rank {r} call {e}: slot of source {s} row {row} tile {t} holds {got}")
+                        yield True
+            for s in range(world):
+                base[r][s] += rows_per_rank * tiles_n
+            finished[r][1] = e
+            done_epoch[r] = e
+            yield True
+
+    _run([producer(r) for r in range(world)] + [reducer(r) for r in range(world)], rng)
+
+
+@pytest.mark.parametrize("world,rows,tiles", [(2, 2, 2), (3, 2, 2), (4, 1, 3)])
+def test_gemm_rs_slot_protocol_is_safe_under_random_schedules(world, rows, tiles):
+    """A source can run at most one call ahead of an owner (its call e + 1 cannot end before the owner has delivered
+    its rows of call e + 1, i.e. has finished call e), so parity slots plus growing counters are enough: the counter
+    of (owner, source) reaches `base + rows * tiles` exactly when the source's stores of THIS call have landed."""
+    for seed in range(150):
+        _gemm_rs_model(world, rows, tiles, calls=5, rng=random.Random(seed))
+
+
+def test_gemm_rs_single_slot_buffer_is_caught():
+    failures = 0
+    for seed in range(150):
+        try:
+            _gemm_rs_model(3, 2, 2, calls=5, rng=random.Random(seed), use_parity=False)
+        except Violation:
+            failures += 1
+    assert failures > 0

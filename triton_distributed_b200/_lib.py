@@ -62,9 +62,21 @@ def check(fn_name: str, code: int) -> None:
         raise NativeError(fn_name, code, msg.decode() if msg else "")
 
 
+_NVTX = os.environ.get("B200DIST_NVTX", "0") == "1"
+
+
 def call(fn_name: str, *args) -> None:
-    """Call a native function that returns an int status and raise on failure."""
+    """Call a native function that returns an int status and raise on failure. With ``B200DIST_NVTX=1`` every
+    launcher call is wrapped in an NVTX range named after the entry point, so the fused kernels show up by name in a
+    timeline next to the library kernels around them."""
     fn = getattr(load(), fn_name)
+    if _NVTX:
+        torch.cuda.nvtx.range_push(fn_name)
+        try:
+            check(fn_name, fn(*args))
+        finally:
+            torch.cuda.nvtx.range_pop()
+        return
     check(fn_name, fn(*args))
 
 

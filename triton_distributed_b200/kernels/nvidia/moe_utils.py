@@ -2,9 +2,10 @@
 
 API parity with ``python/triton_dist/kernels/nvidia/moe_utils.py`` (``calc_gather_scatter_index_triton`` :218,
 ``histogram_by_expert_*`` :32-38, ``reduce_topk_*`` :251-394) and with the CUDA op
-``moe_ag_scatter_align_block_size`` (``csrc/lib/moe_utils.cu``). One launch of ``csrc/kernels/moe_align.cu`` sorts
-the (token, k) pairs by expert (optionally inside every source-rank block), pads every run to the tile height and
-emits the per-tile metadata the grouped GEMMs read; nothing synchronises with the host.
+``moe_ag_scatter_align_block_size`` (``csrc/lib/moe_utils.cu``). Four short launches of ``csrc/kernels/moe_align.cu``
+(count, prefix, offsets, scatter) sort the (token, k) pairs by expert (optionally inside every source-rank block), pad
+every run to the tile height and emit the per-tile metadata the grouped GEMMs read; nothing synchronises with the
+host, nothing allocates, and no kernel waits on another CTA.
 """
 from __future__ import annotations
 
