@@ -130,8 +130,14 @@ def ag_gemm(a: torch.Tensor, b: torch.Tensor, ctx: AllGatherGEMMTensorParallelCo
         raise ValueError(f"problem [{M},{K}] exceeds the context ([{ctx.max_M},{ctx.K}])")
     if not a.is_contiguous() or b.stride(1) != 1:
         raise ValueError("a must be contiguous and b row-major")
+    if b.shape[1] != K:
+        raise ValueError(f"a [{Mr},{K}] and b [{N},{b.shape[1]}] disagree on K")
+    if a.dtype != ctx.dtype or b.dtype != a.dtype:
+        raise TypeError(f"a ({a.dtype}) and b ({b.dtype}) must have the context's dtype ({ctx.dtype})")
     if out is None:
         out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    elif tuple(out.shape) != (M, N) or out.dtype != a.dtype or out.stride(1) != 1:
+        raise ValueError("out must be a row-major [M, N] tensor of the input dtype")
     if straggler_option is not None and straggler_option[0] == ctx.rank:
         torch.cuda._sleep(int(straggler_option[1]))
     _lib.call("b200_ag_gemm", ctx.heap.ctx, ptr(a), ptr(ctx.symm_workspaces[0]), ptr(ctx.symm_workspaces[1]), ptr(b),

@@ -79,8 +79,15 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, ctx: GEMMReduceScatterTensorParall
         raise ValueError("M must be divisible by the world size")
     if a.stride(1) != 1 or b.stride(1) != 1:
         raise ValueError("a and b must be row-major")
+    if b.shape[1] != K:
+        raise ValueError(f"a [{M},{K}] and b [{N},{b.shape[1]}] disagree on K")
+    if a.dtype != ctx.output_dtype or b.dtype != a.dtype:
+        raise TypeError(f"a ({a.dtype}) and b ({b.dtype}) must have the context's dtype ({ctx.output_dtype}): the slots "
+                        "that peers write hold the output dtype")
     if out is None:
         out = torch.empty((M // ctx.world_size, N), dtype=ctx.output_dtype, device=a.device)
+    elif tuple(out.shape) != (M // ctx.world_size, N) or out.dtype != ctx.output_dtype or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [M / world, N] tensor of the context's dtype")
     _lib.call("b200_gemm_rs", ctx.heap.ctx, ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0),
               dtype_code(a.dtype), ptr(ctx.slots[0]), ptr(ctx.slots[1]), ptr(ctx.rs_cnt), ptr(ctx.rs_base), ptr(ctx.sync),
               ctx.max_M // ctx.world_size, ctx.rs_blocks, ctx.group_m, ctx.max_ctas, stream_ptr())
