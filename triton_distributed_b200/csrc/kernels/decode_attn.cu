@@ -13,6 +13,7 @@
 #include "b200/host.h"
 #include "b200/primitives.cuh"
 
+#include <cstdlib>
 #include <cstring>
 
 namespace b200 {
@@ -296,6 +297,257 @@ __global__ void __launch_bounds__(kAttnThreads) decode_split_kernel(const Decode
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Variant with one private cp.async ring per warp (opt-in: B200DIST_ATTN_V2=1).
+//
+// The kernel above keeps at most one 32 KB tile per CTA in flight while it computes the other one; with three CTAs
+// per SM that is ~96 KB in flight per SM, and the measured 0.57 of the copy peak is what Little's law gives for that
+// at the loaded HBM latency (the decode GEMM needs its 216 KB ring to reach 0.87). Here every warp streams its own
+// 16-token slices (4 KB of K + 4 KB of V) through a ring of kNST slots without any CTA-wide barrier in the loop:
+// 4 warps x (kNST - 1) slices x 8 KB in flight per CTA (160 KB with kNST = 6 and one CTA per SM, 2 x 64 KB with
+// kNST = 3 and two). Warp w takes slices w, w + 4, w + 8, ... so that the four warps together read consecutive
+// 64-token tiles. The arithmetic per slice and the final merge of the four warps are those of the kernel above.
+template <bool BF16, int kNST>
+__global__ void __launch_bounds__(kAttnThreads) decode_split_ring_kernel(const DecodeParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  griddep_launch_dependents();
+  griddep_wait();
+  constexpr int kSlice = 16;                      // tokens per slice
+  constexpr int kSliceBytes = kSlice * kD * 2;    // 4 KB (K or V)
+  const int split = blockIdx.x, b = blockIdx.z;
+  const int G = p.Hq / p.Hkv;
+  const int hgroups = (G + 15) / 16;
+  const int kvh = blockIdx.y / hgroups, hg = blockIdx.y - kvh * hgroups;
+  const int head0 = kvh * G + hg * 16;
+  const int nrows = min(16, G - hg * 16);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_len = p.kv_lens[b];
+  int chunk = (kv_len + p.S - 1) / p.S;
+  chunk = (chunk + kTile - 1) / kTile * kTile;
+  const int t0 = split * chunk;
+  const int t1 = min(kv_len, t0 + chunk);
+  const int r_lo = lane >> 2, r_hi = r_lo + 8;
+
+  if (t0 >= t1) {  // empty split: mark it so that the combine skips it
+    if (!p.direct) {
+      for (int r = threadIdx.x; r < nrows; r += blockDim.x)
+        p.lse_part[(static_cast<size_t>(b) * p.Hq + head0 + r) * p.S + split] = -INFINITY;
+    } else {
+      for (int i = threadIdx.x; i < nrows * kD; i += blockDim.x) {
+        const size_t o = (static_cast<size_t>(b) * p.Hq + head0 + i / kD) * kD + (i % kD);
+        if (BF16) static_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16(0.f);
+        else static_cast<__half*>(p.out)[o] = __float2half(0.f);
+      }
+      if (p.out_lse)
+        for (int r = threadIdx.x; r < nrows; r += blockDim.x) p.out_lse[static_cast<size_t>(b) * p.Hq + head0 + r] = -INFINITY;
+    }
+    return;
+  }
+
+  uint32_t qa[8][4];
+  {
+    const uint32_t* q32 = static_cast<const uint32_t*>(p.q);
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      const int c = kk * 16 + (lane & 3) * 2;
+      const size_t base_lo = ((static_cast<size_t>(b) * p.Hq + head0 + r_lo) * kD + c) / 2;
+      const size_t base_hi = ((static_cast<size_t>(b) * p.Hq + head0 + r_hi) * kD + c) / 2;
+      qa[kk][0] = r_lo < nrows ? q32[base_lo] : 0u;
+      qa[kk][1] = r_hi < nrows ? q32[base_hi] : 0u;
+      qa[kk][2] = r_lo < nrows ? q32[base_lo + 4] : 0u;
+      qa[kk][3] = r_hi < nrows ? q32[base_hi + 4] : 0u;
+    }
+  }
+
+  // this warp's ring: slot s holds K at +0 and V at +kSliceBytes
+  const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + warp * (kNST * 2 * kSliceBytes);
+  const uint8_t* kc = static_cast<const uint8_t*>(p.k_cache);
+  const uint8_t* vc = static_cast<const uint8_t*>(p.v_cache);
+  const int nslices_cta = (t1 - t0 + kSlice - 1) / kSlice;
+  const int my_slices = nslices_cta > warp ? (nslices_cta - warp + 3) / 4 : 0;   // slices warp, warp + 4, ...
+  const bool page_fast = (p.page % kSlice) == 0;   // a 16-token slice never crosses a page (t0 is a multiple of 64)
+
+  auto load_slice = [&](int j) {   // j-th slice of this warp; always commits a group so that the counting stays uniform
+    if (j < my_slices) {
+      const int st0 = t0 + (warp + 4 * j) * kSlice;
+      const uint32_t slot = ring + (j % kNST) * (2 * kSliceBytes);
+      size_t slot0 = 0;
+      if (page_fast) {
+        const int blk = p.block_table[static_cast<size_t>(b) * p.bt_stride + st0 / p.page];
+        slot0 = static_cast<size_t>(blk) * p.page + st0 % p.page;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int tok_in = i * 2 + (lane >> 4);
+        const int c = lane & 15;
+        const int tok = st0 + tok_in;
+        const bool valid = tok < t1;
+        size_t off = 0;
+        if (valid) {
+          size_t sl;
+          if (page_fast) {
+            sl = slot0 + tok_in;
+          } else {
+            const int blk = p.block_table[static_cast<size_t>(b) * p.bt_stride + tok / p.page];
+            sl = static_cast<size_t>(blk) * p.page + tok % p.page;
+          }
+          off = ((sl * p.Hkv + kvh) * kD + c * 8) * 2;
+        }
+        const uint32_t so = tok_in * 256 + ((c ^ (tok_in & 7)) * 16);
+        cp_async_16(slot + so, kc + off, valid ? 16 : 0);
+        cp_async_16(slot + kSliceBytes + so, vc + off, valid ? 16 : 0);
+      }
+    }
+    cp_async_commit();
+  };
+
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float oacc[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) oacc[i][e] = 0.f;
+
+  const float kLog2e = 1.4426950408889634f;
+#pragma unroll
+  for (int j = 0; j < kNST - 1; ++j) load_slice(j);
+  for (int j = 0; j < my_slices; ++j) {
+    load_slice(j + kNST - 1);        // into the slot that was computed in the previous iteration
+    cp_async_wait<kNST - 1>();       // slice j has landed (for this lane); the barrier below covers the other lanes
+    __syncwarp();
+    const uint32_t ks = ring + (j % kNST) * (2 * kSliceBytes), vs = ks + kSliceBytes;
+    const int wt0 = t0 + (warp + 4 * j) * kSlice;  // first token of this slice
+    // ---- S = Q K^T for 16 tokens ----
+    float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      const int m = lane >> 3, r = lane & 7;
+      const int tok_in = (m >> 1) * 8 + r;
+      const int c = 2 * kk + (m & 1);
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4(ks + tok_in * 256 + ((c ^ (tok_in & 7)) * 16), b0, b1, b2, b3);
+      mma16816<BF16>(sacc[0], qa[kk], b0, b1);
+      mma16816<BF16>(sacc[1], qa[kk], b2, b3);
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = sacc[nb][e] * p.scale;
+        if (p.soft_cap > 0.f) v = p.soft_cap * tanhf(v / p.soft_cap);
+        v *= kLog2e;
+        const int tok = wt0 + nb * 8 + (lane & 3) * 2 + (e & 1);
+        v = tok < t1 ? v : -INFINITY;
+        sacc[nb][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    uint32_t pa[4];
+    float pr[2][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m_run[h], mx[h]);
+      const float base = m_new == -INFINITY ? 0.f : m_new;
+      const float corr = exp2f(m_run[h] - base);  // m_run = -inf -> 0
+      m_run[h] = m_new;
+      float sum = 0.f;
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float pv = exp2f(sacc[nb][2 * h + e] - base);
+          pr[nb][2 * h + e] = pv;
+          sum += pv;
+        }
+      l_run[h] = l_run[h] * corr + sum;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        oacc[i][2 * h] *= corr;
+        oacc[i][2 * h + 1] *= corr;
+      }
+    }
+    if (BF16) {
+      pa[0] = pack_bf16x2(pr[0][0], pr[0][1]); pa[1] = pack_bf16x2(pr[0][2], pr[0][3]);
+      pa[2] = pack_bf16x2(pr[1][0], pr[1][1]); pa[3] = pack_bf16x2(pr[1][2], pr[1][3]);
+    } else {
+      pa[0] = pack_f16x2(pr[0][0], pr[0][1]); pa[1] = pack_f16x2(pr[0][2], pr[0][3]);
+      pa[2] = pack_f16x2(pr[1][0], pr[1][1]); pa[3] = pack_f16x2(pr[1][2], pr[1][3]);
+    }
+#pragma unroll
+    for (int dn = 0; dn < 8; ++dn) {
+      const int m = lane >> 3, r = lane & 7;
+      const int tok_in = (m & 1) * 8 + r;
+      const int c = 2 * dn + (m >> 1);
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4_trans(vs + tok_in * 256 + ((c ^ (tok_in & 7)) * 16), b0, b1, b2, b3);
+      mma16816<BF16>(oacc[2 * dn], pa, b0, b1);
+      mma16816<BF16>(oacc[2 * dn + 1], pa, b2, b3);
+    }
+    __syncwarp();  // every lane is done with this slot before the next iteration's copies overwrite the previous one
+  }
+  cp_async_wait<0>();
+  __syncthreads();   // all rings are idle: their memory becomes the merge area
+
+  // ---- merge the four warps ----
+  float* red_m = reinterpret_cast<float*>(smem);            // [4][16]
+  float* red_l = red_m + 64;                                // [4][16]
+  float* red_o = red_l + 64;                                // [4][16][128]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+  if ((lane & 3) == 0) {
+    red_m[warp * 16 + r_lo] = m_run[0];
+    red_m[warp * 16 + r_hi] = m_run[1];
+    red_l[warp * 16 + r_lo] = l_run[0];
+    red_l[warp * 16 + r_hi] = l_run[1];
+  }
+  __syncthreads();
+  float scale_w[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = h ? r_hi : r_lo;
+    float mg = fmaxf(fmaxf(red_m[r], red_m[16 + r]), fmaxf(red_m[32 + r], red_m[48 + r]));
+    scale_w[h] = m_run[h] == -INFINITY ? 0.f : exp2f(m_run[h] - mg);
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int c = i * 8 + (lane & 3) * 2;
+    float* lo = red_o + (warp * 16 + r_lo) * kD + c;
+    float* hi = red_o + (warp * 16 + r_hi) * kD + c;
+    lo[0] = oacc[i][0] * scale_w[0];
+    lo[1] = oacc[i][1] * scale_w[0];
+    hi[0] = oacc[i][2] * scale_w[1];
+    hi[1] = oacc[i][3] * scale_w[1];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < nrows * kD; i += blockDim.x) {
+    const int r = i / kD, c = i - r * kD;
+    float mg = fmaxf(fmaxf(red_m[r], red_m[16 + r]), fmaxf(red_m[32 + r], red_m[48 + r]));
+    float lg = 0.f, og = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = red_m[w * 16 + r];
+      lg += mw == -INFINITY ? 0.f : red_l[w * 16 + r] * exp2f(mw - mg);
+      og += red_o[(w * 16 + r) * kD + c];
+    }
+    const float o = lg > 0.f ? og / lg : 0.f;
+    const size_t bh = static_cast<size_t>(b) * p.Hq + head0 + r;
+    const float lse = lg > 0.f ? mg * 0.6931471805599453f + logf(lg) : -INFINITY;
+    if (p.direct) {
+      if (BF16) static_cast<__nv_bfloat16*>(p.out)[bh * kD + c] = __float2bfloat16(o);
+      else static_cast<__half*>(p.out)[bh * kD + c] = __float2half(o);
+      if (c == 0 && p.out_lse) p.out_lse[bh] = lse;
+    } else {
+      p.o_part[(bh * p.S + split) * kD + c] = o;
+      if (c == 0) p.lse_part[bh * p.S + split] = lse;
+    }
+  }
+}
+
 // out[bh, :] = sum_s w_s o[bh, s, :] / sum_s w_s with w_s = exp(lse_s - max lse); partials with
 // lse = -inf are skipped. Strides are in elements so the same kernel merges split partials
 // ([B*Hq, S, D]) and the all-gathered per-rank partials of sequence-parallel decode ([R, B*Hq, D(+1)]).
@@ -324,6 +576,17 @@ __global__ void __launch_bounds__(kD) decode_combine_kernel(const float* o_part,
   }
   if (out_f32) out_f32[static_cast<size_t>(bh) * kD + c] = o;
   if (c == 0 && out_lse) out_lse[bh] = lg > 0.f ? mg + logf(lg) : -INFINITY;
+}
+
+// 0 = the two-stage CTA-wide pipeline (default); 3 or 6 = per-warp rings of that depth (B200DIST_ATTN_V2=3|6, 1 -> 6).
+static int attn_ring_stages() {
+  static int stages = -1;
+  if (stages < 0) {
+    const char* e = getenv("B200DIST_ATTN_V2");
+    const int v = e ? atoi(e) : 0;
+    stages = v == 3 ? 3 : (v == 6 || v == 1) ? 6 : 0;
+  }
+  return stages;
 }
 
 }  // namespace b200
@@ -360,6 +623,27 @@ B200_API int b200_decode_attn_split(const void* q, const void* k_cache, const vo
   const int G = Hq / Hkv;
   dim3 grid(num_splits, Hkv * ((G + 15) / 16), B);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int ring = attn_ring_stages();
+  if (ring > 0) {
+    // per-warp rings: 4 warps x stages x 8 KB, never less than the 33 KB merge area
+    const int smem = 4 * ring * 8192 < 34 * 1024 ? 34 * 1024 : 4 * ring * 8192;
+    static bool ring_configured[64] = {false};
+    if (!ring_configured[dev & 63]) {
+      B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_ring_kernel<true, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+      B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_ring_kernel<false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+      B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_ring_kernel<true, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024));
+      B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_ring_kernel<false, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024));
+      ring_configured[dev & 63] = true;
+    }
+    if (ring == 3) {
+      if (dtype == kBF16) B200_CHECK_CUDA(launch_pdl(decode_split_ring_kernel<true, 3>, grid, kAttnThreads, smem, s, p));
+      else B200_CHECK_CUDA(launch_pdl(decode_split_ring_kernel<false, 3>, grid, kAttnThreads, smem, s, p));
+    } else {
+      if (dtype == kBF16) B200_CHECK_CUDA(launch_pdl(decode_split_ring_kernel<true, 6>, grid, kAttnThreads, smem, s, p));
+      else B200_CHECK_CUDA(launch_pdl(decode_split_ring_kernel<false, 6>, grid, kAttnThreads, smem, s, p));
+    }
+    return kOk;
+  }
   if (dtype == kBF16) B200_CHECK_CUDA(launch_pdl(decode_split_kernel<true>, grid, kAttnThreads, kAttnSmem, s, p));
   else B200_CHECK_CUDA(launch_pdl(decode_split_kernel<false>, grid, kAttnThreads, kAttnSmem, s, p));
   return kOk;
