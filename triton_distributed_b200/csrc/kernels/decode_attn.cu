@@ -37,6 +37,7 @@ struct DecodeParams {
   int bt_stride, Hq, Hkv, page, S;
   float scale, soft_cap;
   int direct;
+  uint32_t* tickets;    // fused combine only: one self-resetting counter per (batch, head group)
 };
 
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
@@ -67,7 +68,44 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
   }
 }
 
+// Fused combine (opt-in): every CTA of a (batch, head group) draws a ticket after its partial is visible; the CTA
+// that draws the last one merges all S partials (the arithmetic of decode_combine_kernel) and writes the final rows,
+// so the separate combine launch disappears. The ticket resets itself for the next call.
 template <bool BF16>
+__device__ __forceinline__ void combine_by_last_cta(const DecodeParams& p, int b, int head0, int nrows) {
+  __shared__ uint32_t is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t* ticket = p.tickets + static_cast<size_t>(b) * gridDim.y + blockIdx.y;
+    const uint32_t t = atomicAdd(ticket, 1u);
+    is_last = t == static_cast<uint32_t>(p.S - 1) ? 1u : 0u;
+    if (is_last) *ticket = 0u;  // every CTA of the group has arrived
+  }
+  __syncthreads();
+  if (is_last == 0u) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < nrows * kD; i += blockDim.x) {
+    const int r = i / kD, c = i - r * kD;
+    const size_t bh = static_cast<size_t>(b) * p.Hq + head0 + r;
+    float mg = -INFINITY;
+    for (int sp = 0; sp < p.S; ++sp) mg = fmaxf(mg, __ldcg(p.lse_part + bh * p.S + sp));
+    float lg = 0.f, og = 0.f;
+    for (int sp = 0; sp < p.S; ++sp) {
+      const float lse = __ldcg(p.lse_part + bh * p.S + sp);
+      if (lse == -INFINITY) continue;
+      const float w = __expf(lse - mg);
+      lg += w;
+      og += w * __ldcg(p.o_part + (bh * p.S + sp) * kD + c);
+    }
+    const float o = lg > 0.f ? og / lg : 0.f;
+    if (BF16) static_cast<__nv_bfloat16*>(p.out)[bh * kD + c] = __float2bfloat16(o);
+    else static_cast<__half*>(p.out)[bh * kD + c] = __float2half(o);
+    if (c == 0 && p.out_lse) p.out_lse[bh] = lg > 0.f ? mg + logf(lg) : -INFINITY;
+  }
+}
+
+template <bool BF16, bool FUSE = false>
 __global__ void __launch_bounds__(kAttnThreads) decode_split_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   griddep_launch_dependents();
@@ -90,6 +128,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_split_kernel(const Decode
     if (!p.direct) {
       for (int r = threadIdx.x; r < nrows; r += blockDim.x)
         p.lse_part[(static_cast<size_t>(b) * p.Hq + head0 + r) * p.S + split] = -INFINITY;
+      if (FUSE) combine_by_last_cta<BF16>(p, b, head0, nrows);
     } else {
       for (int i = threadIdx.x; i < nrows * kD; i += blockDim.x) {
         const size_t o = (static_cast<size_t>(b) * p.Hq + head0 + i / kD) * kD + (i % kD);
@@ -295,6 +334,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_split_kernel(const Decode
       if (c == 0) p.lse_part[bh * p.S + split] = lse;
     }
   }
+  if (FUSE && !p.direct) combine_by_last_cta<BF16>(p, b, head0, nrows);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -307,7 +347,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_split_kernel(const Decode
 // 4 warps x (kNST - 1) slices x 8 KB in flight per CTA (160 KB with kNST = 6 and one CTA per SM, 2 x 64 KB with
 // kNST = 3 and two). Warp w takes slices w, w + 4, w + 8, ... so that the four warps together read consecutive
 // 64-token tiles. The arithmetic per slice and the final merge of the four warps are those of the kernel above.
-template <bool BF16, int kNST>
+template <bool BF16, int kNST, bool FUSE = false>
 __global__ void __launch_bounds__(kAttnThreads) decode_split_ring_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   griddep_launch_dependents();
@@ -332,6 +372,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_split_ring_kernel(const D
     if (!p.direct) {
       for (int r = threadIdx.x; r < nrows; r += blockDim.x)
         p.lse_part[(static_cast<size_t>(b) * p.Hq + head0 + r) * p.S + split] = -INFINITY;
+      if (FUSE) combine_by_last_cta<BF16>(p, b, head0, nrows);
     } else {
       for (int i = threadIdx.x; i < nrows * kD; i += blockDim.x) {
         const size_t o = (static_cast<size_t>(b) * p.Hq + head0 + i / kD) * kD + (i % kD);
@@ -546,6 +587,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_split_ring_kernel(const D
       if (c == 0) p.lse_part[bh * p.S + split] = lse;
     }
   }
+  if (FUSE && !p.direct) combine_by_last_cta<BF16>(p, b, head0, nrows);
 }
 
 // out[bh, :] = sum_s w_s o[bh, s, :] / sum_s w_s with w_s = exp(lse_s - max lse); partials with
@@ -646,6 +688,55 @@ B200_API int b200_decode_attn_split(const void* q, const void* k_cache, const vo
   }
   if (dtype == kBF16) B200_CHECK_CUDA(launch_pdl(decode_split_kernel<true>, grid, kAttnThreads, kAttnSmem, s, p));
   else B200_CHECK_CUDA(launch_pdl(decode_split_kernel<false>, grid, kAttnThreads, kAttnSmem, s, p));
+  return kOk;
+}
+
+// Split-KV attention with the combine fused into the last CTA of every (batch, head group): same arguments as
+// b200_decode_attn_split with num_splits > 1, plus `tickets` u32 [B * Hkv * ceil(G / 16)] (zero-initialised once; the
+// kernel leaves it zeroed). Writes `out` (and out_lse) directly; no b200_decode_combine call follows.
+B200_API int b200_decode_attn_fused(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                                    int bt_stride, const int* kv_lens, int B, int Hq, int Hkv, int head_dim, int page,
+                                    float scale, float soft_cap, int num_splits, float* o_part, float* lse_part,
+                                    uint32_t* tickets, void* out, float* out_lse, int dtype, void* stream) {
+  B200_REQUIRE(dtype == kBF16 || dtype == kF16, "decode attention supports bf16/f16");
+  B200_REQUIRE(head_dim == kD, "decode attention is specialised for head_dim 128, got %d", head_dim);
+  B200_REQUIRE(Hkv > 0 && Hq % Hkv == 0, "Hq (%d) must be a multiple of Hkv (%d)", Hq, Hkv);
+  B200_REQUIRE(num_splits >= 2 && page >= 1, "the fused combine is for num_splits >= 2");
+  B200_REQUIRE(o_part && lse_part && tickets && out, "partial buffers, tickets and out are required");
+  if (B == 0) return kOk;
+  int dev = 0;
+  B200_CHECK_CUDA(cudaGetDevice(&dev));
+  static bool configured[64] = {false};
+  if (!configured[dev & 63]) {
+    B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
+    B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
+    B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_ring_kernel<true, 3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_ring_kernel<false, 3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_ring_kernel<true, 6, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024));
+    B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_ring_kernel<false, 6, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024));
+    configured[dev & 63] = true;
+  }
+  DecodeParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.block_table = block_table; p.kv_lens = kv_lens;
+  p.o_part = o_part; p.lse_part = lse_part; p.out = out; p.out_lse = out_lse; p.tickets = tickets;
+  p.bt_stride = bt_stride; p.Hq = Hq; p.Hkv = Hkv; p.page = page; p.S = num_splits;
+  p.scale = scale; p.soft_cap = soft_cap; p.direct = 0;
+  const int G = Hq / Hkv;
+  dim3 grid(num_splits, Hkv * ((G + 15) / 16), B);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int ring = attn_ring_stages();
+  const bool bf = dtype == kBF16;
+  if (ring == 3) {
+    if (bf) B200_CHECK_CUDA(launch_pdl(decode_split_ring_kernel<true, 3, true>, grid, kAttnThreads, 96 * 1024, s, p));
+    else B200_CHECK_CUDA(launch_pdl(decode_split_ring_kernel<false, 3, true>, grid, kAttnThreads, 96 * 1024, s, p));
+  } else if (ring == 6) {
+    if (bf) B200_CHECK_CUDA(launch_pdl(decode_split_ring_kernel<true, 6, true>, grid, kAttnThreads, 192 * 1024, s, p));
+    else B200_CHECK_CUDA(launch_pdl(decode_split_ring_kernel<false, 6, true>, grid, kAttnThreads, 192 * 1024, s, p));
+  } else {
+    if (bf) B200_CHECK_CUDA(launch_pdl(decode_split_kernel<true, true>, grid, kAttnThreads, kAttnSmem, s, p));
+    else B200_CHECK_CUDA(launch_pdl(decode_split_kernel<false, true>, grid, kAttnThreads, kAttnSmem, s, p));
+  }
   return kOk;
 }
 

@@ -11,6 +11,7 @@ Replaces in the reference: cuBLAS ``F.linear``, ``flashinfer.norm.rmsnorm``,
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -192,6 +193,10 @@ def top_p_sample(logits: torch.Tensor, temperature: float, top_p: float, uniform
     return out
 
 
+_ATTN_FUSED_COMBINE = os.environ.get("B200DIST_ATTN_FUSED_COMBINE", "0") == "1"
+_attn_tickets: dict = {}
+
+
 def choose_kv_splits(batch: int, num_kv_heads: int, group: int, max_kv_len: int, sm_count: int = 148) -> int:
     """Split count so that batch x kv-heads x splits fills the machine about twice, with >= 256 tokens per split."""
     ctas = batch * num_kv_heads * ((group + 15) // 16)
@@ -223,6 +228,20 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                 workspace["o_part"], workspace["lse_part"] = o_part, lse_part
     else:
         o_part = lse_part = None
+    if num_splits > 1 and _ATTN_FUSED_COMBINE:
+        # opt-in: the last CTA of every (batch, head group) merges the splits, so no combine launch follows
+        G = Hq // Hkv
+        n_groups = B * Hkv * ((G + 15) // 16)
+        holder = workspace if workspace is not None else _attn_tickets
+        tickets = holder.get("tickets")
+        if tickets is None or tickets.numel() < n_groups or tickets.device != q.device:
+            tickets = torch.zeros(max(n_groups, 1024), dtype=torch.int32, device=q.device)
+            holder["tickets"] = tickets
+        _lib.call("b200_decode_attn_fused", ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.stride(0),
+                  ptr(kv_lens), B, Hq, Hkv, D, page, c_float(scale), c_float(soft_cap), num_splits, ptr(o_part),
+                  ptr(lse_part), ptr(tickets), ptr(out), ptr(lse), dtype_code(q.dtype), stream_ptr())
+        _count()
+        return (out, lse) if return_lse else out
     _lib.call("b200_decode_attn_split", ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.stride(0),
               ptr(kv_lens), B, Hq, Hkv, D, page, c_float(scale), c_float(soft_cap), num_splits, ptr(o_part),
               ptr(lse_part), ptr(out), ptr(lse), dtype_code(q.dtype), stream_ptr())
