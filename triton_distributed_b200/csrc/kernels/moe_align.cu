@@ -19,6 +19,7 @@
 #include "b200/host.h"
 #include "b200/primitives.cuh"
 
+#include <cstdlib>
 #include <cstring>
 
 namespace b200 {
@@ -169,6 +170,115 @@ __global__ void __launch_bounds__(kChunk) moe_scatter_kernel(const MoeSortParams
   }
 }
 
+// ---- small problems in ONE launch (opt-in: B200DIST_MOE_SORT_SMALL=1): at most 8192 pairs and 1024 (segment, expert)
+// groups. One CTA of 32 warps; warp w owns a contiguous block of pairs and counts them per group in its own row of a
+// shared [32][G] table (one leader lane per distinct group and 32-pair chunk, so no atomics), which also gives every
+// pair its rank among the warp's pairs of the same group. A scan over the warps per group, a scan over the groups,
+// and every pair knows its position. Same outputs as the four-kernel path.
+constexpr int kSmallMaxPerLane = 8;
+
+__global__ void __launch_bounds__(1024) moe_sort_small_kernel(const MoeSortParams p) {
+  extern __shared__ int32_t wcnt[];          // [32][G] per-warp counts, then exclusive offsets over the warps
+  __shared__ int32_t warp_tot[32];
+  __shared__ int32_t carry;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int G = p.segments * p.num_experts;
+  for (int i = tid; i < 32 * G; i += 1024) wcnt[i] = 0;
+  if (tid == 0) carry = 0;
+  __syncthreads();
+  // warp w owns pairs [w * per_warp, (w + 1) * per_warp), per_warp a multiple of 32
+  const int per_warp = ((p.n_pairs + 31) / 32 + 31) / 32 * 32;
+  const int w0 = warp * per_warp;
+  int my_group[kSmallMaxPerLane], my_rank[kSmallMaxPerLane];
+  int32_t* mine = wcnt + warp * G;
+#pragma unroll
+  for (int k = 0; k < kSmallMaxPerLane; ++k) {
+    my_group[k] = -1;
+    my_rank[k] = 0;
+    if (k * 32 < per_warp) {   // uniform over the warp
+      const int pair = w0 + k * 32 + lane;
+      int g = -1;
+      if (pair < p.n_pairs) {
+        const int e = p.ids[pair];
+        if (e >= 0 && e < p.num_experts) g = (pair / p.pairs_per_segment) * p.num_experts + e;
+      }
+      const uint32_t same = __match_any_sync(0xffffffffu, g);
+      const int leader = __ffs(same) - 1;
+      int old = 0;
+      if (g >= 0 && lane == leader) {
+        old = mine[g];
+        mine[g] = old + __popc(same);
+      }
+      old = __shfl_sync(0xffffffffu, old, leader);
+      my_group[k] = g;
+      my_rank[k] = old + __popc(same & ((1u << lane) - 1u));
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+  // per group: exclusive scan of the counts over the warps, total, padded size
+  for (int g0 = 0; g0 < G; g0 += 1024) {
+    const int g = g0 + tid;
+    int total = 0;
+    if (g < G) {
+      for (int w = 0; w < 32; ++w) {
+        const int v = wcnt[w * G + g];
+        wcnt[w * G + g] = total;
+        total += v;
+      }
+      p.group_count[g] = total;
+    }
+    const int padded = (total + p.block_m - 1) / p.block_m * p.block_m;
+    int incl = padded;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    int before = carry;
+    for (int w = 0; w < warp; ++w) before += warp_tot[w];
+    const int off = before + incl - padded;
+    if (g < G) {
+      p.group_off[g] = off;
+      const int seg = g / p.num_experts, e = g - seg * p.num_experts;
+      for (int i = total; i < padded; ++i) p.sorted_ids[off + i] = p.n_pairs;
+      for (int t = 0; t < padded / p.block_m; ++t) {
+        p.tile_expert[off / p.block_m + t] = e;
+        p.tile_seg_start[off / p.block_m + t] = p.segments > 1 ? seg : 0x7fffffff;
+        p.tile_seg_end[off / p.block_m + t] = p.segments > 1 ? seg : -1;
+      }
+      if (e == p.num_experts - 1) p.totals[2 + seg] = (off + padded) / p.block_m;
+    }
+    __syncthreads();
+    if (tid == 1023) carry = off + padded;
+    __syncthreads();
+  }
+  if (tid == 0) {
+    p.totals[0] = carry;
+    p.totals[1] = carry / p.block_m;
+  }
+  __threadfence_block();
+  __syncthreads();   // group_off and the tile table (global memory, this CTA) are visible to every thread
+#pragma unroll
+  for (int k = 0; k < kSmallMaxPerLane; ++k) {
+    const int g = my_group[k];
+    if (g >= 0) {
+      const int pair = w0 + k * 32 + lane;
+      const int pos = p.group_off[g] + wcnt[warp * G + g] + my_rank[k];
+      p.sorted_ids[pos] = pair;
+      if (p.pair_pos) p.pair_pos[pair] = pos;
+      if (p.segments == 1) {
+        const int src = (pair / p.topk) / p.tokens_per_rank;
+        const int tile = pos / p.block_m;
+        atomicMin(p.tile_seg_start + tile, src);
+        atomicMax(p.tile_seg_end + tile, src);
+      }
+    }
+  }
+}
+
 // Stable counting sort of the tiles by stage; one CTA. order[j] = tile issued j-th.
 __global__ void __launch_bounds__(1024) moe_tile_order_kernel(const int32_t* tile_seg_end, const int32_t* totals, int rank,
                                                               int world, int shift, int32_t* order) {
@@ -214,6 +324,15 @@ B200_API long long b200_moe_sorted_capacity(int n_pairs, int num_experts, int bl
   return (static_cast<long long>(n_pairs) + groups * (block_m - 1) + block_m - 1) / block_m * block_m;
 }
 
+static bool small_sort_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("B200DIST_MOE_SORT_SMALL");
+    on = (e && e[0] == '1') ? 1 : 0;
+  }
+  return on == 1;
+}
+
 // Scratch (int32 elements) that b200_moe_sort needs for a problem of this size.
 B200_API long long b200_moe_sort_scratch_ints(int n_pairs, int num_experts, int segments) {
   const long long pps = n_pairs / (segments > 0 ? segments : 1);
@@ -244,6 +363,19 @@ B200_API int b200_moe_sort(const int32_t* ids, int n_pairs, int topk, int num_ex
   p.chunk_cnt = scratch;
   p.group_off = scratch + static_cast<size_t>(p.chunks_per_segment) * segments * num_experts;
   const int chunks = p.chunks_per_segment * segments;
+  if (small_sort_enabled() && n_pairs <= 32 * 32 * kSmallMaxPerLane && segments * num_experts <= 1024) {
+    const size_t smem = static_cast<size_t>(32) * segments * num_experts * sizeof(int32_t);
+    static bool configured[64] = {false};
+    int dev = 0;
+    B200_CHECK_CUDA(cudaGetDevice(&dev));
+    if (!configured[dev & 63]) {
+      B200_CHECK_CUDA(cudaFuncSetAttribute(moe_sort_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
+      configured[dev & 63] = true;
+    }
+    moe_sort_small_kernel<<<1, 1024, smem, s>>>(p);
+    B200_CHECK_CUDA(cudaGetLastError());
+    return kOk;
+  }
   moe_count_kernel<<<chunks, kChunk, num_experts * sizeof(int32_t), s>>>(p);
   moe_chunk_prefix_kernel<<<dim3((num_experts + 31) / 32, segments), 1024, 0, s>>>(p);
   moe_offsets_kernel<<<1, 1024, 0, s>>>(p);
