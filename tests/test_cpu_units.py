@@ -232,3 +232,18 @@ def test_ag_gemm_gather_choice_follows_world_size_and_bytes():
     c = ctx(8)
     c.all_gather_method = "sm_pull_fused"
     assert c.method_for(128) == "sm_pull_fused"
+
+
+def test_bench_reference_arm_reports_unavailable_and_exits_zero():
+    """`bench.py --impl reference` must answer with one JSON line and exit 0 even where the reference cannot run."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    proc = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2",
+                           "--warmup", "1"], capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-500:]
+    line = [l for l in proc.stdout.splitlines() if l.startswith("{")][-1]
+    d = json.loads(line)
+    assert d["impl"] == "reference" and isinstance(d["unavailable"], str) and d["unavailable"]
