@@ -155,6 +155,27 @@ __device__ __forceinline__ void finish_row(const ArParams& p, uint64_t row, Load
   }
 }
 
+// acc = sum over s < world of the vector at addr(s), in rank order. All loads are issued before the first add, so the
+// sum costs one memory latency instead of `world` of them (these vectors sit on the critical path of a decode step).
+template <int DT, typename Addr>
+__device__ __forceinline__ void sum_over_ranks(int world, Addr addr, float* acc) {
+  using V = Vec<DT>;
+  uint4 v[kMaxRanks];
+#pragma unroll
+  for (int s = 0; s < kMaxRanks; ++s)
+    if (s < world) v[s] = ld_v4_relaxed_sys(addr(s));
+#pragma unroll
+  for (int e = 0; e < V::kElems; ++e) acc[e] = 0.f;
+#pragma unroll
+  for (int s = 0; s < kMaxRanks; ++s)
+    if (s < world) {
+      float f[V::kElems];
+      V::unpack(v[s], f);
+#pragma unroll
+      for (int e = 0; e < V::kElems; ++e) acc[e] += f[e];
+    }
+}
+
 // Work maps. A CTA must consume only data that CTA b of the peers staged, because it synchronises with
 // nobody else. "global": unit i belongs to CTA (i / T) % G. "slice": the data is cut into `world` equal
 // slices and unit s * slice + i belongs to the CTA that owns i in the global map of [0, slice).
@@ -205,26 +226,14 @@ __global__ void __launch_bounds__(kArThreads) allreduce_kernel(const ArParams p,
     ok = cta_peer_barrier(ctx, p.flags, 0, epoch);
     if (ok && !fused) {
       for_units_global(nvec, [&](uint64_t i) {
-        float acc[V::kElems] = {};
-        for (int s = 0; s < world; ++s) {
-          float f[V::kElems];
-          V::unpack(ld_v4_relaxed_sys(ws + s * nvec + i), f);
-#pragma unroll
-          for (int e = 0; e < V::kElems; ++e) acc[e] += f[e];
-        }
+        float acc[V::kElems];
+        sum_over_ranks<DT>(world, [&](int s) { return ws + s * nvec + i; }, acc);
         out[i] = V::pack(acc);
       });
     } else if (ok) {
       for (uint64_t r = blockIdx.x; r < rows; r += gridDim.x) {
         auto load_sum = [&](int i, float* acc) {
-#pragma unroll
-          for (int e = 0; e < V::kElems; ++e) acc[e] = 0.f;
-          for (int s = 0; s < world; ++s) {
-            float f[V::kElems];
-            V::unpack(ld_v4_relaxed_sys(ws + s * nvec + r * row_vecs + i), f);
-#pragma unroll
-            for (int e = 0; e < V::kElems; ++e) acc[e] += f[e];
-          }
+          sum_over_ranks<DT>(world, [&](int s) { return ws + s * nvec + r * row_vecs + i; }, acc);
         };
         finish_row<DT>(p, r, load_sum, [&](int i, uint4 res, uint4 nrm) { write_row_outputs(r, i, res, nrm); }, red);
       }
@@ -264,14 +273,7 @@ __global__ void __launch_bounds__(kArThreads) allreduce_kernel(const ArParams p,
     }
     ok = cta_peer_barrier(ctx, p.flags, 0, epoch);
     auto pull_sum = [&](const uint4* addr, float* acc) {
-#pragma unroll
-      for (int e = 0; e < V::kElems; ++e) acc[e] = 0.f;
-      for (int k = 0; k < world; ++k) {
-        float f[V::kElems];
-        V::unpack(ld_v4_relaxed_sys(symm_at(ctx, addr, peer_of(k))), f);
-#pragma unroll
-        for (int e = 0; e < V::kElems; ++e) acc[e] += f[e];
-      }
+      sum_over_ranks<DT>(world, [&](int k) { return symm_at(ctx, addr, peer_of(k)); }, acc);
     };
     auto broadcast = [&](uint4* addr, uint4 v) {
       if (mc) {
