@@ -98,7 +98,8 @@ def main() -> None:
     ap.add_argument("--prefill-backend", default="triton_dist_AR", choices=["torch", "triton_dist", "triton_dist_AR"])
     args = ap.parse_args()
     if args.impl == "reference":
-        _reference_arm()
+        if int(os.environ.get("RANK", "0")) == 0:  # one line per job, also when launched as N ranks
+            _reference_arm()
         return
     if args.warmup < 3:
         args.warmup = 3
