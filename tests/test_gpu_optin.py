@@ -1,0 +1,35 @@
+"""Runs the existing kernel tests once more with each opt-in variant switched on (the variants are chosen by
+environment variables that the native library reads once per process, hence one pytest subprocess per setting).
+
+Off unless B200DIST_TEST_UNVERIFIED=1: these variants are built and desk-checked but have not been run on a GPU yet,
+so they are kept out of the default test run until they have been.
+"""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+VARIANTS = [
+    ({"B200DIST_ATTN_V2": "3"}, ["tests/test_gpu_ops.py", "-k", "decode_attention"]),
+    ({"B200DIST_ATTN_V2": "6"}, ["tests/test_gpu_ops.py", "-k", "decode_attention"]),
+    ({"B200DIST_ATTN_FUSED_COMBINE": "1"}, ["tests/test_gpu_ops.py", "-k", "decode_attention"]),
+    ({"B200DIST_ATTN_V2": "6", "B200DIST_ATTN_FUSED_COMBINE": "1"}, ["tests/test_gpu_ops.py", "tests/test_gpu_model.py", "-k", "decode or engine or model"]),
+    ({"B200DIST_MOE_SORT_SMALL": "1"}, ["tests/test_gpu_moe.py"]),
+]
+
+
+@pytest.mark.skipif(os.environ.get("B200DIST_TEST_UNVERIFIED", "0") != "1", reason="opt-in variants: set B200DIST_TEST_UNVERIFIED=1")
+@pytest.mark.parametrize("env_extra,pytest_args", VARIANTS, ids=[",".join(f"{k}={v}" for k, v in e.items()) for e, _ in VARIANTS])
+def test_existing_tests_pass_with_variant(env_extra, pytest_args):
+    env = dict(os.environ)
+    env.update(env_extra)
+    env.pop("B200DIST_TEST_UNVERIFIED", None)  # the child must not recurse into this file's cases
+    res = subprocess.run([sys.executable, "-m", "pytest", "-q", "-m", "gpu", "-p", "no:cacheprovider", *pytest_args],
+                         cwd=os.path.dirname(HERE), env=env, capture_output=True, text=True, timeout=900)
+    sys.stdout.write(res.stdout[-4000:])
+    sys.stderr.write(res.stderr[-2000:])
+    assert res.returncode == 0, f"tests failed with {env_extra}"
