@@ -14,6 +14,9 @@ API parity with ``python/triton_dist/kernels/nvidia/allreduce.py`` (``create_all
                          hop away, so a tree only adds hops; the name is kept for API parity
   =====================  =====================================================================
 
+With ``B200DIST_AR_LL=1`` fused calls of at most 512 KB take a low-latency packet path
+(``csrc/kernels/allreduce_ll.cu``: 8-byte {data, epoch} packets, no flag exchange).
+
 Unlike the reference there is no staging memcpy outside the kernel and no host-side call counter:
 the kernel stages, synchronises CTA-by-CTA with its peers, reduces and (optionally) normalises, and
 its epoch lives in device memory, so every method — chunked or not — can be captured in a CUDA graph.
@@ -21,6 +24,7 @@ its epoch lives in device memory, so every method — chunked or not — can be 
 from __future__ import annotations
 
 import dataclasses
+import os
 
 import torch
 
@@ -51,9 +55,14 @@ class AllReduceContext:
 
     def finalize(self) -> None:
         torch.cuda.synchronize()
-        for t in self.workspaces + [self.flags]:
+        for t in self.workspaces + [self.flags] + list(getattr(self, "ll_ws", None) or []):
             self.heap.free(t)
         self.workspaces = []
+        self.ll_ws = None
+
+
+_AR_LL = os.environ.get("B200DIST_AR_LL", "0") == "1"
+_LL_MAX_BYTES = 512 * 1024   # input bytes per call served by the low-latency packet path
 
 
 def create_allreduce_ctx(workspace_nbytes: int, rank: int, world_size: int, local_world_size: int) -> AllReduceContext:
@@ -67,6 +76,10 @@ def create_allreduce_ctx(workspace_nbytes: int, rank: int, world_size: int, loca
     flags = heap.create_tensor((2 * max_ctas * 8,), torch.int32)
     ctx = AllReduceContext(workspace_nbytes, rank, world_size, local_world_size, heap, ws, flags,
                            torch.zeros(4, dtype=torch.int32, device="cuda"), max_ctas)
+    if _AR_LL:
+        # opt-in: dedicated packet buffers (data and flag share a word, so they must never hold anything else)
+        ctx.ll_ws = [heap.create_tensor((world_size * _LL_MAX_BYTES * 2,), torch.uint8, align=1024) for _ in range(2)]
+        ctx.ll_sync = torch.zeros(4, dtype=torch.int32, device="cuda")
     heap.barrier_all()
     torch.cuda.synchronize()
     return ctx
@@ -151,6 +164,18 @@ def all_reduce_rmsnorm(x: torch.Tensor, residual: torch.Tensor | None, gamma: to
     """
     rows, hidden = x.shape
     es = x.element_size()
+    if (method is None and getattr(ctx, "ll_ws", None) is not None and es == 2 and x.numel() * es <= _LL_MAX_BYTES
+            and hidden % 2 == 0 and hidden <= 8192 and x.is_contiguous()):
+        # opt-in low-latency path: 8-byte {data, epoch} packets, no flag exchange, no fence
+        if normed_out is None:
+            normed_out = torch.empty_like(x)
+        if residual_out is None:
+            residual_out = residual if residual is not None else torch.empty_like(x)
+        _lib.call("b200_allreduce_ll", ctx.heap.ctx, ptr(x), rows, hidden, dtype_code(x.dtype), ptr(ctx.ll_ws[0]),
+                  ptr(ctx.ll_ws[1]), ptr(ctx.ll_sync), ptr(residual), ptr(residual_out), ptr(gamma), ptr(normed_out),
+                  c_float(eps), stream_ptr())
+        ops._count()
+        return normed_out, residual_out
     if method is None and x.numel() * es <= 512 * 1024:
         # latency-bound: one push, one meeting point, one pass (a two-shot costs two meetings and three passes)
         method = AllReduceMethod.OneShot
