@@ -10,6 +10,7 @@ reference's ``[E, K, N_per_rank]`` layout is accepted and transposed once per we
 from __future__ import annotations
 
 import dataclasses
+import os
 
 import torch
 
@@ -61,6 +62,11 @@ class MoEAllGatherGroupGEMMTensorParallelContext:
         self.symm_workspaces = []
 
 
+# B200DIST_AG_GROUP_PUSH=1 (opt-in, process-wide: a context keeps one gather for its whole life) stores the tokens into the
+# peers' buffers instead of pulling them; the same flag words then serve as rows-landed counters.
+_AG_ENTRY = "b200_ag_grouped_gemm_push" if os.environ.get("B200DIST_AG_GROUP_PUSH", "0") == "1" else "b200_ag_grouped_gemm"
+
+
 def create_ag_group_gemm_context(max_ntokens: int, N_per_rank: int, K: int, num_experts: int, topk: int,
                                  dtype: torch.dtype, rank: int, num_ranks: int, num_local_ranks: int | None = None,
                                  ag_intranode_stream=None, ag_internode_stream=None, BLOCK_SIZE_M: int = 128,
@@ -94,7 +100,7 @@ def ag_group_gemm(a: torch.Tensor, b: torch.Tensor, ctx: MoEAllGatherGroupGEMMTe
     order = order_tiles(plan, ctx.rank, ctx.num_ranks, 0)
     if out is None:
         out = torch.empty((T * ctx.topk, N), dtype=a.dtype, device=a.device)
-    _lib.call("b200_ag_grouped_gemm", ctx.heap.ctx, ptr(a.contiguous()), ptr(ctx.symm_workspaces[0]),
+    _lib.call(_AG_ENTRY, ctx.heap.ctx, ptr(a.contiguous()), ptr(ctx.symm_workspaces[0]),
               ptr(ctx.symm_workspaces[1]), Tr, ctx.topk, ptr(w), E, N, K, ptr(plan.sorted_ids), ptr(plan.tile_expert),
               ptr(order), ptr(plan.totals), plan.max_tiles, ptr(out), out.stride(0), ptr(ctx.symm_ready), ptr(ctx.rank_cnt),
               ptr(ctx.rank_flag), ptr(ctx.sync), dtype_code(a.dtype), stream_ptr())
