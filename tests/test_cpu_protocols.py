@@ -7,8 +7,9 @@ is a property of the protocol, not of the CUDA code, so it is checked here by ex
 producer and consumer threads under thousands of random interleavings. The same model with the parity removed must
 fail, which shows that the checker can see the hazard it is guarding against.
 
-What is modelled: the push gather of AG-GEMM (`csrc/kernels/gemm_sm100.cu`, communication warps and TMA producer) and
-the slot / counter scheme of GEMM-RS (epilogue stores, signalling warp, reduce phase).
+What is modelled: the push gather of AG-GEMM (`csrc/kernels/gemm_sm100.cu`, communication warps and TMA producer), the
+slot / counter scheme of GEMM-RS (epilogue stores, signalling warp, reduce phase), and the barrier-free packet
+all-reduce (`csrc/kernels/allreduce_ll.cu`).
 """
 from __future__ import annotations
 
@@ -182,6 +183,61 @@ def test_gemm_rs_single_slot_buffer_is_caught():
     for seed in range(150):
         try:
             _gemm_rs_model(3, 2, 2, calls=5, rng=random.Random(seed), use_parity=False)
+        except Violation:
+            failures += 1
+    assert failures > 0
+
+
+# ---------------------------------------------------------------------------------------------- packet all-reduce
+def _ll_allreduce_model(world, words, calls, rng, use_parity=True):
+    """Low-latency all-reduce: every word travels as a {data, epoch} packet into slot [source] of every peer's
+    workspace; the receiver polls the packets of call e for flag == e. There is no barrier at all, so the only thing
+    that keeps a fast rank from overwriting packets a slow rank has not read yet is the parity double-buffering."""
+    npar = 2 if use_parity else 1
+    ws = [[[[(0, 0)] * words for _ in range(world)] for _ in range(npar)] for _ in range(world)]  # ws[rank][par][src][w]
+    done = [0] * world
+
+    def rank_thread(r):
+        for e in range(1, calls + 1):
+            par = e % npar
+            mine = [(r + 1) * 1000 + e * 10 + w for w in range(words)]
+            for k in range(1, world):
+                peer = (r + k) % world
+                for w in range(words):
+                    ws[peer][par][r][w] = (mine[w], e)       # one aligned 8-byte store: data and flag land together
+                    yield True
+            for w in range(words):
+                total = 0
+                for s in range(world):
+                    if s == r:
+                        total += mine[w]
+                        continue
+                    while ws[r][par][s][w][1] != e:
+                        yield False
+                    total += ws[r][par][s][w][0]
+                    yield True
+                want = sum((s + 1) * 1000 + e * 10 + w for s in range(world))
+                if total != want:
+                    raise Violation(f"rank {r} call {e} word {w}: {total} != {want}")
+            done[r] = e
+            yield True
+
+    _run([rank_thread(r) for r in range(world)], rng)
+
+
+@pytest.mark.parametrize("world,words", [(2, 3), (4, 2), (8, 1)])
+def test_packet_allreduce_needs_no_barrier_with_parity_buffers(world, words):
+    for seed in range(200):
+        _ll_allreduce_model(world, words, calls=6, rng=random.Random(seed))
+
+
+def test_packet_allreduce_single_buffer_is_caught():
+    """With one buffer a rank that runs ahead replaces packets of call e by packets of call e + 1 before a slow peer has
+    read them; the slow peer then waits for a flag that never comes back (reported as a deadlock)."""
+    failures = 0
+    for seed in range(200):
+        try:
+            _ll_allreduce_model(3, 2, calls=6, rng=random.Random(seed), use_parity=False)
         except Violation:
             failures += 1
     assert failures > 0
