@@ -254,6 +254,36 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     return (out, lse) if return_lse else out
 
 
+def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: torch.Tensor,
+                      cu_seqlens_k: torch.Tensor, max_seqlen_q: int, max_seqlen_k: int, scale: float,
+                      causal: bool = True, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Variable-length (packed) attention on the tcgen05 prefill kernel. q [total_q, Hq, 128]; k, v [total_k, Hkv, 128];
+    cu_seqlens_* int32 [B + 1] on the device. With ``causal`` query i of a sequence attends keys <= i + (k_len - q_len).
+    Returns [total_q, Hq, 128]."""
+    _lib.require_cuda()
+    total_q, Hq, D = q.shape
+    total_k, Hkv, _ = k.shape
+    if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()) or k.shape != v.shape or D != 128:
+        raise ValueError("prefill_attention needs contiguous q / k / v with head dim 128")
+    if q.dtype not in (torch.bfloat16, torch.float16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise TypeError("prefill_attention handles bf16 / f16")
+    B = cu_seqlens_q.numel() - 1
+    cu_q = cu_seqlens_q.to(device=q.device, dtype=torch.int32).contiguous()
+    cu_k = cu_seqlens_k.to(device=q.device, dtype=torch.int32).contiguous()
+    lib = _lib.load()
+    lib.b200_prefill_attention_scratch_bytes.restype = ctypes.c_longlong
+    nbytes = int(lib.b200_prefill_attention_scratch_bytes(B, Hkv, int(max_seqlen_k)))
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    if out is None:
+        out = torch.empty_like(q)
+    status = torch.zeros(1, dtype=torch.int32, device=q.device)
+    _lib.call("b200_prefill_attention", ptr(q), ptr(k), ptr(v), ptr(cu_q), ptr(cu_k), B, total_q, total_k, int(max_seqlen_q),
+              int(max_seqlen_k), Hq, Hkv, D, c_float(scale), 1 if causal else 0, ptr(scratch), ptr(out), dtype_code(q.dtype),
+              ptr(status), stream_ptr())
+    _count(2)
+    return out
+
+
 def combine_partials(o_part: torch.Tensor, lse_part: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """Merge attention partials over dim 0: o_part fp32 [R, BH, 128], lse_part fp32 [R, BH] -> [BH, 128]."""
     _lib.require_cuda()
