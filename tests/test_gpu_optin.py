@@ -20,6 +20,7 @@ VARIANTS = [
     ({"B200DIST_ATTN_V2": "6", "B200DIST_ATTN_FUSED_COMBINE": "1"}, ["tests/test_gpu_ops.py", "tests/test_gpu_model.py", "-k", "decode or engine or model"]),
     ({"B200DIST_MOE_SORT_SMALL": "1"}, ["tests/test_gpu_moe.py"]),
     ({"B200DIST_AG_GROUP_PUSH": "1"}, ["tests/test_gpu_moe.py", "-k", "ag_group_gemm"]),
+    ({"B200DIST_PREFILL_NATIVE": "1"}, ["tests/test_gpu_model.py"]),
     ({"B200DIST_AR_LL": "1"}, ["tests/test_gpu_dist_world1.py", "tests/test_gpu_model.py", "-k", "allreduce or model or engine"]),
 ]
 

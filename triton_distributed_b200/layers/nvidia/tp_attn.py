@@ -12,6 +12,7 @@ kernel does head-norm + RoPE + cache write and the paged decode kernel does atte
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -47,6 +48,9 @@ def _rope_torch(x: torch.Tensor, cos_sin: torch.Tensor, pos: torch.Tensor) -> to
     xf = x.float()
     x1, x2 = xf[..., : D // 2], xf[..., D // 2:]
     return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1).to(x.dtype)
+
+
+_PREFILL_NATIVE = os.environ.get("B200DIST_PREFILL_NATIVE", "0") == "1"
 
 
 class TP_Attn:
@@ -126,6 +130,14 @@ class TP_Attn:
         # prefill from an empty cache: causal attention over this chunk (library SDPA)
         kf = kp.view(-1, self.kv_heads_local, self.head_dim)[step["slots"]].view(bsz, seqlen, self.kv_heads_local, self.head_dim)
         vf = vp.view(-1, self.kv_heads_local, self.head_dim)[step["slots"]].view(bsz, seqlen, self.kv_heads_local, self.head_dim)
+        if _PREFILL_NATIVE and self.head_dim == 128:
+            # opt-in: the tcgen05 prefill kernel on the packed [B * S, heads, 128] layout (equal-length sequences here)
+            cu = torch.arange(0, (bsz + 1) * seqlen, seqlen, dtype=torch.int32, device=qkv.device)
+            o = ops.prefill_attention(q.reshape(bsz * seqlen, self.q_heads_local, self.head_dim).contiguous(),
+                                      kf.reshape(bsz * seqlen, self.kv_heads_local, self.head_dim).contiguous(),
+                                      vf.reshape(bsz * seqlen, self.kv_heads_local, self.head_dim).contiguous(),
+                                      cu, cu, seqlen, seqlen, self.scale, True)
+            return o.reshape(bsz * seqlen, -1)
         o = F.scaled_dot_product_attention(q.view(bsz, seqlen, self.q_heads_local, self.head_dim).transpose(1, 2),
                                            kf.transpose(1, 2), vf.transpose(1, 2), is_causal=True, enable_gqa=True)
         return o.transpose(1, 2).reshape(bsz * seqlen, -1)
