@@ -247,3 +247,36 @@ def test_bench_reference_arm_reports_unavailable_and_exits_zero():
     line = [l for l in proc.stdout.splitlines() if l.startswith("{")][-1]
     d = json.loads(line)
     assert d["impl"] == "reference" and isinstance(d["unavailable"], str) and d["unavailable"]
+
+
+def test_allreduce_method_resolution_and_split_heuristics():
+    """Host-side choices that need no GPU: which native all-reduce a reference method name maps to (with and without
+    an NVLS mapping), the workspace factors, and the KV split heuristic's bounds."""
+    import types
+
+    import pytest
+
+    from triton_distributed_b200 import ops
+    from triton_distributed_b200.kernels.allreduce import AllReduceMethod, get_allreduce_methods, to_allreduce_method
+    from triton_distributed_b200.kernels.nvidia import allreduce as ar
+
+    def ctx(mc):
+        return types.SimpleNamespace(heap=types.SimpleNamespace(has_multicast=mc), world_size=8, max_ctas=128)
+
+    assert ar._resolve(AllReduceMethod.OneShot, 1 << 10, ctx(False)) == 0
+    assert ar._resolve(AllReduceMethod.OneShot_TMA, 1 << 10, ctx(False)) == 0
+    assert ar._resolve(AllReduceMethod.TwoShot, 1 << 24, ctx(False)) == 1
+    assert ar._resolve(AllReduceMethod.DoubleTree, 1 << 10, ctx(False)) == 0      # small: one-shot
+    assert ar._resolve(AllReduceMethod.DoubleTree, 1 << 24, ctx(False)) == 1      # large: two-shot
+    assert ar._resolve(None, 1 << 10, ctx(True)) == 2 and ar._resolve(None, 1 << 24, ctx(True)) == 3
+    assert ar._resolve(None, 1 << 10, ctx(False)) == 0 and ar._resolve(None, 1 << 24, ctx(False)) == 1
+    with pytest.raises(RuntimeError):
+        ar._resolve(AllReduceMethod.TwoShot_Multimem, 1 << 20, ctx(False))
+    assert ar._ws_factor(0, 8, False) == 8 and ar._ws_factor(2, 8, False) == 1
+    assert ar._ws_factor(1, 8, False) == 2 and ar._ws_factor(1, 8, True) == 3
+    assert all(to_allreduce_method(n).name.lower().replace("_", "") == n.replace("_", "") for n in get_allreduce_methods())
+    with pytest.raises(ValueError):
+        to_allreduce_method("ring")
+    for batch, hkv, group, kv in [(1, 1, 8, 128), (8, 8, 8, 2048), (8, 1, 8, 2048), (32, 8, 8, 1 << 20), (1, 8, 8, 1 << 20)]:
+        s = ops.choose_kv_splits(batch, hkv, group, kv)
+        assert 1 <= s <= 128 and (s == 1 or kv // s >= 256)
