@@ -184,8 +184,11 @@ __device__ __forceinline__ void for_units_global(uint64_t n, F f) {
   for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) f(i);
 }
 
+// Launched with kArThreads threads. The register cap (instead of a launch bound, which would let the compiler take
+// 128) keeps a CTA of this kernel small enough to become resident next to a CTA of the preceding decode GEMM when
+// the two are chained by programmatic dependent launch.
 template <int DT>
-__global__ void __launch_bounds__(kArThreads) allreduce_kernel(const ArParams p, const SymmCtx ctx) {
+__global__ void __maxnreg__(80) allreduce_kernel(const ArParams p, const SymmCtx ctx) {
   using V = Vec<DT>;
   __shared__ float red[32];
   griddep_launch_dependents();
