@@ -444,13 +444,13 @@ def sp_ag_attention_prefill():
     from triton_distributed_b200.kernels.nvidia import create_sp_ag_attention_context_intra_node, fused_sp_ag_attn_intra_node
     from triton_distributed_b200.kernels.nvidia.sp_ag_attention_intra_node import zigzag_positions
     rank, world = _rank_world()
-    Hq, Hkv, D = 8, 2, 64
+    Hq, Hkv, D = 8, 2, 128
     lens = [16 * world, 48 * world]
     torch.manual_seed(21)
     q = [torch.randn(L, Hq, D, device="cuda", dtype=torch.bfloat16) for L in lens]
     k = [torch.randn(L, Hkv, D, device="cuda", dtype=torch.bfloat16) for L in lens]
     v = [torch.randn(L, Hkv, D, device="cuda", dtype=torch.bfloat16) for L in lens]
-    ctx = create_sp_ag_attention_context_intra_node(len(lens), Hq, Hkv, sum(lens), max(lens) // world, D, torch.bfloat16,
+    ctx = create_sp_ag_attention_context_intra_node(len(lens), Hq, Hkv, max(lens), max(lens) // world, D, torch.bfloat16,
                                                     torch.bfloat16, rank, world)
     pos = [zigzag_positions(L, rank, world, "cuda") for L in lens]
     q_sh = torch.cat([qq[p] for qq, p in zip(q, pos)])

@@ -280,3 +280,42 @@ def test_allreduce_method_resolution_and_split_heuristics():
     for batch, hkv, group, kv in [(1, 1, 8, 128), (8, 8, 8, 2048), (8, 1, 8, 2048), (32, 8, 8, 1 << 20), (1, 8, 8, 1 << 20)]:
         s = ops.choose_kv_splits(batch, hkv, group, kv)
         assert 1 <= s <= 128 and (s == 1 or kv // s >= 256)
+
+
+def test_bench_withholds_its_result_when_a_wait_expired(capsys):
+    """A kernel whose bounded wait ran out returns early with incomplete data and leaves the status word set.
+    bench.py must then fail instead of printing a tokens/s line; with a clean status it prints exactly one line."""
+    import importlib.util
+    import json
+    import os
+
+    import pytest
+
+    from triton_distributed_b200.runtime.heap import SymmHeap, SymmTimeoutError
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+
+    class FakeHeap:
+        rank = 0
+        check_status = SymmHeap.check_status
+
+        def __init__(self, code):
+            self.code, self.cleared = code, False
+            self._lib = self
+            self._h = None
+
+        def status(self):
+            return [self.code, 3, 7, 6, 123] + [0] * 11
+
+        def b200_heap_status_clear(self, _h):
+            self.cleared = True
+
+    with pytest.raises(SymmTimeoutError, match="who=3"):
+        bench.emit_result({"value": 1.0}, FakeHeap(1), 0)
+    assert capsys.readouterr().out == ""
+    bench.emit_result({"value": 1.0}, FakeHeap(0), 0)
+    assert json.loads(capsys.readouterr().out) == {"value": 1.0}
+    bench.emit_result({"value": 1.0}, FakeHeap(0), 1)   # only rank 0 prints
+    assert capsys.readouterr().out == ""

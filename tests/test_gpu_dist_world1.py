@@ -176,3 +176,28 @@ def test_sp_flash_decode_world1(dist1):
         want, _ = ref.paged_decode_attention_ref(q, kc, vc, lens[0], bt, 1 / math.sqrt(D))
         torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2)
     layer.finalize()
+
+
+@pytest.mark.parametrize("zigzag", [True, False])
+def test_sp_ag_attention_world1(dist1, zigzag):
+    """Context-parallel prefill with one rank: the K/V scatter kernel writes rows in global order (the identity here) and
+    the zig-zag split turns every sequence into two causal problems with prefixes of different length."""
+    from triton_distributed_b200.kernels.nvidia import create_sp_ag_attention_context_intra_node, fused_sp_ag_attn_intra_node
+    torch.manual_seed(3)
+    Hq, Hkv, D = 8, 2, 128
+    lens = [64, 384, 130 * 2]
+    q = torch.randn(sum(lens), Hq, D, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(sum(lens), Hkv, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(sum(lens), Hkv, D, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    ctx = create_sp_ag_attention_context_intra_node(len(lens), Hq, Hkv, max(lens), max(lens), D, torch.bfloat16, torch.bfloat16, 0, 1)
+    for _ in range(2):
+        out = fused_sp_ag_attn_intra_node(ctx, q, k, v, None, cu, cu, max(lens), max(lens), 0, 1, True, zigzag)
+    torch.cuda.synchronize()
+    for b, L in enumerate(lens):
+        s = slice(int(cu[b]), int(cu[b + 1]))
+        want = torch.nn.functional.scaled_dot_product_attention(
+            q[s].float().transpose(0, 1)[None], k[s].float().transpose(0, 1)[None], v[s].float().transpose(0, 1)[None],
+            is_causal=True, enable_gqa=True)[0].transpose(0, 1)
+        torch.testing.assert_close(out[s].float(), want, rtol=3e-2, atol=3e-2)
+    ctx.finalize()

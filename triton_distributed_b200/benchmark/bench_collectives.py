@@ -44,7 +44,7 @@ def _time(fn, iters, warmup, group):
 def bench_allreduce(args, group, rows):
     rank, world = dist.get_rank(), dist.get_world_size()
     heap = utils.get_heap()
-    ctx = create_allreduce_ctx(512 << 20, rank, world, world)
+    ctx = create_allreduce_ctx(min(512 << 20, max(args.ar_max_bytes, 64 << 20)), rank, world, world)
     methods = ["one_shot", "two_shot"] + (["one_shot_multimem", "two_shot_multimem"] if heap.has_multicast else [])
     nbytes = 8 << 10
     while nbytes <= args.ar_max_bytes:
@@ -65,7 +65,7 @@ def bench_allreduce(args, group, rows):
         rows.append(row)
         nbytes *= 4
     hidden = 8192
-    for tokens in (8, 128, 2048, 8192):
+    for tokens in getattr(args, "ar_tokens", (8, 128, 2048, 8192)):
         x = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16)
         res = torch.randn(tokens, hidden, device="cuda", dtype=torch.bfloat16)
         g = torch.ones(hidden, device="cuda", dtype=torch.bfloat16)
@@ -142,8 +142,8 @@ def bench_sp_decode(args, group, rows):
     rank, world = dist.get_rank(), dist.get_world_size()
     Hq, Hkv, D, page = 64, 8, 128, 64
     scale = 1 / math.sqrt(D)
-    for B in (1, 8, 32):
-        for total_kv in (32 << 10, 128 << 10, 1 << 20):
+    for B in getattr(args, "sp_batches", (1, 8, 32)):
+        for total_kv in getattr(args, "sp_kv", (32 << 10, 128 << 10, 1 << 20)):
             per_rank = total_kv // world
             if B * per_rank * Hkv * D * 2 * 2 > (40 << 30):
                 continue  # keep the KV cache of one rank below 40 GB

@@ -31,28 +31,21 @@ def _time(fn, iters, warmup, group):
     return utils.max_over_ranks(min(ts), group)
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--ms", type=int, nargs="+", default=[1024, 2048, 4096, 8192])
-    ap.add_argument("--hidden", type=int, default=8192)
-    ap.add_argument("--inter", type=int, default=28672)
-    ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--out", default=None)
-    args = ap.parse_args()
-    group = utils.initialize_distributed(seed=0, heap_bytes=4 << 30)
+def bench_pair(group, ms, iters: int, warmup: int, rows: list, hidden: int = 8192, inter: int = 28672,
+               both_gathers: bool = True) -> None:
+    """Append one AG-GEMM and one GEMM-RS row per M in `ms` (an int or a list) to `rows`."""
     rank, world = dist.get_rank(), dist.get_world_size()
-    H, I = args.hidden, args.inter
+    ms = [ms] if isinstance(ms, int) else list(ms)
+    H, I = hidden, inter
     n_ag = 2 * I // world   # gate_up shard rows
     k_rs = I // world
     dt = torch.bfloat16
-    maxM = max(args.ms)
+    maxM = max(ms)
     w1 = torch.randn(n_ag, H, device="cuda", dtype=dt) * 0.02
     w2 = torch.randn(H, k_rs, device="cuda", dtype=dt) * 0.02
     ag_ctx = create_ag_gemm_context(torch.empty(maxM // world, H, device="cuda", dtype=dt), w1, rank, world, maxM)
     rs_ctx = create_gemm_rs_context(maxM, H, rank, world, world, dt)
-    rows = []
-    for M in args.ms:
+    for M in ms:
         a = torch.randn(M // world, H, device="cuda", dtype=dt)
         full = torch.empty(M, H, device="cuda", dtype=dt)
         c = torch.empty(M, n_ag, device="cuda", dtype=dt)
@@ -64,15 +57,15 @@ def main() -> None:
             else:
                 torch.matmul(a, w1.t(), out=c)
 
-        t_ours = _time(lambda: ag_gemm(a, w1, ag_ctx, out=c), args.iters, args.warmup, group)
+        t_ours = _time(lambda: ag_gemm(a, w1, ag_ctx, out=c), iters, warmup, group)
         chosen = ag_ctx.method_for(M // world)
         by_method = {}
-        if world > 1:  # both gathers, so that the automatic choice can be checked against the data
+        if world > 1 and both_gathers:  # both gathers, so that the automatic choice can be checked against the data
             for m in ("sm_push_fused", "sm_pull_fused"):
                 ag_ctx.all_gather_method = m
-                by_method[m] = _time(lambda: ag_gemm(a, w1, ag_ctx, out=c), args.iters, args.warmup, group) * 1e3
+                by_method[m] = _time(lambda: ag_gemm(a, w1, ag_ctx, out=c), iters, warmup, group) * 1e3
             ag_ctx.all_gather_method = "auto"
-        t_base = _time(base_ag, args.iters, args.warmup, group)
+        t_base = _time(base_ag, iters, warmup, group)
         flops = 2.0 * M * n_ag * H
         nv_bytes = (world - 1) * (M // world) * H * 2
         roof = max(flops / (PEAK_TFLOPS * 1e9), nv_bytes / (LINK_GBS * 1e6))
@@ -89,8 +82,8 @@ def main() -> None:
             if world > 1:
                 dist.reduce_scatter_tensor(out, part, group=group)
 
-        t_ours = _time(lambda: gemm_rs(x, w2, rs_ctx, out=out), args.iters, args.warmup, group)
-        t_base = _time(base_rs, args.iters, args.warmup, group)
+        t_ours = _time(lambda: gemm_rs(x, w2, rs_ctx, out=out), iters, warmup, group)
+        t_base = _time(base_rs, iters, warmup, group)
         flops = 2.0 * M * H * k_rs
         nv_bytes = (world - 1) * (M // world) * H * 2
         roof = max(flops / (PEAK_TFLOPS * 1e9), nv_bytes / (LINK_GBS * 1e6))
@@ -98,6 +91,23 @@ def main() -> None:
                      "nccl_cublas_us": t_base * 1e3, "speedup": t_base / t_ours, "roofline_us": roof * 1e3,
                      "frac_of_roofline": roof / t_ours, "tflops": flops / t_ours / 1e9})
     utils.get_heap().check_status("bench_comm_gemm")
+    ag_ctx.finalize()
+    rs_ctx.finalize()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--ms", type=int, nargs="+", default=[1024, 2048, 4096, 8192])
+    ap.add_argument("--hidden", type=int, default=8192)
+    ap.add_argument("--inter", type=int, default=28672)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args()
+    group = utils.initialize_distributed(seed=0, heap_bytes=4 << 30)
+    rank = dist.get_rank()
+    rows: list[dict] = []
+    bench_pair(group, args.ms, args.iters, args.warmup, rows, args.hidden, args.inter)
     if rank == 0:
         for r in rows:
             print(json.dumps(r), flush=True)
@@ -105,8 +115,6 @@ def main() -> None:
             os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
             with open(args.out, "w") as f:
                 json.dump(rows, f, indent=1)
-    ag_ctx.finalize()
-    rs_ctx.finalize()
     utils.finalize_distributed()
 
 

@@ -68,7 +68,7 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
   }
 }
 
-// Fused combine (opt-in): every CTA of a (batch, head group) draws a ticket after its partial is visible; the CTA
+// Fused combine: every CTA of a (batch, head group) draws a ticket after its partial is visible; the CTA
 // that draws the last one merges all S partials (the arithmetic of decode_combine_kernel) and writes the final rows,
 // so the separate combine launch disappears. The ticket resets itself for the next call.
 template <bool BF16>
@@ -338,7 +338,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_split_kernel(const Decode
 }
 
 // ------------------------------------------------------------------------------------------------
-// Variant with one private cp.async ring per warp (opt-in: B200DIST_ATTN_V2=1).
+// Variant with one private cp.async ring per warp.
 //
 // The kernel above keeps at most one 32 KB tile per CTA in flight while it computes the other one; with three CTAs
 // per SM that is ~96 KB in flight per SM, and the measured 0.57 of the copy peak is what Little's law gives for that
@@ -620,100 +620,66 @@ __global__ void __launch_bounds__(kD) decode_combine_kernel(const float* o_part,
   if (c == 0 && out_lse) out_lse[bh] = lg > 0.f ? mg + logf(lg) : -INFINITY;
 }
 
-// 0 = the two-stage CTA-wide pipeline (default); 3 or 6 = per-warp rings of that depth (B200DIST_ATTN_V2=3|6, 1 -> 6).
-static int attn_ring_stages() {
+// Pipeline variant when the caller passes ring < 0: B200DIST_ATTN_V2 = 0 (two-stage CTA-wide pipeline), 3 or 6
+// (per-warp rings of that depth) forces one; unset picks the three-deep rings (two CTAs of 96 KB per SM), which
+// measured fastest from 2 K to 128 K tokens per sequence: 4.7-4.9 TB/s at batch 8 x 16 K and batch 32 x 4 K against
+// 3.7-3.8 TB/s for the CTA-wide pipeline and 3.1-3.2 TB/s for six-deep rings (one CTA per SM).
+static int attn_ring_default() {
   static int stages = -1;
   if (stages < 0) {
     const char* e = getenv("B200DIST_ATTN_V2");
-    const int v = e ? atoi(e) : 0;
-    stages = v == 3 ? 3 : (v == 6 || v == 1) ? 6 : 0;
+    if (!e) stages = 3;
+    else {
+      const int v = atoi(e);
+      stages = v == 3 ? 3 : (v == 6 || v == 1) ? 6 : 0;
+    }
   }
   return stages;
+}
+
+template <typename K>
+static int set_smem(K kernel, int bytes) {
+  B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return kOk;
 }
 
 }  // namespace b200
 
 using namespace b200;
 
-// q [B,Hq,128]; caches [num_blocks, page, Hkv, 128]; block_table [B, bt_stride] int32; kv_lens [B] int32.
-// num_splits == 1 writes `out` (and out_lse) directly; otherwise o_part [B,Hq,S,128] / lse_part [B,Hq,S]
-// (fp32 scratch) are filled and merged by b200_decode_combine.
-B200_API int b200_decode_attn_split(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
-                                    int bt_stride, const int* kv_lens, int B, int Hq, int Hkv, int head_dim, int page,
-                                    float scale, float soft_cap, int num_splits, float* o_part, float* lse_part,
-                                    void* out, float* out_lse, int dtype, void* stream) {
+// Paged GQA decode attention with split-KV.
+//   q [B,Hq,128]; caches [num_blocks, page, Hkv, 128]; block_table [B, bt_stride] int32; kv_lens [B] int32.
+//   num_splits == 1 writes `out` (and out_lse) directly.
+//   num_splits > 1 fills o_part [B,Hq,S,128] / lse_part [B,Hq,S] (fp32 scratch). With `tickets` (u32
+//   [B * Hkv * ceil(G / 16)], zero-initialised once; the kernel leaves it zeroed) the CTA that finishes last in a
+//   (batch, head group) merges the partials and writes `out` / `out_lse`, so no combine launch follows; without
+//   tickets the caller merges them (b200_decode_combine, or the cross-rank merge of sequence-parallel decode).
+//   ring: 0 = two-stage CTA-wide cp.async pipeline, 3 / 6 = one private ring of that depth per warp, < 0 = default.
+B200_API int b200_decode_attn(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                              int bt_stride, const int* kv_lens, int B, int Hq, int Hkv, int head_dim, int page,
+                              float scale, float soft_cap, int num_splits, float* o_part, float* lse_part,
+                              uint32_t* tickets, void* out, float* out_lse, int dtype, int ring, void* stream) {
   B200_REQUIRE(dtype == kBF16 || dtype == kF16, "decode attention supports bf16/f16");
   B200_REQUIRE(head_dim == kD, "decode attention is specialised for head_dim 128, got %d", head_dim);
   B200_REQUIRE(Hkv > 0 && Hq % Hkv == 0, "Hq (%d) must be a multiple of Hkv (%d)", Hq, Hkv);
   B200_REQUIRE(num_splits >= 1 && page >= 1, "bad num_splits/page");
+  if (ring < 0) ring = attn_ring_default();
+  B200_REQUIRE(ring == 0 || ring == 3 || ring == 6, "ring must be 0, 3 or 6, got %d", ring);
   if (B == 0) return kOk;
-  static bool configured[64] = {false};
-  int dev = 0;
-  B200_CHECK_CUDA(cudaGetDevice(&dev));
-  if (!configured[dev & 63]) {
-    B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-    B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-    configured[dev & 63] = true;
-  }
-  DecodeParams p;
-  memset(&p, 0, sizeof(p));
-  p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.block_table = block_table; p.kv_lens = kv_lens;
-  p.o_part = o_part; p.lse_part = lse_part; p.out = out; p.out_lse = out_lse;
-  p.bt_stride = bt_stride; p.Hq = Hq; p.Hkv = Hkv; p.page = page; p.S = num_splits;
-  p.scale = scale; p.soft_cap = soft_cap; p.direct = num_splits == 1 && out != nullptr;
-  B200_REQUIRE(p.direct || (o_part && lse_part), "split partial buffers are required when num_splits > 1");
-  const int G = Hq / Hkv;
-  dim3 grid(num_splits, Hkv * ((G + 15) / 16), B);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int ring = attn_ring_stages();
-  if (ring > 0) {
-    // per-warp rings: 4 warps x stages x 8 KB, never less than the 33 KB merge area
-    const int smem = 4 * ring * 8192 < 34 * 1024 ? 34 * 1024 : 4 * ring * 8192;
-    static bool ring_configured[64] = {false};
-    if (!ring_configured[dev & 63]) {
-      B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_ring_kernel<true, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-      B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_ring_kernel<false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-      B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_ring_kernel<true, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024));
-      B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_ring_kernel<false, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024));
-      ring_configured[dev & 63] = true;
-    }
-    if (ring == 3) {
-      if (dtype == kBF16) B200_CHECK_CUDA(launch_pdl(decode_split_ring_kernel<true, 3>, grid, kAttnThreads, smem, s, p));
-      else B200_CHECK_CUDA(launch_pdl(decode_split_ring_kernel<false, 3>, grid, kAttnThreads, smem, s, p));
-    } else {
-      if (dtype == kBF16) B200_CHECK_CUDA(launch_pdl(decode_split_ring_kernel<true, 6>, grid, kAttnThreads, smem, s, p));
-      else B200_CHECK_CUDA(launch_pdl(decode_split_ring_kernel<false, 6>, grid, kAttnThreads, smem, s, p));
-    }
-    return kOk;
-  }
-  if (dtype == kBF16) B200_CHECK_CUDA(launch_pdl(decode_split_kernel<true>, grid, kAttnThreads, kAttnSmem, s, p));
-  else B200_CHECK_CUDA(launch_pdl(decode_split_kernel<false>, grid, kAttnThreads, kAttnSmem, s, p));
-  return kOk;
-}
-
-// Split-KV attention with the combine fused into the last CTA of every (batch, head group): same arguments as
-// b200_decode_attn_split with num_splits > 1, plus `tickets` u32 [B * Hkv * ceil(G / 16)] (zero-initialised once; the
-// kernel leaves it zeroed). Writes `out` (and out_lse) directly; no b200_decode_combine call follows.
-B200_API int b200_decode_attn_fused(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
-                                    int bt_stride, const int* kv_lens, int B, int Hq, int Hkv, int head_dim, int page,
-                                    float scale, float soft_cap, int num_splits, float* o_part, float* lse_part,
-                                    uint32_t* tickets, void* out, float* out_lse, int dtype, void* stream) {
-  B200_REQUIRE(dtype == kBF16 || dtype == kF16, "decode attention supports bf16/f16");
-  B200_REQUIRE(head_dim == kD, "decode attention is specialised for head_dim 128, got %d", head_dim);
-  B200_REQUIRE(Hkv > 0 && Hq % Hkv == 0, "Hq (%d) must be a multiple of Hkv (%d)", Hq, Hkv);
-  B200_REQUIRE(num_splits >= 2 && page >= 1, "the fused combine is for num_splits >= 2");
-  B200_REQUIRE(o_part && lse_part && tickets && out, "partial buffers, tickets and out are required");
-  if (B == 0) return kOk;
+  const bool fuse = tickets != nullptr && num_splits > 1;
+  B200_REQUIRE(!fuse || out != nullptr, "the fused combine writes `out`");
   int dev = 0;
   B200_CHECK_CUDA(cudaGetDevice(&dev));
   static bool configured[64] = {false};
   if (!configured[dev & 63]) {
-    B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-    B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-    B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_ring_kernel<true, 3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-    B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_ring_kernel<false, 3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-    B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_ring_kernel<true, 6, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024));
-    B200_CHECK_CUDA(cudaFuncSetAttribute(decode_split_ring_kernel<false, 6, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024));
+    int rc = kOk;
+#define B200_ATTN_SMEM(BF, FU)                                                                \
+    if (rc == kOk) rc = set_smem(decode_split_kernel<BF, FU>, kAttnSmem);                       \
+    if (rc == kOk) rc = set_smem(decode_split_ring_kernel<BF, 3, FU>, 96 * 1024);               \
+    if (rc == kOk) rc = set_smem(decode_split_ring_kernel<BF, 6, FU>, 192 * 1024);
+    B200_ATTN_SMEM(true, false) B200_ATTN_SMEM(false, false) B200_ATTN_SMEM(true, true) B200_ATTN_SMEM(false, true)
+#undef B200_ATTN_SMEM
+    if (rc != kOk) return rc;
     configured[dev & 63] = true;
   }
   DecodeParams p;
@@ -721,23 +687,49 @@ B200_API int b200_decode_attn_fused(const void* q, const void* k_cache, const vo
   p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.block_table = block_table; p.kv_lens = kv_lens;
   p.o_part = o_part; p.lse_part = lse_part; p.out = out; p.out_lse = out_lse; p.tickets = tickets;
   p.bt_stride = bt_stride; p.Hq = Hq; p.Hkv = Hkv; p.page = page; p.S = num_splits;
-  p.scale = scale; p.soft_cap = soft_cap; p.direct = 0;
+  p.scale = scale; p.soft_cap = soft_cap; p.direct = num_splits == 1 && out != nullptr;
+  B200_REQUIRE(p.direct || (o_part && lse_part), "split partial buffers are required when num_splits > 1");
   const int G = Hq / Hkv;
   dim3 grid(num_splits, Hkv * ((G + 15) / 16), B);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int ring = attn_ring_stages();
   const bool bf = dtype == kBF16;
-  if (ring == 3) {
-    if (bf) B200_CHECK_CUDA(launch_pdl(decode_split_ring_kernel<true, 3, true>, grid, kAttnThreads, 96 * 1024, s, p));
-    else B200_CHECK_CUDA(launch_pdl(decode_split_ring_kernel<false, 3, true>, grid, kAttnThreads, 96 * 1024, s, p));
-  } else if (ring == 6) {
-    if (bf) B200_CHECK_CUDA(launch_pdl(decode_split_ring_kernel<true, 6, true>, grid, kAttnThreads, 192 * 1024, s, p));
-    else B200_CHECK_CUDA(launch_pdl(decode_split_ring_kernel<false, 6, true>, grid, kAttnThreads, 192 * 1024, s, p));
+  const int smem = ring == 0 ? kAttnSmem : ring == 3 ? 96 * 1024 : 192 * 1024;
+#define B200_ATTN_LAUNCH(KERNEL) B200_CHECK_CUDA(launch_pdl(KERNEL, grid, kAttnThreads, smem, s, p))
+  if (ring == 0) {
+    if (bf && fuse) B200_ATTN_LAUNCH((decode_split_kernel<true, true>));
+    else if (bf) B200_ATTN_LAUNCH((decode_split_kernel<true, false>));
+    else if (fuse) B200_ATTN_LAUNCH((decode_split_kernel<false, true>));
+    else B200_ATTN_LAUNCH((decode_split_kernel<false, false>));
+  } else if (ring == 3) {
+    if (bf && fuse) B200_ATTN_LAUNCH((decode_split_ring_kernel<true, 3, true>));
+    else if (bf) B200_ATTN_LAUNCH((decode_split_ring_kernel<true, 3, false>));
+    else if (fuse) B200_ATTN_LAUNCH((decode_split_ring_kernel<false, 3, true>));
+    else B200_ATTN_LAUNCH((decode_split_ring_kernel<false, 3, false>));
   } else {
-    if (bf) B200_CHECK_CUDA(launch_pdl(decode_split_kernel<true, true>, grid, kAttnThreads, kAttnSmem, s, p));
-    else B200_CHECK_CUDA(launch_pdl(decode_split_kernel<false, true>, grid, kAttnThreads, kAttnSmem, s, p));
+    if (bf && fuse) B200_ATTN_LAUNCH((decode_split_ring_kernel<true, 6, true>));
+    else if (bf) B200_ATTN_LAUNCH((decode_split_ring_kernel<true, 6, false>));
+    else if (fuse) B200_ATTN_LAUNCH((decode_split_ring_kernel<false, 6, true>));
+    else B200_ATTN_LAUNCH((decode_split_ring_kernel<false, 6, false>));
   }
+#undef B200_ATTN_LAUNCH
   return kOk;
+}
+
+// Earlier entry points, kept for callers of the C ABI: split only (the caller merges), and split with the fused merge.
+B200_API int b200_decode_attn_split(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                                    int bt_stride, const int* kv_lens, int B, int Hq, int Hkv, int head_dim, int page,
+                                    float scale, float soft_cap, int num_splits, float* o_part, float* lse_part,
+                                    void* out, float* out_lse, int dtype, void* stream) {
+  return b200_decode_attn(q, k_cache, v_cache, block_table, bt_stride, kv_lens, B, Hq, Hkv, head_dim, page, scale, soft_cap,
+                          num_splits, o_part, lse_part, nullptr, out, out_lse, dtype, -1, stream);
+}
+B200_API int b200_decode_attn_fused(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                                    int bt_stride, const int* kv_lens, int B, int Hq, int Hkv, int head_dim, int page,
+                                    float scale, float soft_cap, int num_splits, float* o_part, float* lse_part,
+                                    uint32_t* tickets, void* out, float* out_lse, int dtype, void* stream) {
+  B200_REQUIRE(num_splits >= 2 && tickets, "the fused combine is for num_splits >= 2 and needs tickets");
+  return b200_decode_attn(q, k_cache, v_cache, block_table, bt_stride, kv_lens, B, Hq, Hkv, head_dim, page, scale, soft_cap,
+                          num_splits, o_part, lse_part, tickets, out, out_lse, dtype, -1, stream);
 }
 
 B200_API int b200_decode_combine(const float* o_part, const float* lse_part, long long o_stride_bh, long long o_stride_s,

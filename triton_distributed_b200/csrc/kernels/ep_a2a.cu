@@ -138,7 +138,12 @@ __global__ void __launch_bounds__(kEpThreads) ep_row_a2a_kernel(const EpParams p
   for (int r = blockIdx.x * warps + warp; r < n; r += gridDim.x * warps) {
     int d = 0;
     while (d + 1 < ctx.world && r >= cum[(d + 1) * p.E_local]) ++d;
-    const size_t slot = static_cast<size_t>(ctx.rank) * p.max_m + (r - cum[d * p.E_local]);
+    const int idx = r - cum[d * p.E_local];
+    if (idx >= p.max_m) {  // more rows for this peer than its receive area holds: drop the row, tell the host
+      if (lane == 0) report_status(ctx, kStatusBadArgument, d, p.max_m, idx, __LINE__);
+      continue;
+    }
+    const size_t slot = static_cast<size_t>(ctx.rank) * p.max_m + idx;
     copy_row_warp(symm_at(ctx, p.recv[par] + slot * p.row_bytes, d), static_cast<const uint8_t*>(p.x) + static_cast<size_t>(r) * p.row_bytes,
                   p.row_bytes, lane);
     if (p.scale_floats && lane < p.scale_floats)
@@ -166,22 +171,33 @@ __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const EpParams 
     // destination of each of the k copies (lane k holds copy k)
     uint8_t* my_dst = nullptr;
     float* my_sdst = nullptr;
-    if (lane < p.topk) {
+    if (lane < p.topk) {  // a copy whose expert id or slot is out of range is dropped and reported (null destination)
       const int e = p.topk_ids[t * p.topk + lane];
-      const int d = e / p.E_local;
-      const size_t slot = static_cast<size_t>(ctx.rank) * p.max_m + (p.pair_pos[t * p.topk + lane] - cum[d * p.E_local]);
-      my_dst = symm_at(ctx, p.recv[par] + slot * p.row_bytes, d);
-      if (p.scale_floats) my_sdst = symm_at(ctx, p.recv_scale[par] + slot * p.scale_floats, d);
+      if (e >= 0 && e < p.E) {
+        const int d = e / p.E_local;
+        const int idx = p.pair_pos[t * p.topk + lane] - cum[d * p.E_local];
+        if (idx >= 0 && idx < p.max_m) {
+          const size_t slot = static_cast<size_t>(ctx.rank) * p.max_m + idx;
+          my_dst = symm_at(ctx, p.recv[par] + slot * p.row_bytes, d);
+          if (p.scale_floats) my_sdst = symm_at(ctx, p.recv_scale[par] + slot * p.scale_floats, d);
+        } else {
+          report_status(ctx, kStatusBadArgument, d, p.max_m, idx, __LINE__);
+        }
+      } else {
+        report_status(ctx, kStatusBadArgument, lane, p.E, static_cast<uint32_t>(e), __LINE__);
+      }
     }
     const uint8_t* row = x + static_cast<size_t>(t) * p.H * 2;
     if (!p.quant) {
-      for (int i0 = lane * 16; i0 < p.H * 2; i0 += 4 * 512) {  // four loads in flight, then k stores each
+      for (int base = 0; base < p.H * 2; base += 4 * 512) {  // four loads in flight, then k stores each; the trip
+        const int i0 = base + lane * 16;                      // count is the same for every lane (shuffles inside)
         uint4 v[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u)
           v[u] = i0 + u * 512 < p.H * 2 ? *reinterpret_cast<const uint4*>(row + i0 + u * 512) : make_uint4(0, 0, 0, 0);
         for (int k = 0; k < p.topk; ++k) {
           uint8_t* dst = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_dst), k));
+          if (dst == nullptr) continue;
 #pragma unroll
           for (int u = 0; u < 4; ++u)
             if (i0 + u * 512 < p.H * 2) st_v4(dst + i0 + u * 512, v[u]);
@@ -229,7 +245,7 @@ __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const EpParams 
           for (int k = 0; k < p.topk; ++k) {
             uint8_t* dst = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_dst), k));
             float* sdst = reinterpret_cast<float*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_sdst), k));
-            if (in) {
+            if (in && dst != nullptr) {
               *reinterpret_cast<uint2*>(dst + blk * 128 + hl * 8) = make_uint2(lo, hi);
               if (hl == 0) sdst[blk] = scale;
             }
@@ -254,7 +270,7 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const EpParams p
   if (threadIdx.x < ctx.world) {
     int n = 0;
     for (int e = 0; e < p.E_local; ++e) n += p.dispatch_splits[dpar][threadIdx.x * p.E_local + e];
-    src_rows[threadIdx.x] = n;
+    src_rows[threadIdx.x] = n < p.max_m ? n : p.max_m;  // a sender that overflowed its area dropped the excess rows
   }
   __syncthreads();
   // phase 1: return every received row's output to the rank it came from, same slot numbering
@@ -274,14 +290,20 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const EpParams p
     for (int t = blockIdx.x * warps + warp; t < p.T; t += gridDim.x * warps) {
       const uint8_t* my_src = nullptr;
       float my_w = 1.f;
-      if (lane < p.topk) {
+      if (lane < p.topk) {  // copies that the dispatch dropped (bad expert id, full receive area) contribute nothing
         const int e = p.topk_ids[t * p.topk + lane];
-        const int d = e / p.E_local;
-        const size_t slot = static_cast<size_t>(d) * p.max_m + (p.pair_pos[t * p.topk + lane] - cum[d * p.E_local]);
-        my_src = p.comb[par] + slot * row_bytes;
-        if (p.topk_weight) my_w = p.topk_weight[t * p.topk + lane];
+        if (e >= 0 && e < p.E) {
+          const int d = e / p.E_local;
+          const int idx = p.pair_pos[t * p.topk + lane] - cum[d * p.E_local];
+          if (idx >= 0 && idx < p.max_m) {
+            my_src = p.comb[par] + (static_cast<size_t>(d) * p.max_m + idx) * row_bytes;
+            if (p.topk_weight) my_w = p.topk_weight[t * p.topk + lane];
+          }
+        }
       }
-      for (int i = lane * 16; i < row_bytes; i += 512) {
+      for (int base = 0; base < row_bytes; base += 512) {  // same trip count for every lane (shuffles inside)
+        const int i = base + lane * 16;
+        const bool in = i < row_bytes;
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         for (int k0 = 0; k0 < p.topk; k0 += 8) {  // up to eight copies in flight before the first add
           uint4 v[8];
@@ -290,8 +312,10 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const EpParams p
           for (int u = 0; u < 8; ++u) {
             const int k = k0 + u < p.topk ? k0 + u : k0;
             const uint8_t* src = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_src), k));
-            wk[u] = k0 + u < p.topk ? __shfl_sync(0xffffffffu, my_w, k) : 0.f;
-            v[u] = k0 + u < p.topk ? ld_v4_relaxed_sys(src + i) : make_uint4(0, 0, 0, 0);
+            const float w = __shfl_sync(0xffffffffu, my_w, k);
+            const bool use = in && k0 + u < p.topk && src != nullptr;
+            wk[u] = use ? w : 0.f;
+            v[u] = use ? ld_v4_relaxed_sys(src + i) : make_uint4(0, 0, 0, 0);
           }
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
@@ -304,8 +328,9 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const EpParams p
             }
           }
         }
-        st_v4(static_cast<uint8_t*>(p.out) + static_cast<size_t>(t) * row_bytes + i,
-              make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7])));
+        if (in)
+          st_v4(static_cast<uint8_t*>(p.out) + static_cast<size_t>(t) * row_bytes + i,
+                make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7])));
       }
     }
   }

@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(kChunk) moe_scatter_kernel(const MoeSortParams
   }
 }
 
-// ---- small problems in ONE launch (opt-in: B200DIST_MOE_SORT_SMALL=1): at most 8192 pairs and 1024 (segment, expert)
+// ---- small problems in ONE launch (B200DIST_MOE_SORT_SMALL=0 turns it off): at most 8192 pairs and 1024 (segment, expert)
 // groups. One CTA of 32 warps; warp w owns a contiguous block of pairs and counts them per group in its own row of a
 // shared [32][G] table (one leader lane per distinct group and 32-pair chunk, so no atomics), which also gives every
 // pair its rank among the warp's pairs of the same group. A scan over the warps per group, a scan over the groups,
@@ -328,7 +328,7 @@ static bool small_sort_enabled() {
   static int on = -1;
   if (on < 0) {
     const char* e = getenv("B200DIST_MOE_SORT_SMALL");
-    on = (e && e[0] == '1') ? 1 : 0;
+    on = (e && e[0] == '0') ? 0 : 1;
   }
   return on == 1;
 }

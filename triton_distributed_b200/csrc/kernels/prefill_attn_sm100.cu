@@ -34,7 +34,8 @@ constexpr int kPThreads = 256;
 struct PrefillParams {
   int Hq, Hkv, causal, bf16;
   const int* cu_q;      // [B + 1] first packed query row of every sequence
-  const int* cu_k;      // [B + 1] first packed key row of every sequence
+  const int* cu_k;      // [B + 1] first key row of every sequence (only [0, B) is read when k_lens is given)
+  const int* k_lens;    // nullable [B]: keys of every sequence; null = cu_k[b + 1] - cu_k[b] (packed sequences)
   float scale_log2e;    // softmax scale * log2(e)
   void* out;            // [total_q, Hq, 128]
   uint32_t* status;     // nullable: set non-zero when a pipeline wait expired
@@ -42,10 +43,11 @@ struct PrefillParams {
 
 // V [total_k, Hkv, 128] -> Vt [B * Hkv, 128, s_pad] (keys contiguous, zero beyond each sequence's length)
 __global__ void __launch_bounds__(256) transpose_v_kernel(const uint16_t* __restrict__ v, uint16_t* __restrict__ vt,
-                                                          const int* __restrict__ cu_k, int Hkv, int s_pad) {
+                                                          const int* __restrict__ cu_k, const int* __restrict__ k_lens,
+                                                          int Hkv, int s_pad) {
   __shared__ uint16_t tile[32][33];
   const int bh = blockIdx.z, b = bh / Hkv, kvh = bh - b * Hkv;
-  const int k_start = cu_k[b], k_len = cu_k[b + 1] - k_start;
+  const int k_start = cu_k[b], k_len = k_lens ? k_lens[b] : cu_k[b + 1] - k_start;
   const int s0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
   for (int i = ty; i < 32; i += 8) {
@@ -64,7 +66,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const __grid_constant__ CUtensorMap tmVt, const PrefillParams p) {
   const int m_blk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int q_start = p.cu_q[b], q_len = p.cu_q[b + 1] - q_start;
-  const int k_start = p.cu_k[b], k_len = p.cu_k[b + 1] - k_start;
+  const int k_start = p.cu_k[b], k_len = p.k_lens ? p.k_lens[b] : p.cu_k[b + 1] - k_start;
   if (m_blk * kPM >= q_len) return;  // uniform over the CTA, before anything is allocated
   const int kvh = h / (p.Hq / p.Hkv);
   const int offset = k_len - q_len;  // bottom-right alignment of the causal mask
@@ -309,10 +311,14 @@ B200_API long long b200_prefill_attention_scratch_bytes(int B, int Hkv, int max_
   return static_cast<long long>(B) * Hkv * kPD * s_pad * 2;
 }
 
-// q [total_q, Hq, 128], k / v [total_k, Hkv, 128] (packed sequences, contiguous), cu_q / cu_k int32 [B + 1] on the
-// device, out [total_q, Hq, 128]. With causal != 0 query i of a sequence attends keys <= i + (k_len - q_len).
-// vt_scratch: b200_prefill_attention_scratch_bytes(...) bytes, 16-byte aligned. dtype 0 = bf16, 1 = f16.
-B200_API int b200_prefill_attention(const void* q, const void* k, const void* v, const int* cu_q, const int* cu_k, int B,
+// q [total_q, Hq, 128], k / v [total_k, Hkv, 128] (contiguous rows), cu_q / cu_k int32 [B + 1] on the device, out
+// [total_q, Hq, 128]. Sequence b's keys are rows [cu_k[b], cu_k[b] + len) with len = k_lens[b], or cu_k[b + 1] - cu_k[b]
+// when k_lens is null (packed sequences); with k_lens the key rows may sit anywhere in k / v, e.g. in the pages of a
+// KV cache whose sequences own contiguous runs of slots. With causal != 0 query i of a sequence attends keys
+// <= i + (k_len - q_len). vt_scratch: b200_prefill_attention_scratch_bytes(...) bytes, 16-byte aligned.
+// dtype 0 = bf16, 1 = f16.
+B200_API int b200_prefill_attention(const void* q, const void* k, const void* v, const int* cu_q, const int* cu_k,
+                                    const int* k_lens, int B,
                                     int total_q, int total_k, int max_q, int max_k, int Hq, int Hkv, int head_dim,
                                     float scale, int causal, void* vt_scratch, void* out, int dtype, uint32_t* status,
                                     void* stream) {
@@ -324,7 +330,7 @@ B200_API int b200_prefill_attention(const void* q, const void* k, const void* v,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int s_pad = (max_k + 127) / 128 * 128;
   transpose_v_kernel<<<dim3(s_pad / 32, kPD / 32, B * Hkv), 256, 0, s>>>(static_cast<const uint16_t*>(v),
-                                                                          static_cast<uint16_t*>(vt_scratch), cu_k, Hkv, s_pad);
+                                                                          static_cast<uint16_t*>(vt_scratch), cu_k, k_lens, Hkv, s_pad);
   B200_CHECK_CUDA(cudaGetLastError());
   CUtensorMap tq, tk, tv;
   int rc = make_tma_3d(&tq, q, dtype, kPD, Hq, total_q, kPD, static_cast<uint64_t>(Hq) * kPD, 64, 1, kPM, true);
@@ -344,7 +350,7 @@ B200_API int b200_prefill_attention(const void* q, const void* k, const void* v,
   PrefillParams p;
   memset(&p, 0, sizeof(p));
   p.Hq = Hq; p.Hkv = Hkv; p.causal = causal; p.bf16 = dtype == kBF16;
-  p.cu_q = cu_q; p.cu_k = cu_k;
+  p.cu_q = cu_q; p.cu_k = cu_k; p.k_lens = k_lens;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.out = out; p.status = status;
   dim3 grid((max_q + kPM - 1) / kPM, Hq, B);

@@ -75,7 +75,7 @@ class AllGatherGEMMTensorParallelContext:
         return int(self.sync[0].item())
 
     def finalize(self) -> None:
-        torch.cuda.synchronize()
+        self.heap.sync_and_check(type(self).__name__)
         for t in self.symm_workspaces + [self.symm_ready] + ([self.symm_blk_cnt] if self.symm_blk_cnt is not None else []):
             self.heap.free(t)
         self.symm_workspaces = []

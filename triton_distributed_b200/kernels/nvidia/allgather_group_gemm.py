@@ -56,7 +56,7 @@ class MoEAllGatherGroupGEMMTensorParallelContext:
         raise ValueError(f"weights {tuple(b.shape)} match neither [E, {self.N_per_rank}, {self.K}] nor [E, {self.K}, {self.N_per_rank}]")
 
     def finalize(self) -> None:
-        torch.cuda.synchronize()
+        self.heap.sync_and_check(type(self).__name__)
         for t in self.symm_workspaces + [self.symm_ready]:
             self.heap.free(t)
         self.symm_workspaces = []

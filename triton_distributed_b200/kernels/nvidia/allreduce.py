@@ -54,7 +54,7 @@ class AllReduceContext:
     max_ctas: int
 
     def finalize(self) -> None:
-        torch.cuda.synchronize()
+        self.heap.sync_and_check(type(self).__name__)
         for t in self.workspaces + [self.flags] + list(getattr(self, "ll_ws", None) or []):
             self.heap.free(t)
         self.workspaces = []

@@ -51,9 +51,10 @@ def gqa_fwd_batch_decode_intra_rank(q, k_cache, v_cache, workspace, q_lens, kv_l
 def gqa_fwd_batch_decode_persistent(q, k_cache, v_cache, workspace, q_lens, kv_lens, block_table, scale,
                                     soft_cap: float = 0.0, output_split=None, output_combine=None, kv_split: int = -1,
                                     max_kv_len: int | None = None):
-    """The reference fuses split + grid barrier + combine in one cooperative launch sized for 132 SMs; here the
-    split kernel writes the final output directly when one split suffices and otherwise a second tiny launch
-    merges, sized from the device's SM count."""
+    """Split + combine in ONE launch (reference: flash_decode.py:587-760, a cooperative launch of 132 CTAs with a grid
+    barrier between the phases). Here no CTA waits for another: every CTA of a (batch, head group) draws a ticket
+    once its partial is visible and the one that draws the last merges the partials, so the grid may be larger than
+    the machine and needs no co-residency. ``gqa_fwd_batch_decode`` takes the same path."""
     return gqa_fwd_batch_decode(q, k_cache, v_cache, workspace, q_lens, kv_lens, block_table, scale, soft_cap,
                                 output_split, output_combine, kv_split, max_kv_len)
 

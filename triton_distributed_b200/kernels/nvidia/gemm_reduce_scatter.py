@@ -45,7 +45,7 @@ class GEMMReduceScatterTensorParallelContext:
     stage: torch.Tensor | None = None   # local [max_M, N] staging of the opt-in forwarding variant
 
     def finalize(self) -> None:
-        torch.cuda.synchronize()
+        self.heap.sync_and_check(type(self).__name__)
         for t in self.slots + [self.rs_cnt]:
             self.heap.free(t)
         self.slots = []

@@ -40,7 +40,7 @@ class AllToAllContext:
         return self.calls + 1
 
     def finalize(self) -> None:
-        torch.cuda.synchronize()
+        self.heap.sync_and_check(type(self).__name__)
         for t in self.recv_bufs + self.scale_recv_bufs + self.split_recv_bufs + [self.flags]:
             self.heap.free(t)
         self.recv_bufs = []

@@ -38,7 +38,7 @@ class FastAllGatherContext:
     max_ctas: int
 
     def finalize(self) -> None:
-        torch.cuda.synchronize()
+        self.heap.sync_and_check(type(self).__name__)
         for t in self.ll_buffers + [self.flags]:
             self.heap.free(t)
         self.ll_buffers = []

@@ -60,7 +60,7 @@ class MoEReduceRSContext:
         return self.plans[ntokens]
 
     def finalize(self) -> None:
-        torch.cuda.synchronize()
+        self.heap.sync_and_check(type(self).__name__)
         for t in self.slots + [self.rs_cnt]:
             self.heap.free(t)
         self.slots = []

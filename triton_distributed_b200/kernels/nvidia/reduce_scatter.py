@@ -30,7 +30,7 @@ class ReduceScatter2DContext:
     sync: torch.Tensor
 
     def finalize(self) -> None:
-        torch.cuda.synchronize()
+        self.heap.sync_and_check(type(self).__name__)
         for t in self.workspaces + [self.flags]:
             self.heap.free(t)
         self.workspaces = []

@@ -5,19 +5,22 @@ API parity with ``python/triton_dist/kernels/nvidia/sp_ag_attention_intra_node.p
 sequence, every rank's K/V shard is gathered into a symmetric buffer, and each rank runs causal variable-length
 attention of its Q rows over the gathered keys, with the zig-zag sharding that balances causal work.
 
-As in the reference snapshot, the gather completes before attention starts (its kernel has no per-shard wait,
-:159-183). The gather is this library's push all-gather kernel over NVLink; the attention math is the library SDPA
-call, which is the role flash-attn plays for the reference's layers. The inter-node twin is out of scope.
+Two native launches and no host synchronisation: ``sp_kv_scatter_kernel`` pushes every local K / V row over NVLink into
+the row of its global position in every rank's buffer (the zig-zag permutation is folded into the gather), and the
+tcgen05 prefill attention kernel then treats every (sequence, local chunk) as one causal problem whose keys are the
+contiguous prefix that chunk may see: chunk r of a sequence cut into 2 * world chunks attends the first (r + 1)
+chunks with the bottom-right aligned mask. As in the reference snapshot the gather completes before attention starts
+(its kernel has no per-shard wait, :159-183). Head dim 128. The inter-node twin is out of scope.
 """
 from __future__ import annotations
 
 import dataclasses
 
 import torch
-import torch.nn.functional as F
 
+from ... import _lib, ops
+from ..._lib import ptr, stream_ptr
 from ...runtime.heap import SymmHeap, get_heap
-from .low_latency_allgather import FastAllGatherContext, create_fast_allgather_context, fast_allgather
 
 
 @dataclasses.dataclass
@@ -25,26 +28,26 @@ class SPAllGatherAttentionContextIntraNode:
     rank: int
     world_size: int
     heap: SymmHeap
-    ag_ctx: FastAllGatherContext
-    k_buffer: torch.Tensor   # symmetric [world, max_kv_shard_tokens, kv_head, head_dim]
+    k_buffer: torch.Tensor   # symmetric [max total keys, kv_head, head_dim], global token order
     v_buffer: torch.Tensor
 
     def finalize(self) -> None:
-        torch.cuda.synchronize()
+        self.heap.sync_and_check(type(self).__name__)
         self.heap.free(self.k_buffer)
         self.heap.free(self.v_buffer)
-        self.ag_ctx.finalize()
 
 
 def create_sp_ag_attention_context_intra_node(batch_size: int, q_head: int, kv_head: int, max_seqlen_k: int,
                                               max_q_shard_len: int, head_dim: int, input_dtype, output_dtype, rank: int,
                                               world_size: int, device="cuda") -> SPAllGatherAttentionContextIntraNode:
+    """Buffers for up to ``batch_size`` sequences of up to ``max_seqlen_k`` keys each (global lengths)."""
+    if head_dim != 128:
+        raise NotImplementedError("the native prefill attention is specialised for head_dim 128")
     heap = get_heap()
-    shard = batch_size * ((max_seqlen_k + world_size - 1) // world_size)
-    kb = heap.create_tensor((world_size, shard, kv_head, head_dim), input_dtype, align=1024)
-    vb = heap.create_tensor((world_size, shard, kv_head, head_dim), input_dtype, align=1024)
-    ag = create_fast_allgather_context(rank, 0, world_size, 1, max_buffer_size=16)
-    return SPAllGatherAttentionContextIntraNode(rank, world_size, heap, ag, kb, vb)
+    rows = batch_size * ((max_seqlen_k + world_size - 1) // world_size) * world_size
+    kb = heap.create_tensor((rows, kv_head, head_dim), input_dtype, align=1024)
+    vb = heap.create_tensor((rows, kv_head, head_dim), input_dtype, align=1024)
+    return SPAllGatherAttentionContextIntraNode(rank, world_size, heap, kb, vb)
 
 
 def zigzag_positions(seq_len: int, rank: int, world: int, device) -> torch.Tensor:
@@ -60,41 +63,38 @@ def fused_sp_ag_attn_intra_node(ctx: SPAllGatherAttentionContextIntraNode, q_sha
                                 v_shard: torch.Tensor, output: torch.Tensor | None, cu_seqlens_q: torch.Tensor,
                                 cu_seqlens_k: torch.Tensor, max_seqlen_q: int, max_seqlen_k: int, rank: int,
                                 world_size: int, is_causal: bool = True, enable_zig_zag: bool = True) -> torch.Tensor:
-    """q_shard [sum_q_local, Hq, D]; k_shard / v_shard [sum_k_local, Hkv, D] (this rank's tokens of every sequence,
+    """q_shard [sum_q_local, Hq, 128]; k_shard / v_shard [sum_k_local, Hkv, 128] (this rank's tokens of every sequence,
     concatenated); cu_seqlens_q int32 [B + 1] over the LOCAL q tokens; cu_seqlens_k int32 [B + 1] over the GLOBAL keys.
-    Every sequence length must be divisible by ``2 * world`` (zig-zag) or ``world``. Returns [sum_q_local, Hq, D]."""
-    n_local = k_shard.shape[0]
-    ctx.k_buffer[rank, :n_local].copy_(k_shard)
-    ctx.v_buffer[rank, :n_local].copy_(v_shard)
-    ctx.heap.barrier_all()
-    fast_allgather(ctx.k_buffer, ctx.ag_ctx, mode="push2d")
-    fast_allgather(ctx.v_buffer, ctx.ag_ctx, mode="push2d")
-    if output is None:
-        output = torch.empty_like(q_shard)
-    cu_q, cu_k = cu_seqlens_q.tolist(), cu_seqlens_k.tolist()
-    scale = q_shard.shape[-1] ** -0.5
-    for b in range(len(cu_q) - 1):
-        Lk = cu_k[b + 1] - cu_k[b]
-        lk_local = Lk // world_size
-        k_off = cu_k[b] // world_size
-        # assemble the sequence's keys in global order from the per-rank shards
-        k_full = torch.empty((Lk, *k_shard.shape[1:]), dtype=k_shard.dtype, device=k_shard.device)
-        v_full = torch.empty_like(k_full)
-        for r in range(world_size):
-            pos = zigzag_positions(Lk, r, world_size, k_shard.device) if enable_zig_zag else torch.arange(
-                r * lk_local, (r + 1) * lk_local, device=k_shard.device)
-            k_full[pos] = ctx.k_buffer[r, k_off:k_off + lk_local]
-            v_full[pos] = ctx.v_buffer[r, k_off:k_off + lk_local]
-        q = q_shard[cu_q[b]:cu_q[b + 1]]
-        lq = q.shape[0]
-        qpos = zigzag_positions(Lk, rank, world_size, q.device) if enable_zig_zag else torch.arange(
-            rank * lq, (rank + 1) * lq, device=q.device)
-        mask = (torch.arange(Lk, device=q.device)[None, :] <= qpos[:, None]) if is_causal else None
-        o = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k_full.transpose(0, 1)[None], v_full.transpose(0, 1)[None],
-                                           attn_mask=mask, scale=scale, enable_gqa=True)
-        output[cu_q[b]:cu_q[b + 1]] = o[0].transpose(0, 1)
-    ctx.heap.barrier_all()
-    return output
+    Every sequence length must be divisible by ``2 * world`` (zig-zag) or ``world``. Returns [sum_q_local, Hq, 128]."""
+    dev = q_shard.device
+    W = world_size
+    k_shard, v_shard = k_shard.contiguous(), v_shard.contiguous()
+    cu_q = cu_seqlens_q.to(device=dev, dtype=torch.int32)
+    cu_k = cu_seqlens_k.to(device=dev, dtype=torch.int32).contiguous()
+    B = cu_k.numel() - 1
+    row_bytes = k_shard.shape[1] * k_shard.shape[2] * k_shard.element_size()
+    if max_seqlen_k * B > ctx.k_buffer.shape[0]:
+        raise ValueError("the batch does not fit the context's gather buffers")
+    _lib.call("b200_sp_kv_scatter", ctx.heap.ctx, ptr(k_shard), ptr(v_shard), ptr(ctx.k_buffer), ptr(ctx.v_buffer), ptr(cu_k),
+              B, k_shard.shape[0], row_bytes, 1 if enable_zig_zag else 0, stream_ptr())
+    ops._count()
+    ctx.heap.barrier_all()   # every rank's rows have landed everywhere
+    # one causal problem per (sequence, local chunk): queries = the chunk, keys = the prefix the chunk may see
+    lq = cu_q[1:] - cu_q[:-1]
+    if not is_causal:
+        cu_q2, cu_k2, k_lens, max_q = cu_q, cu_k, cu_k[1:] - cu_k[:-1], max_seqlen_q
+    elif enable_zig_zag:
+        c = lq // 2
+        cu_q2 = torch.cat([torch.stack([cu_q[:-1], cu_q[:-1] + c], 1).reshape(-1), cu_q[-1:]])
+        cu_k2 = torch.cat([cu_k[:-1].repeat_interleave(2), cu_k[-1:]])
+        k_lens = torch.stack([(rank + 1) * c, (2 * W - rank) * c], 1).reshape(-1)
+        max_q = (max_seqlen_q + 1) // 2
+    else:
+        cu_q2, cu_k2, k_lens, max_q = cu_q, cu_k, (rank + 1) * lq, max_seqlen_q
+    out = ops.prefill_attention(q_shard.contiguous(), ctx.k_buffer, ctx.v_buffer, cu_q2, cu_k2, max_q, max_seqlen_k,
+                                q_shard.shape[-1] ** -0.5, is_causal, out=output, seqlens_k=k_lens)
+    ctx.heap.barrier_all()   # nobody overwrites the buffers of a rank that is still reading them
+    return out
 
 
 def create_sp_ag_attention_context_inter_node(*args, **kwargs):

@@ -104,7 +104,7 @@ class EPAll2AllLayer:
         return out
 
     def finalize(self) -> None:
-        torch.cuda.synchronize()
+        self.heap.sync_and_check(type(self).__name__)
         for t in self.recv + self.recv_scale + self.recv_splits + self.comb + [self.dflags, self.cflags]:
             self.heap.free(t)
         self.recv = []

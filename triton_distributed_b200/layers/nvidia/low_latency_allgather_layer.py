@@ -53,7 +53,7 @@ class AllGatherLayer:
     forward_push_3d_ll = forward_push_numa_2d_ll = forward_push_numa_2d_ll_multinode = forward_push_2d_ll
 
     def finalize(self) -> None:
-        torch.cuda.synchronize()
+        self.heap.sync_and_check(type(self).__name__)
         for b in self.buffers:
             self.heap.free(b)
         self.buffers = []

@@ -54,14 +54,15 @@ class SpGQAFlashDecodeAttention:
         if max_kv_len is None:
             max_kv_len = block_table.shape[1] * k_cache.shape[1]
         S = kv_split if kv_split > 0 else ops.choose_kv_splits(B, self.num_kv_heads, Hq // self.num_kv_heads, max_kv_len)
-        key = (B, S)
-        if key not in self._ws:
-            self._ws = {key: (torch.empty(B * Hq * S * D, dtype=torch.float32, device=q.device),
-                              torch.empty(B * Hq * S, dtype=torch.float32, device=q.device))}
-        o_part, lse_part = self._ws[key]
-        _lib.call("b200_decode_attn_split", ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.stride(0),
+        need = B * Hq * S
+        if self._ws.get("rows", 0) < need:  # grows to the largest (batch, splits) seen, then stays: nothing is
+            self._ws = {"rows": need,        # allocated once the shapes of a serving loop have been met
+                        "o": torch.empty(need * D, dtype=torch.float32, device=q.device),
+                        "lse": torch.empty(need, dtype=torch.float32, device=q.device)}
+        o_part, lse_part = self._ws["o"], self._ws["lse"]
+        _lib.call("b200_decode_attn", ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.stride(0),
                   ptr(kv_lens), B, Hq, self.num_kv_heads, D, k_cache.shape[1], c_float(self.scale), c_float(self.soft_cap), S,
-                  ptr(o_part), ptr(lse_part), None, None, dtype_code(q.dtype), stream_ptr())
+                  ptr(o_part), ptr(lse_part), None, None, None, dtype_code(q.dtype), -1, stream_ptr())
         out = torch.empty_like(q)
         _lib.call("b200_sp_decode_combine", self.heap.ctx, ptr(o_part), ptr(lse_part), B * Hq, S, ptr(self.ll[0]),
                   ptr(self.ll[1]), ptr(self.sync), ptr(out), None, dtype_code(q.dtype), 1 if self.use_multicast else 0,
@@ -72,7 +73,7 @@ class SpGQAFlashDecodeAttention:
     __call__ = forward
 
     def finalize(self) -> None:
-        torch.cuda.synchronize()
+        self.heap.sync_and_check(type(self).__name__)
         for t in self.ll:
             self.heap.free(t)
         self.ll = []

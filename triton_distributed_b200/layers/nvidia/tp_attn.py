@@ -6,13 +6,12 @@ forward modes ``torch_fwd`` / ``dist_triton_fwd`` / ``dist_triton_AR_fwd``. Head
 ``wqkv = [q shard; k shard; v shard]`` (rows), ``wo`` column shard (:100-105).
 
 The reference calls flashinfer for norm/rope and flash-attn for attention + cache append; here one native
-kernel does head-norm + RoPE + cache write and the paged decode kernel does attention. Prefill attention
-(many query tokens) uses torch SDPA, the same library role flash-attn has in the reference.
+kernel does head-norm + RoPE + cache write, the paged decode kernel does single-token attention and the tcgen05
+prefill kernel does many-token attention. The ``torch`` mode keeps the library composition as golden and baseline.
 """
 from __future__ import annotations
 
 import math
-import os
 
 import torch
 import torch.distributed as dist
@@ -22,6 +21,7 @@ from ... import ops
 from ...kernels.allreduce import AllReduceMethod
 from ...kernels.nvidia import (ag_gemm, all_reduce, create_ag_gemm_context, create_allreduce_ctx,
                                create_gemm_rs_context, gemm_rs)
+from . import golden
 from .tp_mlp import shard_local
 
 
@@ -40,17 +40,7 @@ def _set_cos_sin_cache(inv_freq: torch.Tensor, max_length: int) -> torch.Tensor:
     return torch.cat([freqs.cos(), freqs.sin()], dim=-1).contiguous()
 
 
-def _rope_torch(x: torch.Tensor, cos_sin: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
-    """x [T, H, D] (any float dtype), neox style."""
-    D = x.shape[-1]
-    cs = cos_sin[pos.long()]
-    cos, sin = cs[:, None, : D // 2], cs[:, None, D // 2:]
-    xf = x.float()
-    x1, x2 = xf[..., : D // 2], xf[..., D // 2:]
-    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1).to(x.dtype)
-
-
-_PREFILL_NATIVE = os.environ.get("B200DIST_PREFILL_NATIVE", "0") == "1"
+_rope_torch = golden.rope_torch
 
 
 class TP_Attn:
@@ -127,53 +117,33 @@ class TP_Attn:
             out = ops.decode_attention(q, kp, vp, step["kv_lens"], kv_cache.block_table, self.scale, 0.0, splits,
                                        workspace=self._attn_ws)
             return out.view(bsz, -1)
-        # prefill from an empty cache: causal attention over this chunk (library SDPA)
-        kf = kp.view(-1, self.kv_heads_local, self.head_dim)[step["slots"]].view(bsz, seqlen, self.kv_heads_local, self.head_dim)
-        vf = vp.view(-1, self.kv_heads_local, self.head_dim)[step["slots"]].view(bsz, seqlen, self.kv_heads_local, self.head_dim)
-        if _PREFILL_NATIVE and self.head_dim == 128:
-            # opt-in: the tcgen05 prefill kernel on the packed [B * S, heads, 128] layout (equal-length sequences here)
-            cu = torch.arange(0, (bsz + 1) * seqlen, seqlen, dtype=torch.int32, device=qkv.device)
-            o = ops.prefill_attention(q.reshape(bsz * seqlen, self.q_heads_local, self.head_dim).contiguous(),
-                                      kf.reshape(bsz * seqlen, self.kv_heads_local, self.head_dim).contiguous(),
-                                      vf.reshape(bsz * seqlen, self.kv_heads_local, self.head_dim).contiguous(),
-                                      cu, cu, seqlen, seqlen, self.scale, True)
-            return o.reshape(bsz * seqlen, -1)
-        o = F.scaled_dot_product_attention(q.view(bsz, seqlen, self.q_heads_local, self.head_dim).transpose(1, 2),
-                                           kf.transpose(1, 2), vf.transpose(1, 2), is_causal=True, enable_gqa=True)
-        return o.transpose(1, 2).reshape(bsz * seqlen, -1)
+        # prefill: the tcgen05 attention kernel reads this chunk's keys and values in place from the cache (sequence b
+        # owns a contiguous run of slots), causal with bottom-right alignment, so a chunk after a cached prefix works too
+        if self.head_dim != 128:
+            raise NotImplementedError("the native prefill attention is specialised for head_dim 128")
+        L = kv_cache.blocks_per_seq * kv_cache.page_size
+        cu_q = torch.arange(0, (bsz + 1) * seqlen, seqlen, dtype=torch.int32, device=qkv.device)
+        cu_k = torch.arange(0, (bsz + 1) * L, L, dtype=torch.int32, device=qkv.device)
+        o = ops.prefill_attention(q, kp.view(-1, self.kv_heads_local, self.head_dim), vp.view(-1, self.kv_heads_local, self.head_dim),
+                                  cu_q, cu_k, seqlen, min(L, kv_cache.max_length), self.scale, True, seqlens_k=step["kv_lens"])
+        return o.reshape(bsz * seqlen, -1)
 
     def _attn_torch(self, qkv, position_ids, cos_sin_cache, kv_cache, layer_idx, bsz, seqlen):
-        """Pure torch: the golden for the native core."""
+        """The library composition of the reference's torch mode (tp_attn.py:159-195): q/k RMSNorm and RoPE from
+        flashinfer, attention and the cache append from ``flash_attn_with_kvcache`` on this sequence's contiguous run
+        of pages; each call falls back to its PyTorch statement when the library is unusable (see ``golden.py``)."""
         D, Hq, Hkv = self.head_dim, self.q_heads_local, self.kv_heads_local
         q, k, v = qkv.view(bsz * seqlen, -1).split([Hq * D, Hkv * D, Hkv * D], dim=-1)
-        q, k, v = q.reshape(-1, Hq, D), k.reshape(-1, Hkv, D), v.reshape(-1, Hkv, D)
+        q, k, v = q.reshape(-1, Hq, D).contiguous(), k.reshape(-1, Hkv, D).contiguous(), v.reshape(-1, Hkv, D)
         if self.q_norm_w is not None:
-            q, k = layer_norm(q, self.eps, self.q_norm_w), layer_norm(k, self.eps, self.k_norm_w)
-        q, k = self.apply_rotary_pos_emb(q, k, cos_sin_cache, position_ids)
+            q, k = golden.rmsnorm(q, self.q_norm_w, self.eps), golden.rmsnorm(k, self.k_norm_w, self.eps)
+        q, k = golden.rope_(q, k, cos_sin_cache, position_ids.reshape(-1))
         kp, vp = kv_cache.layer(layer_idx)
-        slots = kv_cache.slots(position_ids)
-        kp.view(-1, Hkv, D)[slots] = k
-        vp.view(-1, Hkv, D)[slots] = v
-        if seqlen == 1:
-            # decode: no host sync (CUDA-graph capturable). Sequence b owns a contiguous run of pages, so its
-            # keys are a view of the cache; positions beyond the current length are masked.
-            L = kv_cache.blocks_per_seq * kv_cache.page_size
-            kb = kp.view(bsz, L, Hkv, D).transpose(1, 2)
-            vb = vp.view(bsz, L, Hkv, D).transpose(1, 2)
-            mask = (torch.arange(L, device=qkv.device)[None, :] <= position_ids[:, -1:]).view(bsz, 1, 1, L)
-            ob = F.scaled_dot_product_attention(q.view(bsz, 1, Hq, D).transpose(1, 2), kb, vb, attn_mask=mask, enable_gqa=True)
-            return ob.transpose(1, 2).reshape(bsz, Hq * D)
-        outs = []
-        for b in range(bsz):
-            L = int(position_ids[b, -1].item()) + 1
-            sl = torch.arange(L, device=qkv.device) + b * kv_cache.blocks_per_seq * kv_cache.page_size
-            kb = kp.view(-1, Hkv, D)[sl].transpose(0, 1)[None]
-            vb = vp.view(-1, Hkv, D)[sl].transpose(0, 1)[None]
-            qb = q.view(bsz, seqlen, Hq, D)[b].transpose(0, 1)[None]
-            mask = torch.arange(L, device=qkv.device)[None, :] <= position_ids[b][:, None]
-            ob = F.scaled_dot_product_attention(qb, kb, vb, attn_mask=mask, enable_gqa=True)
-            outs.append(ob[0].transpose(0, 1).reshape(seqlen, Hq * D))
-        return torch.cat(outs, 0)
+        L = kv_cache.blocks_per_seq * kv_cache.page_size
+        o = golden.attention_with_kvcache(q.view(bsz, seqlen, Hq, D), k.view(bsz, seqlen, Hkv, D),
+                                          v.reshape(bsz, seqlen, Hkv, D), kp.view(bsz, L, Hkv, D), vp.view(bsz, L, Hkv, D),
+                                          position_ids[:, 0].to(torch.int32).contiguous())
+        return o.reshape(bsz * seqlen, Hq * D)
 
     # ------------------------------------------------------------------ forwards
     @torch.no_grad()

@@ -130,6 +130,9 @@ class Engine:
         for _ in range(gen_len - 1):
             out.append(self.decode_one())
         torch.cuda.synchronize()
+        from ..runtime.heap import get_heap, heap_initialized
+        if heap_initialized():
+            get_heap().check_status("Engine.serve")  # an expired wait means tokens computed from incomplete sums
         if prof is not None:
             prof.__exit__(None, None, None)
             prof.export_chrome_trace(f"decode_rank{self.model_config.rank}.json")

@@ -23,7 +23,7 @@ from .. import ops
 from ..kernels.allreduce import AllReduceMethod
 from ..kernels.nvidia import (all_reduce_rmsnorm, create_ag_gemm_context, create_allreduce_ctx,
                               create_gemm_rs_context)
-from ..layers.nvidia import TP_MLP, TP_Attn, TP_MoE, _set_cos_sin_cache, layer_norm
+from ..layers.nvidia import TP_MLP, TP_Attn, TP_MoE, _set_cos_sin_cache, golden, layer_norm
 from .config import ArchConfig, ModelConfig
 from .kv_cache import KV_Cache
 from .utils import logger
@@ -76,15 +76,19 @@ class Qwen3Layer:
     @torch.no_grad()
     def fwd(self, hidden, position_ids, cos_sin_cache, kv_cache, step=None):
         """Unfused layer forward for the ``torch`` and ``triton_dist`` modes (pre-norm residual block)."""
+        if self.mode == "torch":  # the library composition (flashinfer norm when usable)
+            def norm(h, w): return golden.rmsnorm(h, w, self.eps)
+        else:
+            def norm(h, w): return layer_norm(h, self.eps, w)
         residual = hidden
-        x = layer_norm(hidden, self.eps, self.input_norm_w)
+        x = norm(hidden, self.input_norm_w)
         if self.mode == "torch":
             x = self.attn.torch_fwd(x, position_ids, cos_sin_cache, kv_cache, self.layer_idx)
         else:
             x = self.attn.dist_triton_fwd(x, position_ids, cos_sin_cache, kv_cache, self.layer_idx, step=step)
         hidden = residual + x
         residual = hidden
-        x = layer_norm(hidden, self.eps, self.post_norm_w)
+        x = norm(hidden, self.post_norm_w)
         x2 = x.reshape(-1, x.shape[-1])
         x2 = self.mlp.torch_fwd(x2) if self.mode == "torch" else self.mlp.dist_triton_fwd(x2)
         return residual + x2.reshape(x.shape)
@@ -229,7 +233,8 @@ class Qwen3:
                         "kv_lens": (position_ids[:, -1] + 1).to(torch.int32)}
             for layer in self.layers:
                 hidden = layer.fwd(hidden, position_ids, self.cos_sin_cache, kv_cache, step)
-            hidden = layer_norm(hidden, self.eps, self.norm_w)
+            hidden = (golden.rmsnorm(hidden, self.norm_w, self.eps) if self.mode == "torch"
+                      else layer_norm(hidden, self.eps, self.norm_w))
             if self.mode == "triton_dist":
                 full = torch.empty((bsz, seqlen, hidden.shape[-1]), dtype=hidden.dtype, device=hidden.device)
                 dist.all_gather_into_tensor(full, hidden.contiguous(), group=self.group)

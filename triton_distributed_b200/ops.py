@@ -193,23 +193,35 @@ def top_p_sample(logits: torch.Tensor, temperature: float, top_p: float, uniform
     return out
 
 
-_ATTN_FUSED_COMBINE = os.environ.get("B200DIST_ATTN_FUSED_COMBINE", "0") == "1"
 _attn_tickets: dict = {}
 
 
 def choose_kv_splits(batch: int, num_kv_heads: int, group: int, max_kv_len: int, sm_count: int = 148) -> int:
-    """Split count so that batch x kv-heads x splits fills the machine about twice, with >= 256 tokens per split."""
+    """Split count for the decode kernel: one wave of CTAs at two per SM (the per-warp-ring kernel keeps 96 KB of
+    shared memory per CTA), at least 512 tokens per split so that the merge stays small next to the stream.
+    ``B200DIST_KV_SPLITS`` forces a value (for experiments)."""
+    forced = os.environ.get("B200DIST_KV_SPLITS")
+    if forced:
+        return max(1, int(forced))
     ctas = batch * num_kv_heads * ((group + 15) // 16)
-    want = max(1, (2 * sm_count + ctas - 1) // ctas)
-    by_len = max(1, max_kv_len // 256)
-    return int(max(1, min(want, by_len, 128)))
+    by_machine = max(1, (2 * sm_count) // max(ctas, 1))
+    by_len = max(1, max_kv_len // 512)
+    return int(max(1, min(by_machine, by_len, 64)))
+
+
+_FUSED_COMBINE_DEFAULT = os.environ.get("B200DIST_ATTN_FUSED_COMBINE", "1") != "0"
 
 
 def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_lens: torch.Tensor,
                      block_table: torch.Tensor, scale: float, soft_cap: float = 0.0, num_splits: int = 1,
-                     out: torch.Tensor | None = None, return_lse: bool = False, workspace: dict | None = None):
+                     out: torch.Tensor | None = None, return_lse: bool = False, workspace: dict | None = None,
+                     fused_combine: bool | None = None, ring: int = -1):
     """Paged GQA decode attention. q [B,Hq,128]; caches [num_blocks, page, Hkv, 128]; kv_lens int32 [B];
-    block_table int32 [B, max_blocks]. Returns out [B,Hq,128] (and natural-log LSE fp32 [B,Hq])."""
+    block_table int32 [B, max_blocks]. Returns out [B,Hq,128] (and natural-log LSE fp32 [B,Hq]).
+
+    With ``num_splits > 1`` the last CTA of every (batch, head group) merges the split partials inside the same
+    launch (``fused_combine=False`` runs the separate combine kernel instead). ``ring`` selects the K/V pipeline:
+    0 = two-stage CTA-wide, 3 / 6 = per-warp rings of that depth, -1 = the library default."""
     _lib.require_cuda()
     B, Hq, D = q.shape
     page, Hkv = k_cache.shape[1], k_cache.shape[2]
@@ -217,7 +229,10 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         raise ValueError("decode_attention needs contiguous q / caches and a row-major block table")
     if out is None:
         out = torch.empty_like(q)
+    if fused_combine is None:
+        fused_combine = _FUSED_COMBINE_DEFAULT
     lse = torch.empty((B, Hq), dtype=torch.float32, device=q.device) if return_lse else None
+    tickets = None
     if num_splits > 1:
         if workspace is not None and "o_part" in workspace and workspace["o_part"].numel() >= B * Hq * num_splits * D:
             o_part, lse_part = workspace["o_part"], workspace["lse_part"]
@@ -226,27 +241,20 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
             lse_part = torch.empty(B * Hq * num_splits, dtype=torch.float32, device=q.device)
             if workspace is not None:
                 workspace["o_part"], workspace["lse_part"] = o_part, lse_part
+        if fused_combine:
+            n_groups = B * Hkv * ((Hq // Hkv + 15) // 16)
+            holder = workspace if workspace is not None else _attn_tickets.setdefault(q.device, {})
+            tickets = holder.get("tickets")
+            if tickets is None or tickets.numel() < n_groups or tickets.device != q.device:
+                tickets = torch.zeros(max(n_groups, 1024), dtype=torch.int32, device=q.device)
+                holder["tickets"] = tickets
     else:
         o_part = lse_part = None
-    if num_splits > 1 and _ATTN_FUSED_COMBINE:
-        # opt-in: the last CTA of every (batch, head group) merges the splits, so no combine launch follows
-        G = Hq // Hkv
-        n_groups = B * Hkv * ((G + 15) // 16)
-        holder = workspace if workspace is not None else _attn_tickets
-        tickets = holder.get("tickets")
-        if tickets is None or tickets.numel() < n_groups or tickets.device != q.device:
-            tickets = torch.zeros(max(n_groups, 1024), dtype=torch.int32, device=q.device)
-            holder["tickets"] = tickets
-        _lib.call("b200_decode_attn_fused", ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.stride(0),
-                  ptr(kv_lens), B, Hq, Hkv, D, page, c_float(scale), c_float(soft_cap), num_splits, ptr(o_part),
-                  ptr(lse_part), ptr(tickets), ptr(out), ptr(lse), dtype_code(q.dtype), stream_ptr())
-        _count()
-        return (out, lse) if return_lse else out
-    _lib.call("b200_decode_attn_split", ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.stride(0),
+    _lib.call("b200_decode_attn", ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.stride(0),
               ptr(kv_lens), B, Hq, Hkv, D, page, c_float(scale), c_float(soft_cap), num_splits, ptr(o_part),
-              ptr(lse_part), ptr(out), ptr(lse), dtype_code(q.dtype), stream_ptr())
+              ptr(lse_part), ptr(tickets), ptr(out), ptr(lse), dtype_code(q.dtype), ring, stream_ptr())
     _count()
-    if num_splits > 1:
+    if num_splits > 1 and tickets is None:
         _lib.call("b200_decode_combine", ptr(o_part), ptr(lse_part), ctypes.c_longlong(num_splits * D),
                   ctypes.c_longlong(D), ctypes.c_longlong(num_splits), ctypes.c_longlong(1), B * Hq, num_splits,
                   ptr(out), None, ptr(lse), dtype_code(q.dtype), stream_ptr())
@@ -254,12 +262,41 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     return (out, lse) if return_lse else out
 
 
+_pipe_status: dict = {}
+
+
+def _pipeline_status(device: torch.device) -> torch.Tensor:
+    """One int32 word per device that single-GPU pipeline kernels raise when an internal wait expires."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    st = _pipe_status.get(key)
+    if st is None:
+        st = _pipe_status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return st
+
+
+def check_pipeline_status(device=None) -> None:
+    """Synchronise and raise if a pipeline kernel of this device gave up on an internal wait since the last check."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    st = _pipe_status.get(key)
+    if st is None:
+        return
+    code = int(st.item())
+    if code != 0:
+        st.zero_()
+        raise RuntimeError(f"a pipeline kernel on {dev} gave up on an internal wait (status {code}); its output is incomplete")
+
+
 def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: torch.Tensor,
                       cu_seqlens_k: torch.Tensor, max_seqlen_q: int, max_seqlen_k: int, scale: float,
-                      causal: bool = True, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Variable-length (packed) attention on the tcgen05 prefill kernel. q [total_q, Hq, 128]; k, v [total_k, Hkv, 128];
+                      causal: bool = True, out: torch.Tensor | None = None,
+                      seqlens_k: torch.Tensor | None = None) -> torch.Tensor:
+    """Variable-length attention on the tcgen05 prefill kernel. q [total_q, Hq, 128]; k, v [total_k, Hkv, 128];
     cu_seqlens_* int32 [B + 1] on the device. With ``causal`` query i of a sequence attends keys <= i + (k_len - q_len).
-    Returns [total_q, Hq, 128]."""
+
+    Packed sequences: leave ``seqlens_k`` None (lengths are differences of ``cu_seqlens_k``). Keys in place: give
+    ``seqlens_k`` int32 [B]; sequence b then reads rows ``cu_seqlens_k[b] ... + seqlens_k[b]`` of k / v, which may be the
+    slot view of a paged KV cache whose sequences own contiguous runs of slots. Returns [total_q, Hq, 128]."""
     _lib.require_cuda()
     total_q, Hq, D = q.shape
     total_k, Hkv, _ = k.shape
@@ -270,16 +307,16 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seql
     B = cu_seqlens_q.numel() - 1
     cu_q = cu_seqlens_q.to(device=q.device, dtype=torch.int32).contiguous()
     cu_k = cu_seqlens_k.to(device=q.device, dtype=torch.int32).contiguous()
+    k_lens = seqlens_k.to(device=q.device, dtype=torch.int32).contiguous() if seqlens_k is not None else None
     lib = _lib.load()
     lib.b200_prefill_attention_scratch_bytes.restype = ctypes.c_longlong
     nbytes = int(lib.b200_prefill_attention_scratch_bytes(B, Hkv, int(max_seqlen_k)))
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
     if out is None:
         out = torch.empty_like(q)
-    status = torch.zeros(1, dtype=torch.int32, device=q.device)
-    _lib.call("b200_prefill_attention", ptr(q), ptr(k), ptr(v), ptr(cu_q), ptr(cu_k), B, total_q, total_k, int(max_seqlen_q),
-              int(max_seqlen_k), Hq, Hkv, D, c_float(scale), 1 if causal else 0, ptr(scratch), ptr(out), dtype_code(q.dtype),
-              ptr(status), stream_ptr())
+    _lib.call("b200_prefill_attention", ptr(q), ptr(k), ptr(v), ptr(cu_q), ptr(cu_k), ptr(k_lens), B, total_q, total_k,
+              int(max_seqlen_q), int(max_seqlen_k), Hq, Hkv, D, c_float(scale), 1 if causal else 0, ptr(scratch), ptr(out),
+              dtype_code(q.dtype), ptr(_pipeline_status(q.device)), stream_ptr())
     _count(2)
     return out
 

@@ -292,6 +292,12 @@ class SymmHeap:
                 f"{what or 'kernel'}: {_STATUS_NAMES.get(st[0], f'status {st[0]}')} on rank {self.rank} "
                 f"(who={st[1]}, expected={st[2]}, seen={st[3]}, line={st[4]})")
 
+    def sync_and_check(self, what: str = "") -> None:
+        """Wait for this device's work, then raise if one of its kernels gave up on a wait. Contexts call this when
+        they are finalised, so an expired wait cannot pass unnoticed even if the caller never looks at the status."""
+        torch.cuda.synchronize()
+        self.check_status(what)
+
     # ------------------------------------------------------------------ teardown
     def _destroy_handle(self) -> None:
         if self._h:
