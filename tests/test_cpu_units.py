@@ -225,7 +225,7 @@ def test_ag_gemm_gather_choice_follows_world_size_and_bytes():
     def ctx(world, K=8192):
         return Ctx(rank=0, num_ranks=world, num_local_ranks=world, max_M=8192, N_per_rank=1024, K=K, dtype=torch.bfloat16,
                    heap=None, symm_workspaces=[], symm_ready=None, blk_cnt=None, blk_flag=None, sync=None)
-    assert ctx(2).method_for(64) == "sm_pull_fused"
+    assert ctx(2).method_for(64) == "sm_push_fused"      # one peer: pushed rows arrive as one stream
     assert ctx(8).method_for(128) == "sm_push_fused"      # M = 1024: 14.7 MB out
     assert ctx(8).method_for(512) == "sm_push_fused"      # M = 4096: 58.7 MB out
     assert ctx(8).method_for(1024) == "sm_pull_fused"     # M = 8192: 117 MB out

@@ -208,3 +208,95 @@ def test_top_p_sampling_matches_sorted_reference():
     tiny[0, 9] = 5.0
     tiny[1, 0] = 5.0
     assert ops.top_p_sample(tiny, 0.7, 0.5).flatten().tolist() == [9, 0]
+
+
+@pytest.mark.parametrize("M,K,Hq,Hkv,with_norm,with_scale", [(8, 5120, 8, 1, True, True), (3, 512, 2, 2, False, False),
+                                                             (16, 1024, 64, 8, True, False)])
+def test_gemm_skinny_qkv_heads_epilogue(M, K, Hq, Hkv, with_norm, with_scale):
+    """The qkv projection that finishes every head in its epilogue (per-head RMSNorm, RoPE, q buffer, cache write),
+    optionally with the input's RMSNorm folded in as a per-row scale, against the fp32 statement of the same chain."""
+    from triton_distributed_b200 import ops
+    torch.manual_seed(11)
+    D, eps = 128, 1e-6
+    N = (Hq + 2 * Hkv) * D
+    h = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * K ** -0.5
+    pos = torch.randint(0, 4000, (M,), device="cuda", dtype=torch.int32)
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2, device="cuda", dtype=torch.float32) / D))
+    ang = torch.arange(4096, device="cuda", dtype=torch.float32)[:, None] * inv[None, :]
+    cos_sin = torch.cat([ang.cos(), ang.sin()], -1).contiguous()
+    qg = torch.randn(D, device="cuda", dtype=torch.bfloat16) if with_norm else None
+    kg = torch.randn(D, device="cuda", dtype=torch.bfloat16) if with_norm else None
+    slots = torch.randperm(64, device="cuda")[:M].to(torch.int64)
+    kc = torch.zeros(64, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    q = torch.zeros(M, Hq, D, device="cuda", dtype=torch.bfloat16)
+    ep = ops.skinny_qkv_heads(pos, slots, cos_sin, Hq, Hkv, q, kc, vc, qg, kg, eps)
+    x_in = h
+    scale = torch.ones(M, 1, device="cuda")
+    if with_scale:  # input = h * gain, rows scaled by 1 / rms(h) in the epilogue
+        gain = torch.randn(K, device="cuda", dtype=torch.bfloat16)
+        x_in = (h.float() * gain.float()).to(torch.bfloat16)
+        sumsq = torch.zeros(16, device="cuda")
+        sumsq[:M] = h.float().pow(2).sum(-1)
+        ops.skinny_row_scale(sumsq, K, eps, base=ep)
+        scale = torch.rsqrt(sumsq[:M] / K + eps)[:, None]
+    for _ in range(2):
+        ops.gemm_skinny(x_in, w, epilogue=ep)
+    y = (x_in.float() @ w.float().t() * scale).view(M, Hq + 2 * Hkv, D)
+
+    def norm(v, g):
+        return v if g is None else v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * g.float()
+
+    q_ref = _rope_ref(norm(y[:, :Hq], qg), pos)
+    k_ref = _rope_ref(norm(y[:, Hq:Hq + Hkv], kg), pos)
+    torch.testing.assert_close(q.float(), q_ref, rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(kc[slots].float(), k_ref, rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(vc[slots].float(), y[:, Hq + Hkv:], rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 5120, 1024), (5, 384, 4096), (16, 1000, 520)])
+def test_gemm_skinny_residual_and_row_scale_epilogues(M, N, K):
+    """Producer side: h = x W^T + residual, h * gain and sum(h^2). Consumer side: (h * gain) W2^T scaled by 1 / rms(h),
+    plain and with SwiGLU, i.e. an RMSNorm between two projections without a normalisation kernel."""
+    from triton_distributed_b200 import ops
+    torch.manual_seed(12)
+    eps = 1e-6
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * K ** -0.5
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    res0 = res.clone()
+    gain = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    xg = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    sumsq = torch.zeros(16, device="cuda")
+    ops.gemm_skinny(x, w, epilogue=ops.skinny_residual(res, sumsq, gain, xg))
+    h = (x.float() @ w.float().t() + res0.float())
+    torch.testing.assert_close(res.float(), h, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(xg.float(), res.float() * gain.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(sumsq[:M], res.float().pow(2).sum(-1), rtol=1e-3, atol=1e-2)
+    assert float(sumsq[M:].abs().sum()) == 0.0
+    if N % 8 == 0:
+        I = 256
+        w2 = torch.randn(2 * I, N, device="cuda", dtype=torch.bfloat16) * N ** -0.5
+        normed = (res.float() * torch.rsqrt(res.float().pow(2).mean(-1, keepdim=True) + eps) * gain.float())
+        y = ops.gemm_skinny(xg, w2, epilogue=ops.skinny_row_scale(sumsq, N, eps))
+        torch.testing.assert_close(y.float(), normed @ w2.float().t(), rtol=3e-2, atol=3e-2)
+        act = ops.gemm_skinny(xg, w2, swiglu=True, epilogue=ops.skinny_row_scale(sumsq, N, eps))
+        gu = normed @ w2.float().t()
+        torch.testing.assert_close(act.float(), torch.nn.functional.silu(gu[:, :I]) * gu[:, I:], rtol=3e-2, atol=3e-2)
+
+
+def test_embedding_with_norm_outputs():
+    from triton_distributed_b200 import ops
+    torch.manual_seed(13)
+    V, H = 1000, 640
+    table = torch.randn(V, H, device="cuda", dtype=torch.bfloat16)
+    ids = torch.tensor([[3, 999], [0, 17]], device="cuda")
+    gain = torch.randn(H, device="cuda", dtype=torch.bfloat16)
+    assert torch.equal(ops.embedding(ids, table), table[ids])
+    xg = torch.empty(4, H, device="cuda", dtype=torch.bfloat16)
+    ss = torch.zeros(16, device="cuda")
+    out = ops.embedding(ids.reshape(-1), table, gamma=gain, scaled_out=xg, sumsq_out=ss)
+    assert torch.equal(out, table[ids.reshape(-1)])
+    torch.testing.assert_close(xg.float(), out.float() * gain.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(ss[:4], out.float().pow(2).sum(-1), rtol=1e-4, atol=1e-3)

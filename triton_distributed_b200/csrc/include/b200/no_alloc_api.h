@@ -14,7 +14,8 @@
 //     ceil(N / 128) <= 4096 tiles. Larger problems are rejected with an error; nothing is launched.
 //     Every GPU that loads the library holds these 4 MiB + 16 KiB until the process exits.
 //   * the first call on each device resolves the device address of the arrays (cudaGetSymbolAddress, with
-//     that device current). Make that first call outside of any stream capture.
+//     that device current) under a lock, so host threads may race to make it. Make that first call outside of
+//     any stream capture.
 //   * no call allocates or frees: no cudaMalloc / cudaFree, no allocating library routine.
 //   * all calls on a device share the one area. The kernel leaves it zeroed when it finishes, which is what
 //     the next call relies on, so two calls that overlap on the GPU (different streams without an ordering

@@ -11,7 +11,9 @@
 // One CTA of 1024 threads owns a row: it sends the row, gathers the `world` contributions of every word (all loads
 // of a word issued together, summed in rank order in fp32), adds the residual, rounds to the storage type, and
 // normalises. Arithmetic and rounding are those of the fused path in allreduce.cu (finish_row), so both give the
-// same numbers. Opt-in (B200DIST_AR_LL=1 selects it for fused calls of at most 512 KB).
+// same numbers. It serves fused calls of at most 512 KB (B200DIST_AR_LL=0 sends them to allreduce.cu instead). With an
+// NVLS multicast mapping one multimem.st per packet reaches every rank through the switch, so a rank injects its row
+// once instead of world - 1 times.
 //
 // Role in the reference: the GEMM + AllReduce decode path (layers/nvidia/tp_mlp.py:177-191, tp_attn.py:240-271), whose
 // all-reduce is kernels/nvidia/allreduce.py:364-414 followed by a separate flashinfer RMSNorm.
@@ -29,7 +31,7 @@ struct ArLLParams {
   const uint32_t* in;          // [rows, hidden / 2] words of this rank's partial result
   uint64_t* ws[2];             // symmetric, per parity: [world][rows][hidden / 2] packets
   uint32_t* sync;              // local u32[4]: epoch, done counter
-  int rows, hidden, bf16;
+  int rows, hidden, bf16, use_mc;
   const uint32_t* residual_in; // [rows, hidden / 2] or null
   uint32_t* residual_out;      // [rows, hidden / 2] or null
   const uint32_t* gamma;       // [hidden / 2]
@@ -63,10 +65,15 @@ __global__ void __launch_bounds__(kLLThreads) allreduce_ll_kernel(const ArLLPara
         const uint32_t d = p.in[static_cast<size_t>(row) * row_words + i];
         mine[u] = d;
         uint64_t* slot = ws + (static_cast<size_t>(me) * p.rows + row) * row_words + i;
-        for (int k = 1; k < world; ++k) {
-          int peer = me + k;
-          if (peer >= world) peer -= world;
-          ll_store(symm_at(ctx, slot, peer), d, epoch);
+        if (p.use_mc) {
+          const uint64_t v = (static_cast<uint64_t>(epoch) << 32) | d;
+          asm volatile("multimem.st.relaxed.sys.global.u64 [%0], %1;" ::"l"(mc_ptr(ctx, slot)), "l"(v) : "memory");
+        } else {
+          for (int k = 1; k < world; ++k) {
+            int peer = me + k;
+            if (peer >= world) peer -= world;
+            ll_store(symm_at(ctx, slot, peer), d, epoch);
+          }
         }
       }
     }
@@ -161,10 +168,10 @@ B200_API long long b200_allreduce_ll_ws_bytes(int world, int rows, int hidden) {
 // in / residual / normed_out: [rows, hidden] of bf16 (dtype 0) or f16 (1), 4-byte aligned rows (hidden even).
 // ws0 / ws1: symmetric parity buffers of b200_allreduce_ll_ws_bytes each, zero-initialised once; sync: local u32[4],
 // zero-initialised once and used by LL calls only (its epoch is the packet flag). residual_in / residual_out may be
-// null and may alias each other.
+// null and may alias each other. use_multimem != 0 broadcasts packets with multimem.st (needs the NVLS mapping).
 B200_API int b200_allreduce_ll(const void* symm_ctx, const void* in, int rows, int hidden, int dtype, void* ws0, void* ws1,
                                uint32_t* sync, const void* residual_in, void* residual_out, const void* gamma,
-                               void* normed_out, float eps, void* stream) {
+                               void* normed_out, float eps, int use_multimem, void* stream) {
   SymmCtx ctx;
   memcpy(&ctx, symm_ctx, sizeof(ctx));
   B200_REQUIRE(dtype == kBF16 || dtype == kF16, "the LL all-reduce handles bf16 and f16");
@@ -172,13 +179,14 @@ B200_API int b200_allreduce_ll(const void* symm_ctx, const void* in, int rows, i
   B200_REQUIRE(hidden / 2 <= kLLThreads * kLLWordsPerThread, "hidden (%d) exceeds %d", hidden, 2 * kLLThreads * kLLWordsPerThread);
   B200_REQUIRE(ctx.world >= 1 && ctx.world <= kMaxRanks, "world (%d) out of range", ctx.world);
   B200_REQUIRE(in && ws0 && ws1 && sync && gamma && normed_out, "missing buffers");
+  B200_REQUIRE(!use_multimem || ctx.mc_base != 0, "multimem packets need an NVLS multicast mapping");
   ArLLParams p;
   memset(&p, 0, sizeof(p));
   p.in = static_cast<const uint32_t*>(in);
   p.ws[0] = static_cast<uint64_t*>(ws0);
   p.ws[1] = static_cast<uint64_t*>(ws1);
   p.sync = sync;
-  p.rows = rows; p.hidden = hidden; p.bf16 = dtype == kBF16;
+  p.rows = rows; p.hidden = hidden; p.bf16 = dtype == kBF16; p.use_mc = use_multimem && ctx.world > 1;
   p.residual_in = static_cast<const uint32_t*>(residual_in);
   p.residual_out = static_cast<uint32_t*>(residual_out);
   p.gamma = static_cast<const uint32_t*>(gamma);

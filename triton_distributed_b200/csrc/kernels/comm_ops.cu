@@ -4,7 +4,7 @@
 // All-gather (python/triton_dist/kernels/nvidia/low_latency_allgather.py:47-777, 964-994): the
 // buffer is symmetric, [world][bytes_per_rank], and slot `rank` is pre-filled by the caller.
 //   PULL          barrier, copy every peer's slot out of the peer's buffer, barrier
-//   PUSH          write the local slot into every peer's buffer, barrier
+//   PUSH          barrier, write the local slot into every peer's buffer, barrier
 //   PUSH_LL       8-byte {data, flag} packets into a double-buffered packet area; the receiver polls the
 //                 payload itself, so there is no barrier at all (latency = one NVLink store + one poll)
 //   PUSH_LL_MC    as PUSH_LL but one multimem.st per packet reaches all ranks through the switch
@@ -60,13 +60,17 @@ __global__ void __launch_bounds__(kAgThreads) allgather_kernel(const AgParams p,
       ag_cta_barrier(ctx, p.flags, 1, epoch);
     }
   } else if (p.mode == kAgPush) {
+    // entry barrier: a peer enters this call only after whatever consumed its buffer since the previous call has
+    // finished (stream order), so only then may its slots be overwritten
     const uint64_t nvec = p.bytes / 16;
     uint4* mine = reinterpret_cast<uint4*>(p.buf + me * p.bytes);
-    for (uint64_t i = tid; i < nvec; i += nthreads) {
-      const uint4 v = mine[i];
-      for (int k = 1; k < world; ++k) st_v4(symm_at(ctx, mine + i, (me + k) % world), v);
+    if (ag_cta_barrier(ctx, p.flags, 0, epoch)) {
+      for (uint64_t i = tid; i < nvec; i += nthreads) {
+        const uint4 v = mine[i];
+        for (int k = 1; k < world; ++k) st_v4(symm_at(ctx, mine + i, (me + k) % world), v);
+      }
+      ag_cta_barrier(ctx, p.flags, 1, epoch);
     }
-    ag_cta_barrier(ctx, p.flags, 0, epoch);
   } else {
     // LL: word i of rank s travels as packet ll[s][i] = {word, epoch}
     const uint64_t nwords = p.bytes / 4;

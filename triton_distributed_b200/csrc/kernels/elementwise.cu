@@ -4,6 +4,7 @@
 //                    write of k / v into the paged KV cache, all in one kernel over the fused qkv projection
 //   silu_mul         SwiGLU gate: silu(gate) * up over a fused [gate | up] projection
 //   topk_softmax     router: softmax over experts + top-k (ids, weights)
+//   embedding        out[t] = table[ids[t]] (token embedding lookup, 16-byte vectors)
 //
 // Role in the reference: flashinfer.norm.rmsnorm, flashinfer.apply_rope_with_cos_sin_cache_inplace and
 // the unfused torch act_fn(gate) * up (python/triton_dist/layers/nvidia/tp_attn.py:60-75,159-195,
@@ -237,6 +238,73 @@ __global__ void topk_softmax_kernel(const void* logits, int dtype, int T, int E,
 }  // namespace b200
 
 using namespace b200;
+
+// ids int64 [T]; table [V, H]; out [T, H]. Ids outside [0, V) read as zero rows. Optionally also emits, for the
+// RMSNorm that follows, the row's sum of squares (sumsq_out fp32 [T], stored) and the row times the norm's gain
+// (scaled_out [T, H] with gamma [H]), so that the consumer GEMM can apply 1 / rms in its epilogue.
+// (torch's F.embedding in python/triton_dist/models/qwen.py:213.)
+namespace b200 {
+template <bool BF16>
+__global__ void __launch_bounds__(256) embedding_kernel(const long long* __restrict__ ids, const uint4* __restrict__ table,
+                                                        uint4* __restrict__ out, int T, long long V, int row_vec,
+                                                        const uint4* __restrict__ gamma, uint4* __restrict__ scaled_out,
+                                                        float* __restrict__ sumsq_out) {
+  __shared__ float red[8];
+  griddep_launch_dependents();
+  griddep_wait();
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    const long long id = ids[t];
+    const bool ok = id >= 0 && id < V;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < row_vec; i += blockDim.x) {
+      const uint4 v = ok ? ld_v4_nc(table + id * row_vec + i) : make_uint4(0, 0, 0, 0);
+      out[static_cast<size_t>(t) * row_vec + i] = v;
+      if (sumsq_out != nullptr || scaled_out != nullptr) {
+        float f[8];
+        unpack8<BF16>(v, f);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) ss += f[q] * f[q];
+        if (scaled_out != nullptr) {
+          float g[8];
+          unpack8<BF16>(gamma[i], g);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) f[q] *= g[q];
+          scaled_out[static_cast<size_t>(t) * row_vec + i] = pack8<BF16>(f);
+        }
+      }
+    }
+    if (sumsq_out != nullptr) {
+      ss = warp_sum(ss);
+      __syncthreads();
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float tot = 0.f;
+        for (int w = 0; w < 8; ++w) tot += red[w];
+        sumsq_out[t] = tot;
+      }
+    }
+  }
+}
+}  // namespace b200
+B200_API int b200_embedding(const long long* ids, const void* table, void* out, int T, long long V, int H, int dtype,
+                            const void* gamma, void* scaled_out, float* sumsq_out, void* stream) {
+  B200_REQUIRE(dtype == b200::kBF16 || dtype == b200::kF16, "embedding handles bf16 / f16 tables");
+  B200_REQUIRE(H > 0 && H % 8 == 0, "embedding width (%d) must be a multiple of 8", H);
+  B200_REQUIRE(scaled_out == nullptr || gamma != nullptr, "scaled_out needs gamma");
+  if (T <= 0) return b200::kOk;
+  const int grid = T < 4 * b200::sm_count() ? T : 4 * b200::sm_count();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == b200::kBF16)
+    B200_CHECK_CUDA(b200::launch_pdl(b200::embedding_kernel<true>, dim3(grid), dim3(256), 0, s, ids, static_cast<const uint4*>(table),
+                                     static_cast<uint4*>(out), T, V, H / 8, static_cast<const uint4*>(gamma),
+                                     static_cast<uint4*>(scaled_out), sumsq_out));
+  else
+    B200_CHECK_CUDA(b200::launch_pdl(b200::embedding_kernel<false>, dim3(grid), dim3(256), 0, s, ids, static_cast<const uint4*>(table),
+                                     static_cast<uint4*>(out), T, V, H / 8, static_cast<const uint4*>(gamma),
+                                     static_cast<uint4*>(scaled_out), sumsq_out));
+  return b200::kOk;
+}
 
 B200_API int b200_rmsnorm(const void* x, const void* residual_in, void* residual_out, const void* gamma, void* y,
                           int rows, int hidden, float eps, int dtype, void* stream) {

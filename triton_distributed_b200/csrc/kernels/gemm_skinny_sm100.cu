@@ -15,6 +15,14 @@
 // The tokens are the TMEM columns, so an epilogue thread owns one output feature for all tokens and a
 // warp writes 32 consecutive features of one token: coalesced without a shared-memory transpose.
 //
+// Fused epilogues (at most 16 tokens, i.e. one accumulator chunk per epilogue thread), applied by whichever CTA holds
+// the finished tile:
+//   row scale     out[m, :] *= rsqrt(sumsq[m] / dim + eps): the RMSNorm of the GEMM's input, whose gain the producer
+//                 of the input already multiplied in, so no normalisation kernel runs between two GEMMs
+//   qkv heads     a 128-feature tile is one attention head: per-head RMSNorm, neox RoPE, and the write of q to its
+//                 buffer and of k / v into the paged KV cache (replaces a separate norm + rope + cache-write kernel)
+//   residual      h = out + residual; writes h, h * gain_of_the_next_norm and adds sum(h^2) per token to a buffer
+//
 // Role in the reference: the cuBLAS F.linear calls of the AllReduce forward mode
 // (python/triton_dist/layers/nvidia/tp_mlp.py:177-191, tp_attn.py:240-271) and the unfused
 // act_fn(gate) * up (tp_mlp.py:159-160).
@@ -31,7 +39,33 @@ constexpr int kSkBN = 128;  // weight rows per tile
 constexpr int kSkBK = 64;
 constexpr int kSkWBytes = kSkBN * kSkBK * 2;
 constexpr int kSkMaxStages = 12;
-constexpr int kSkSmemBudget = 225 * 1024;
+constexpr int kSkSmemBudget = 216 * 1024;  // ring; the kernel's static shared memory (8.7 KB) comes on top
+
+enum SkinnyEpilogueKind : int { kEpNone = 0, kEpQkvHeads = 1, kEpResidual = 2 };
+
+struct SkinnyEpilogue {
+  int kind;
+  // row scale (any kind, nullable): per-token sum of squares of the un-normalised input
+  const float* sumsq_in;
+  float scale_dim, eps;
+  // kEpQkvHeads: tile t is head t of [q heads | k heads | v heads]
+  int Hq, Hkv;
+  const int* positions;      // [M]
+  const long long* slots;    // [M] cache slot of every token, null = identity
+  const float* cos_sin;      // [max_pos, 128] = cos | sin
+  const void* q_gamma;       // [128] or null (no per-head norm)
+  const void* k_gamma;
+  void* q_out;               // [M, Hq, 128]
+  void* k_cache;             // [slots, Hkv, 128]
+  void* v_cache;
+  float head_eps;
+  // kEpResidual
+  const void* residual_in;   // [M, N] (row pitch ldc), may alias residual_out
+  void* residual_out;        // [M, N] (row pitch ldc)
+  const void* next_gamma;    // [N] gain of the norm that follows, or null
+  void* scaled_out;          // [M, N] (row pitch ldc) = h * next_gamma (with next_gamma)
+  float* sumsq_out;          // [M], accumulated with atomics (zero it before the first producer of a step)
+};
 
 struct SkinnyParams {
   int M, N, K;        // N = weight rows per projection (the output features)
@@ -47,6 +81,7 @@ struct SkinnyParams {
   int ldc;
   float* scratch;     // [tiles][dual ? 2 : 1][MB][128] fp32, zero on entry and on exit
   uint32_t* tickets;  // [tiles], zero on entry and on exit
+  SkinnyEpilogue ep;
 };
 
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
@@ -66,6 +101,108 @@ __device__ __forceinline__ bool next_segment(const SkinnyParams& p, int& u, int 
   return true;
 }
 
+__device__ __forceinline__ float ld_elem(const void* p, size_t i, bool bf16) {
+  return bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]) : __half2float(static_cast<const __half*>(p)[i]);
+}
+__device__ __forceinline__ float round_elem(float v, bool bf16) {
+  return bf16 ? __bfloat162float(__float2bfloat16(v)) : __half2float(__float2half(v));
+}
+__device__ __forceinline__ void st_elem(void* p, size_t i, float v, bool bf16) {
+  if (bf16) static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16(v);
+  else static_cast<__half*>(p)[i] = __float2half(v);
+}
+
+// Finishes one 128-feature tile for up to 16 tokens. Executed by the 128 epilogue threads together (thread et owns
+// feature et of the tile for every token); g / uu hold the complete sums. `xch` is [16][128] floats and `red` [4][16]
+// floats of shared memory.
+template <bool kDual>
+__device__ __forceinline__ void finish_tile16(const SkinnyParams& p, int tile, int et, float (&g)[16], float (&uu)[16],
+                                              float* xch, float* red) {
+  const SkinnyEpilogue& ep = p.ep;
+  const bool bf16 = p.bf16 != 0;
+  const int n = tile * kSkBN + et;
+  const int w = et >> 5, lane = et & 31;
+  if (ep.sumsq_in != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float sc = j < p.M ? rsqrtf(__ldcg(ep.sumsq_in + j) / ep.scale_dim + ep.eps) : 0.f;
+      g[j] *= sc;
+      if (kDual) uu[j] *= sc;
+    }
+  }
+  if (ep.kind == kEpQkvHeads) {
+    const int head = tile;
+    const bool is_q = head < ep.Hq, is_k = !is_q && head < ep.Hq + ep.Hkv;
+    const void* gamma = is_q ? ep.q_gamma : is_k ? ep.k_gamma : nullptr;
+    if (gamma != nullptr) {  // per-head RMSNorm over the 128 features of the tile
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float t = warp_sum(g[j] * g[j]);
+        if (lane == 0) red[w * 16 + j] = t;
+      }
+      epi_bar();
+      const float gm = ld_elem(gamma, et, bf16);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float tot = red[j] + red[16 + j] + red[32 + j] + red[48 + j];
+        g[j] *= rsqrtf(tot / 128.f + ep.head_eps) * gm;
+      }
+    }
+    if (is_q || is_k) {  // neox rotary embedding: feature i pairs with feature i +- 64
+#pragma unroll
+      for (int j = 0; j < 16; ++j) xch[j * kSkBN + et] = g[j];
+      epi_bar();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (j < p.M) {
+          const float other = xch[j * kSkBN + (et ^ 64)];
+          const float* cs = ep.cos_sin + static_cast<size_t>(ep.positions[j]) * 128;
+          const float c = cs[et & 63], sn = cs[64 + (et & 63)];
+          g[j] = et < 64 ? g[j] * c - other * sn : g[j] * c + other * sn;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (j < p.M) {
+        if (is_q) {
+          st_elem(ep.q_out, (static_cast<size_t>(j) * ep.Hq + head) * 128 + et, g[j], bf16);
+        } else {
+          const size_t slot = ep.slots ? static_cast<size_t>(ep.slots[j]) : static_cast<size_t>(j);
+          const int kvh = is_k ? head - ep.Hq : head - ep.Hq - ep.Hkv;
+          st_elem(is_k ? ep.k_cache : ep.v_cache, (slot * ep.Hkv + kvh) * 128 + et, g[j], bf16);
+        }
+      }
+    }
+    epi_bar();  // red / xch are reused by the next tile
+    return;
+  }
+  if (ep.kind == kEpResidual) {
+    const float gm = (ep.next_gamma != nullptr && n < p.N) ? ld_elem(ep.next_gamma, n, bf16) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      float sq = 0.f;
+      if (j < p.M && n < p.N) {
+        const size_t o = static_cast<size_t>(j) * p.ldc + n;
+        const float h = round_elem(g[j] + ld_elem(ep.residual_in, o, bf16), bf16);  // the stream is kept in storage type
+        st_elem(ep.residual_out, o, h, bf16);
+        if (ep.scaled_out != nullptr) st_elem(ep.scaled_out, o, h * gm, bf16);
+        sq = h * h;
+      }
+      sq = warp_sum(sq);
+      if (lane == 0 && j < p.M && ep.sumsq_out != nullptr) atomicAdd(ep.sumsq_out + j, sq);
+    }
+    return;
+  }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    if (j < p.M && n < p.N) {
+      const float v = kDual ? g[j] / (1.f + __expf(-g[j])) * uu[j] : g[j];
+      st_elem(p.C, static_cast<size_t>(j) * p.ldc + n, v, bf16);
+    }
+  }
+}
+
 template <bool kDual>
 __global__ void __launch_bounds__(256, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const SkinnyParams p) {
@@ -78,7 +215,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __shared__ uint32_t tmem_slot;
   __shared__ uint32_t abort_word;
   __shared__ uint32_t last_flag;
+  __shared__ float ep_xch[16 * kSkBN];  // fused epilogues: partner exchange of the rotary embedding
+  __shared__ float ep_red[4 * 16];      //                  per-warp partial sums of the per-head norm
   volatile uint32_t* abort_flag = &abort_word;
+  const bool fused_ep = p.ep.kind != kEpNone || p.ep.sumsq_in != nullptr;  // host guarantees MB == 16 then
 
   const int warp = threadIdx.x >> 5;
   constexpr int kW = kDual ? 2 : 1;
@@ -207,7 +347,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         tmem_ld_32x16(taddr + c0, g);
         if (kDual) tmem_ld_32x16(taddr + p.MB + c0, uu);
         tmem_ld_wait();
-        if (contributors == 1) {
+        if (contributors == 1 && fused_ep) {
+          float gf[16], uf[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            gf[j] = __uint_as_float(g[j]);
+            uf[j] = kDual ? __uint_as_float(uu[j]) : 0.f;
+          }
+          finish_tile16<kDual>(p, sg.tile, et, gf, uf, ep_xch, ep_red);
+        } else if (contributors == 1) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) store_out(c0 + j, __uint_as_float(g[j]), kDual ? __uint_as_float(uu[j]) : 0.f);
         } else {
@@ -233,7 +381,26 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           last_flag = (t == static_cast<uint32_t>(contributors - 1)) ? 1u : 0u;
         }
         epi_bar();
-        if (last_flag) {
+        if (last_flag && fused_ep) {
+          __threadfence();
+          float gf[16], uf[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            gf[j] = uf[j] = 0.f;
+            if (j < p.M) {
+              float* gs = scratch + static_cast<size_t>(j) * kSkBN + et;
+              gf[j] = __ldcg(gs);
+              __stcg(gs, 0.f);
+              if (kDual) {
+                float* us = scratch + static_cast<size_t>(p.MB + j) * kSkBN + et;
+                uf[j] = __ldcg(us);
+                __stcg(us, 0.f);
+              }
+            }
+          }
+          finish_tile16<kDual>(p, sg.tile, et, gf, uf, ep_xch, ep_red);
+          if (et == 0) p.tickets[sg.tile] = 0;
+        } else if (last_flag) {
           __threadfence();
           for (int m = 0; m < p.M; ++m) {
             float* gs = scratch + static_cast<size_t>(m) * kSkBN + et;
@@ -302,8 +469,8 @@ B200_API long long b200_gemm_skinny_scratch_floats(int M, int N, int dual) {
 // dual == 0: N = Nw. dual == 1: W = [gate (N rows); up (N rows)], C = silu(X gate^T) * (X up^T).
 // scratch / tickets: zero-initialised once by the caller; every call leaves them zeroed.
 // splits <= 0: one CTA per SM (stream-K); splits > 0 forces tiles * splits CTAs.
-B200_API int b200_gemm_skinny(const void* X, const void* W, void* C, int M, int N, int K, int ldx, int ldw, int ldc,
-                              int dual, int dtype, float* scratch, uint32_t* tickets, int splits, void* stream) {
+static int skinny_impl(const void* X, const void* W, void* C, int M, int N, int K, int ldx, int ldw, int ldc, int dual,
+                       int dtype, float* scratch, uint32_t* tickets, int splits, const SkinnyEpilogue* ep, void* stream) {
   B200_REQUIRE(dtype == kBF16 || dtype == kF16, "gemm_skinny supports bf16/f16");
   B200_REQUIRE(M >= 1 && M <= 256, "gemm_skinny handles 1..256 tokens, got %d", M);
   B200_REQUIRE(K % 8 == 0, "K (%d) must be a multiple of 8", K);
@@ -321,6 +488,21 @@ B200_API int b200_gemm_skinny(const void* X, const void* W, void* C, int M, int 
   p.up_row0 = N;
   p.bf16 = dtype == kBF16;
   p.C = C; p.ldc = ldc; p.scratch = scratch; p.tickets = tickets;
+  if (ep != nullptr) {
+    p.ep = *ep;
+    const bool fused = ep->kind != kEpNone || ep->sumsq_in != nullptr;
+    B200_REQUIRE(!fused || M <= 16, "the fused epilogues handle at most 16 tokens, got %d", M);
+    if (ep->kind == kEpQkvHeads) {
+      B200_REQUIRE(!dual && N == (ep->Hq + 2 * ep->Hkv) * kSkBN, "qkv epilogue: N (%d) must be (Hq + 2 Hkv) * 128", N);
+      B200_REQUIRE(ep->positions && ep->cos_sin && ep->q_out && ep->k_cache && ep->v_cache, "qkv epilogue: missing buffers");
+    } else if (ep->kind == kEpResidual) {
+      B200_REQUIRE(!dual && ep->residual_in && ep->residual_out, "residual epilogue: missing buffers");
+      B200_REQUIRE(ep->scaled_out == nullptr || ep->next_gamma != nullptr, "residual epilogue: scaled_out needs next_gamma");
+    } else {
+      B200_REQUIRE(ep->kind == kEpNone, "unknown epilogue kind %d", ep->kind);
+      B200_REQUIRE(C != nullptr, "gemm_skinny needs an output");
+    }
+  }
   const int tiles = (N + kSkBN - 1) / kSkBN;
   p.num_kb = (K + kSkBK - 1) / kSkBK;
   p.units_total = tiles * p.num_kb;
@@ -341,10 +523,28 @@ B200_API int b200_gemm_skinny(const void* X, const void* W, void* C, int M, int 
   return dual ? launch_skinny<true>(tw, tx, p, grid, smem, s) : launch_skinny<false>(tw, tx, p, grid, smem, s);
 }
 
+B200_API int b200_gemm_skinny(const void* X, const void* W, void* C, int M, int N, int K, int ldx, int ldw, int ldc,
+                              int dual, int dtype, float* scratch, uint32_t* tickets, int splits, void* stream) {
+  return skinny_impl(X, W, C, M, N, K, ldx, ldw, ldc, dual, dtype, scratch, tickets, splits, nullptr, stream);
+}
+
+// As b200_gemm_skinny with a fused epilogue (M <= 16). `epilogue` points to a SkinnyEpilogue (see the top of this file;
+// the Python binding mirrors its layout). C may be null for the kinds that write their own outputs.
+B200_API int b200_gemm_skinny_fused(const void* X, const void* W, void* C, int M, int N, int K, int ldx, int ldw, int ldc,
+                                    int dual, int dtype, float* scratch, uint32_t* tickets, const void* epilogue,
+                                    void* stream) {
+  B200_REQUIRE(epilogue != nullptr, "b200_gemm_skinny_fused needs an epilogue description");
+  return skinny_impl(X, W, C, M, N, K, ldx, ldw, ldc, dual, dtype, scratch, tickets, 0,
+                     static_cast<const SkinnyEpilogue*>(epilogue), stream);
+}
+B200_API int b200_gemm_skinny_epilogue_bytes() { return static_cast<int>(sizeof(SkinnyEpilogue)); }
+
 // ------------------------------------------------------------------------------------------------
 // Entry point that allocates nothing (declared and documented in b200/no_alloc_api.h).
 // ------------------------------------------------------------------------------------------------
 #include "b200/no_alloc_api.h"
+
+#include <mutex>
 
 namespace b200 {
 constexpr long long kStaticScratchFloats = 1 << 20;
@@ -359,12 +559,15 @@ struct StaticArea {
   float* scratch = nullptr;
   uint32_t* tickets = nullptr;
 };
-// Resolved once per device, with that device current.
+// Resolved once per device, with that device current. The table is filled under a lock, so host threads that make
+// their first call on a device at the same time see either nothing or a complete entry.
 static int static_area(StaticArea** out) {
   static StaticArea areas[64];
+  static std::mutex mu;
   int dev = 0;
   B200_CHECK_CUDA(cudaGetDevice(&dev));
   B200_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
   StaticArea& a = areas[dev];
   if (a.scratch == nullptr) {
     void* ps = nullptr;

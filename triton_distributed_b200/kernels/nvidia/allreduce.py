@@ -14,8 +14,10 @@ API parity with ``python/triton_dist/kernels/nvidia/allreduce.py`` (``create_all
                          hop away, so a tree only adds hops; the name is kept for API parity
   =====================  =====================================================================
 
-With ``B200DIST_AR_LL=1`` fused calls of at most 512 KB take a low-latency packet path
-(``csrc/kernels/allreduce_ll.cu``: 8-byte {data, epoch} packets, no flag exchange).
+Fused calls of at most 512 KB (the decode path) take a low-latency packet kernel (``csrc/kernels/allreduce_ll.cu``:
+8-byte {data, epoch} packets that the receiver polls, so there is no flag exchange, fence or barrier; one
+``multimem.st`` per packet when the heap has an NVLS mapping). ``B200DIST_AR_LL=0`` / ``B200DIST_AR_LL_MC=0`` switch the
+packet path / its multicast stores off.
 
 Unlike the reference there is no staging memcpy outside the kernel and no host-side call counter:
 the kernel stages, synchronises CTA-by-CTA with its peers, reduces and (optionally) normalises, and
@@ -61,7 +63,8 @@ class AllReduceContext:
         self.ll_ws = None
 
 
-_AR_LL = os.environ.get("B200DIST_AR_LL", "0") == "1"
+_AR_LL = os.environ.get("B200DIST_AR_LL", "1") != "0"
+_AR_LL_MC = os.environ.get("B200DIST_AR_LL_MC", "1") != "0"
 _LL_MAX_BYTES = 512 * 1024   # input bytes per call served by the low-latency packet path
 
 
@@ -76,8 +79,8 @@ def create_allreduce_ctx(workspace_nbytes: int, rank: int, world_size: int, loca
     flags = heap.create_tensor((2 * max_ctas * 8,), torch.int32)
     ctx = AllReduceContext(workspace_nbytes, rank, world_size, local_world_size, heap, ws, flags,
                            torch.zeros(4, dtype=torch.int32, device="cuda"), max_ctas)
-    if _AR_LL:
-        # opt-in: dedicated packet buffers (data and flag share a word, so they must never hold anything else)
+    if _AR_LL and world_size > 1:
+        # dedicated packet buffers (data and flag share a word, so they must never hold anything else)
         ctx.ll_ws = [heap.create_tensor((world_size * _LL_MAX_BYTES * 2,), torch.uint8, align=1024) for _ in range(2)]
         ctx.ll_sync = torch.zeros(4, dtype=torch.int32, device="cuda")
     heap.barrier_all()
@@ -166,14 +169,14 @@ def all_reduce_rmsnorm(x: torch.Tensor, residual: torch.Tensor | None, gamma: to
     es = x.element_size()
     if (method is None and getattr(ctx, "ll_ws", None) is not None and es == 2 and x.numel() * es <= _LL_MAX_BYTES
             and hidden % 2 == 0 and hidden <= 8192 and x.is_contiguous()):
-        # opt-in low-latency path: 8-byte {data, epoch} packets, no flag exchange, no fence
+        # low-latency path: 8-byte {data, epoch} packets, no flag exchange, no fence
         if normed_out is None:
             normed_out = torch.empty_like(x)
         if residual_out is None:
             residual_out = residual if residual is not None else torch.empty_like(x)
         _lib.call("b200_allreduce_ll", ctx.heap.ctx, ptr(x), rows, hidden, dtype_code(x.dtype), ptr(ctx.ll_ws[0]),
                   ptr(ctx.ll_ws[1]), ptr(ctx.ll_sync), ptr(residual), ptr(residual_out), ptr(gamma), ptr(normed_out),
-                  c_float(eps), stream_ptr())
+                  c_float(eps), 1 if (_AR_LL_MC and ctx.heap.has_multicast) else 0, stream_ptr())
         ops._count()
         return normed_out, residual_out
     if method is None and x.numel() * es <= 512 * 1024:

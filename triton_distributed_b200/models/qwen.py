@@ -15,6 +15,8 @@ only its slices. The vocabulary is sharded over ranks for ``lm_head`` (logits ar
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 import torch.nn.functional as F
@@ -22,12 +24,14 @@ import torch.nn.functional as F
 from .. import ops
 from ..kernels.allreduce import AllReduceMethod
 from ..kernels.nvidia import (all_reduce_rmsnorm, create_ag_gemm_context, create_allreduce_ctx,
-                              create_gemm_rs_context)
+                              create_fast_allgather_context, create_gemm_rs_context, fast_allgather)
 from ..layers.nvidia import TP_MLP, TP_Attn, TP_MoE, _set_cos_sin_cache, golden, layer_norm
 from .config import ArchConfig, ModelConfig
 from .kv_cache import KV_Cache
 from .utils import logger
 from .weights import RandomSource, SafetensorsSource, WeightSource
+
+_FUSED_DECODE = os.environ.get("B200DIST_FUSED_DECODE", "1") != "0"
 
 
 class Qwen3Layer:
@@ -109,6 +113,8 @@ class Qwen3:
         self.device = "cuda" if torch.cuda.is_available() else "cpu"
         self.mode = "torch"
         self.ar_ctx = self.ag_ctx_qkv = self.ag_ctx_mlp = self.rs_ctx = self.moe_ctx = None
+        self.gather_ctx = None      # small-message all-gather of the native modes (logits, last hidden rows)
+        self.gather_rows = 0
         self.ar_method = None
         self.max_length = model_config.max_length
         self.init_parameters(source)
@@ -155,6 +161,7 @@ class Qwen3:
     def init_triton_dist_ctx(self, max_M: int) -> None:
         H = self.arch.hidden_size
         l0 = self.layers[0]
+        self._init_gather_ctx()
         dummy = torch.empty(max_M // self.world_size, H, dtype=self.dtype, device="cuda")
         if self.ag_ctx_qkv is None:
             # one gather context serves both projections (same K); one scatter context serves o_proj and down
@@ -170,8 +177,35 @@ class Qwen3:
             else:
                 layer.mlp._init_ctx(max_M, ag_ctx=self.ag_ctx_qkv, rs_ctx=self.rs_ctx)
 
+    _GATHER_ROWS = 32  # batch rows the native logits gather holds; larger batches take the NCCL all-gather
+
+    def _init_gather_ctx(self) -> None:
+        """Symmetric buffers for the per-step gathers of the native modes: the vocabulary-sharded logits and, in
+        ``triton_dist`` mode, the last hidden row of every sequence (both a few hundred KB)."""
+        if self.world_size == 1 or self.gather_ctx is not None:
+            return
+        from ..runtime.heap import get_heap
+        heap, w = get_heap(), self.world_size
+        rows, vloc, H = self._GATHER_ROWS, self.lm_head.shape[0], self.arch.hidden_size
+        self.gather_rows = rows
+        self.logit_buf = heap.create_tensor((w, rows, vloc), self.dtype, align=1024)
+        self.hidden_buf = heap.create_tensor((w, rows, H), self.dtype, align=1024)
+        self.gather_ctx = create_fast_allgather_context(self.rank, 0, w, 1, max_buffer_size=w * rows * max(vloc, H) * 2)
+        self.gather_mode = "push2d_ll_multimem" if heap.has_multicast else "push2d_ll"
+
+    def _gather_rows(self, buf: torch.Tensor, n_rows: int) -> torch.Tensor:
+        """All-gather the first n_rows of every rank's slot of `buf` [world, rows, C]; returns [world, n_rows, C]."""
+        if n_rows == buf.shape[1]:
+            fast_allgather(buf, self.gather_ctx, mode=self.gather_mode)
+            return buf
+        # fewer rows than the buffer holds: gather a compact view of the same symmetric allocation
+        view = buf.view(-1)[: self.world_size * n_rows * buf.shape[2]].view(self.world_size, n_rows, buf.shape[2])
+        fast_allgather(view, self.gather_ctx, mode=self.gather_mode)
+        return view
+
     def init_triton_dist_AR_ctx(self, max_M: int, ar_method: AllReduceMethod | None = None) -> None:
         self.ar_method = ar_method
+        self._init_gather_ctx()
         if self.world_size > 1 and self.ar_ctx is None:
             # fixed-size workspace: larger inputs are processed in row chunks
             self.ar_ctx = create_allreduce_ctx(64 << 20, self.rank, self.world_size, self.world_size)
@@ -186,10 +220,14 @@ class Qwen3:
                                    (widest + 127) // 128)
 
     def finalize(self) -> None:
-        for c in (self.ar_ctx, self.ag_ctx_qkv, self.rs_ctx) + tuple(self.moe_ctx or ()):
+        for c in (self.ar_ctx, self.ag_ctx_qkv, self.rs_ctx, self.gather_ctx) + tuple(self.moe_ctx or ()):
             if c:
                 c.finalize()
-        self.ar_ctx = self.ag_ctx_qkv = self.rs_ctx = self.moe_ctx = None
+        if self.gather_ctx is not None:
+            from ..runtime.heap import get_heap
+            get_heap().free(self.logit_buf)
+            get_heap().free(self.hidden_buf)
+        self.ar_ctx = self.ag_ctx_qkv = self.rs_ctx = self.moe_ctx = self.gather_ctx = None
 
     # ------------------------------------------------------------------ forward
     def _reduce_norm(self, partial, residual, gamma):
@@ -201,11 +239,16 @@ class Qwen3:
 
     @torch.no_grad()
     def _inference_AR(self, input_ids, position_ids, kv_cache):
+        """Returns (hidden, sumsq): with sumsq None, hidden [B, S, H] is final-normed; otherwise hidden is
+        ``h * final gain`` [B, 1, H] and the consumer applies ``rsqrt(sumsq / H + eps)`` per row."""
         bsz, seqlen = input_ids.shape
         T = bsz * seqlen
-        residual = F.embedding(input_ids.reshape(-1), self.embed_tokens)  # [T, H], becomes the residual stream
         step = {"pos": position_ids.reshape(-1).to(torch.int32), "slots": kv_cache.slots(position_ids),
                 "kv_lens": (position_ids[:, -1] + 1).to(torch.int32)}
+        if (self.world_size == 1 and seqlen == 1 and T <= 16 and self.arch.head_dim == 128 and not self.arch.num_experts
+                and _FUSED_DECODE):
+            return self._decode_fused_single_gpu(input_ids, kv_cache, step)
+        residual = ops.embedding(input_ids.reshape(-1), self.embed_tokens)  # [T, H], becomes the residual stream
         x = ops.rmsnorm(residual, self.layers[0].input_norm_w, self.eps)
         for i, layer in enumerate(self.layers):
             part = layer.attn.partial_fwd(x, position_ids, self.cos_sin_cache, kv_cache, i, bsz, seqlen, step)
@@ -213,7 +256,31 @@ class Qwen3:
             part = layer.mlp.partial_fwd(x)
             nxt = self.layers[i + 1].input_norm_w if i + 1 < self.num_layers else self.norm_w
             x = self._reduce_norm(part, residual, nxt)
-        return x.view(bsz, seqlen, -1)  # already final-normed
+        return x.view(bsz, seqlen, -1), None  # already final-normed
+
+    def _decode_fused_single_gpu(self, input_ids, kv_cache, step):
+        """One decode step on one GPU in five launches per layer. No normalisation kernel runs: the producer of the
+        residual stream (embedding, o_proj, down) also emits ``h * gain`` of the next RMSNorm and the row's sum of
+        squares, and the consumer projection multiplies its rows by ``rsqrt(sumsq / H + eps)``; the qkv projection
+        finishes the heads (norm, RoPE, cache write) in its epilogue."""
+        T, H, L = input_ids.numel(), self.arch.hidden_size, self.num_layers
+        dev = self.embed_tokens.device
+        if getattr(self, "_sumsq", None) is None:
+            self._sumsq = torch.zeros((2 * L + 1, 16), dtype=torch.float32, device=dev)
+        S = self._sumsq
+        S.zero_()
+        residual = torch.empty((T, H), dtype=self.dtype, device=dev)
+        xg = torch.empty_like(residual)   # h * gain of the next norm (input of the next projection)
+        ops.embedding(input_ids.reshape(-1), self.embed_tokens, out=residual, gamma=self.layers[0].input_norm_w,
+                      scaled_out=xg, sumsq_out=S[0])
+        for i, layer in enumerate(self.layers):
+            o = layer.attn.decode_attn_fused(xg, self.cos_sin_cache, kv_cache, i, step, in_sumsq=S[2 * i])
+            ops.gemm_skinny(o, layer.attn.wo, epilogue=ops.skinny_residual(residual, S[2 * i + 1], layer.post_norm_w, xg))
+            act = ops.gemm_skinny(xg, layer.mlp.gate_up_proj, swiglu=True,
+                                  epilogue=ops.skinny_row_scale(S[2 * i + 1], H, self.eps))
+            nxt = self.layers[i + 1].input_norm_w if i + 1 < L else self.norm_w
+            ops.gemm_skinny(act, layer.mlp.down_proj, epilogue=ops.skinny_residual(residual, S[2 * i + 2], nxt, xg))
+        return xg.view(T, 1, H), S[2 * L]
 
     @torch.no_grad()
     def inference(self, input_ids: torch.Tensor, position_ids: torch.Tensor, kv_cache: KV_Cache,
@@ -221,29 +288,52 @@ class Qwen3:
         """input_ids / position_ids [B, S] (full batch on every rank). Returns fp32 logits [B, 1, V] of the last
         position (or the normed hidden states with ``wo_lm_head``). ``triton_dist`` mode needs B % world == 0."""
         bsz, seqlen = input_ids.shape
+        native_gather = self.world_size > 1 and self.gather_ctx is not None and bsz <= self.gather_rows
+        sumsq = None
         if self.mode == "triton_dist_AR":
-            hidden = self._inference_AR(input_ids, position_ids, kv_cache)
+            hidden, sumsq = self._inference_AR(input_ids, position_ids, kv_cache)
+            if sumsq is not None and wo_lm_head:
+                inv = torch.rsqrt(sumsq[:bsz] / hidden.shape[-1] + self.eps)
+                hidden, sumsq = (hidden.float() * inv[:, None, None]).to(hidden.dtype), None
         else:
-            hidden = F.embedding(input_ids, self.embed_tokens)
+            native = self.mode == "triton_dist"
+            hidden = ops.embedding(input_ids, self.embed_tokens) if native else F.embedding(input_ids, self.embed_tokens)
             step = None
-            if self.mode == "triton_dist":
+            if native:
                 bl = bsz // self.world_size
                 hidden = hidden[self.rank * bl:(self.rank + 1) * bl].contiguous()
                 step = {"pos": position_ids.reshape(-1).to(torch.int32), "slots": kv_cache.slots(position_ids),
                         "kv_lens": (position_ids[:, -1] + 1).to(torch.int32)}
             for layer in self.layers:
                 hidden = layer.fwd(hidden, position_ids, self.cos_sin_cache, kv_cache, step)
-            hidden = (golden.rmsnorm(hidden, self.norm_w, self.eps) if self.mode == "torch"
-                      else layer_norm(hidden, self.eps, self.norm_w))
-            if self.mode == "triton_dist":
-                full = torch.empty((bsz, seqlen, hidden.shape[-1]), dtype=hidden.dtype, device=hidden.device)
-                dist.all_gather_into_tensor(full, hidden.contiguous(), group=self.group)
-                hidden = full
+            if native and not wo_lm_head and native_gather:
+                # only the last position feeds the head: norm and gather b_local rows instead of the whole sequence
+                last_local = layer_norm(hidden[:, -1, :].contiguous(), self.eps, self.norm_w)
+                bl = last_local.shape[0]
+                self.hidden_buf.view(-1)[: self.world_size * bl * last_local.shape[1]].view(self.world_size, bl, -1)[self.rank].copy_(last_local)
+                hidden = self._gather_rows(self.hidden_buf, bl).reshape(bsz, 1, -1)
+            else:
+                hidden = (golden.rmsnorm(hidden, self.norm_w, self.eps) if self.mode == "torch"
+                          else layer_norm(hidden, self.eps, self.norm_w))
+                if native:
+                    full = torch.empty((bsz, seqlen, hidden.shape[-1]), dtype=hidden.dtype, device=hidden.device)
+                    dist.all_gather_into_tensor(full, hidden.contiguous(), group=self.group)
+                    hidden = full
         if wo_lm_head:
             return hidden
         last = hidden[:, -1, :].contiguous()
         if self.mode == "torch":
             local = F.linear(last, self.lm_head)
+        elif native_gather:
+            # the head writes its vocabulary shard straight into this rank's slot of the symmetric gather buffer
+            vloc = self.lm_head.shape[0]
+            slot = self.logit_buf.view(-1)[: self.world_size * bsz * vloc].view(self.world_size, bsz, vloc)[self.rank]
+            ops.linear(last, self.lm_head, out=slot)  # (never with a pending row scale: that path is single-GPU)
+            gathered = self._gather_rows(self.logit_buf, bsz)
+            local = gathered.permute(1, 0, 2).reshape(bsz, -1)
+            return local[:, : self.arch.vocab_size].float().unsqueeze(1)
+        elif sumsq is not None:
+            local = ops.gemm_skinny(last, self.lm_head, epilogue=ops.skinny_row_scale(sumsq, last.shape[-1], self.eps))
         else:
             local = ops.linear(last, self.lm_head)
         if self.world_size > 1:

@@ -75,26 +75,98 @@ def reserve_skinny_scratch(device, floats: int, tiles: int) -> None:
     _skinny_scratch.get(torch.device(device), floats, tiles)
 
 
+class SkinnyEpilogue(ctypes.Structure):
+    """Mirror of ``b200::SkinnyEpilogue`` (csrc/kernels/gemm_skinny_sm100.cu): what the decode GEMM does with a
+    finished tile besides storing it. Build one with ``skinny_row_scale``, ``skinny_qkv_heads`` or ``skinny_residual``."""
+    _fields_ = [("kind", ctypes.c_int), ("sumsq_in", ctypes.c_void_p), ("scale_dim", ctypes.c_float), ("eps", ctypes.c_float),
+                ("Hq", ctypes.c_int), ("Hkv", ctypes.c_int), ("positions", ctypes.c_void_p), ("slots", ctypes.c_void_p),
+                ("cos_sin", ctypes.c_void_p), ("q_gamma", ctypes.c_void_p), ("k_gamma", ctypes.c_void_p),
+                ("q_out", ctypes.c_void_p), ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p),
+                ("head_eps", ctypes.c_float), ("residual_in", ctypes.c_void_p), ("residual_out", ctypes.c_void_p),
+                ("next_gamma", ctypes.c_void_p), ("scaled_out", ctypes.c_void_p), ("sumsq_out", ctypes.c_void_p)]
+
+    def __init__(self, **kw):
+        super().__init__()
+        self._keep = []  # tensors referenced by raw pointers stay alive as long as the description does
+        for k, v in kw.items():
+            if isinstance(v, torch.Tensor):
+                self._keep.append(v)
+                v = v.data_ptr()
+            setattr(self, k, v)
+
+
+def _dptr(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def skinny_row_scale(sumsq: torch.Tensor, dim: int, eps: float, base: SkinnyEpilogue | None = None) -> SkinnyEpilogue:
+    """Epilogue ``out[m, :] *= rsqrt(sumsq[m] / dim + eps)``: the RMSNorm of the GEMM's input when its producer already
+    applied the gain. `sumsq` fp32 [>= M]. Combines with another epilogue when `base` is given."""
+    ep = base if base is not None else SkinnyEpilogue(kind=0)
+    ep.sumsq_in, ep.scale_dim, ep.eps = sumsq.data_ptr(), float(dim), float(eps)
+    ep._keep.append(sumsq)
+    return ep
+
+
+def skinny_qkv_heads(positions: torch.Tensor, slots: torch.Tensor | None, cos_sin: torch.Tensor, num_q_heads: int,
+                     num_kv_heads: int, q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     q_gamma: torch.Tensor | None, k_gamma: torch.Tensor | None, eps: float) -> SkinnyEpilogue:
+    """Epilogue of the fused qkv projection (head dim 128): per-head RMSNorm of q / k, neox RoPE, q to ``q_out``
+    [M, Hq, 128] and k / v into the caches viewed as [slots, Hkv, 128] at ``slots`` (int64 [M], None = identity)."""
+    if positions.dtype != torch.int32 or cos_sin.dtype != torch.float32 or (slots is not None and slots.dtype != torch.int64):
+        raise ValueError("positions must be int32, slots int64 and cos_sin float32")
+    ep = SkinnyEpilogue(kind=1, Hq=num_q_heads, Hkv=num_kv_heads, positions=positions, cos_sin=cos_sin, q_out=q_out,
+                        k_cache=k_cache, v_cache=v_cache, head_eps=float(eps))
+    for name, t in (("slots", slots), ("q_gamma", q_gamma), ("k_gamma", k_gamma)):
+        if t is not None:
+            setattr(ep, name, t.data_ptr())
+            ep._keep.append(t)
+    return ep
+
+
+def skinny_residual(residual: torch.Tensor, sumsq_out: torch.Tensor | None, next_gamma: torch.Tensor | None = None,
+                    scaled_out: torch.Tensor | None = None, residual_out: torch.Tensor | None = None) -> SkinnyEpilogue:
+    """Epilogue ``h = out + residual``: writes h to ``residual_out`` (default: in place), ``h * next_gamma`` to
+    ``scaled_out`` and adds ``sum(h^2)`` per token to ``sumsq_out`` (fp32, zeroed by the caller once per step)."""
+    ro = residual if residual_out is None else residual_out
+    ep = SkinnyEpilogue(kind=2, residual_in=residual, residual_out=ro)
+    for name, t in (("sumsq_out", sumsq_out), ("next_gamma", next_gamma), ("scaled_out", scaled_out)):
+        if t is not None:
+            setattr(ep, name, t.data_ptr())
+            ep._keep.append(t)
+    return ep
+
+
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, swiglu: bool = False,
-                splits: int = 0) -> torch.Tensor:
+                splits: int = 0, epilogue: SkinnyEpilogue | None = None) -> torch.Tensor | None:
     """Decode GEMM for ``M <= 256`` tokens: ``x[M,K] @ w[N,K].T`` with the weights streamed once.
 
     With ``swiglu=True``, ``w`` is ``[gate; up]`` (2*I rows) and the result is ``silu(x gate^T) * (x up^T)`` [M, I].
+    With ``epilogue`` (M <= 16) the finished tiles go through a fused epilogue instead of (or before) the plain store;
+    the qkv-heads and residual kinds write their own outputs and return None unless ``out`` is given.
     """
     _lib.require_cuda()
     _check_2d(x, "x"), _check_2d(w, "w")
     M, K = x.shape
     n_rows = w.shape[0]
     N = n_rows // 2 if swiglu else n_rows
-    if out is None:
+    own_output = epilogue is not None and epilogue.kind in (1, 2)
+    if out is None and not own_output:
         out = torch.empty((M, N), dtype=x.dtype, device=x.device)
     lib = _lib.load()
     lib.b200_gemm_skinny_scratch_floats.restype = ctypes.c_longlong
     floats = lib.b200_gemm_skinny_scratch_floats(M, N, 1 if swiglu else 0)
     tiles = (N + 127) // 128
     scratch, tickets = _skinny_scratch.get(x.device, floats, tiles)
-    _lib.call("b200_gemm_skinny", ptr(x), ptr(w), ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
-              1 if swiglu else 0, dtype_code(x.dtype), ptr(scratch), ptr(tickets), splits, stream_ptr())
+    ldc = out.stride(0) if out is not None else (epilogue._keep[0].stride(0) if epilogue.kind == 2 else N)
+    if epilogue is None:
+        _lib.call("b200_gemm_skinny", ptr(x), ptr(w), ptr(out), M, N, K, x.stride(0), w.stride(0), ldc,
+                  1 if swiglu else 0, dtype_code(x.dtype), ptr(scratch), ptr(tickets), splits, stream_ptr())
+    else:
+        if ctypes.sizeof(SkinnyEpilogue) != lib.b200_gemm_skinny_epilogue_bytes():
+            raise RuntimeError("SkinnyEpilogue layout differs between the Python binding and the native library")
+        _lib.call("b200_gemm_skinny_fused", ptr(x), ptr(w), ptr(out), M, N, K, x.stride(0), w.stride(0), ldc,
+                  1 if swiglu else 0, dtype_code(x.dtype), ptr(scratch), ptr(tickets), ctypes.byref(epilogue), stream_ptr())
     _count()
     return out
 
@@ -150,6 +222,25 @@ def qk_norm_rope(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tens
               dtype_code(qkv.dtype), stream_ptr())
     _count()
     return q_out
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None, gamma: torch.Tensor | None = None,
+              scaled_out: torch.Tensor | None = None, sumsq_out: torch.Tensor | None = None) -> torch.Tensor:
+    """``table[ids]`` for int64 ids of any shape -> [*ids.shape, H] (ids outside the table give zero rows).
+
+    For a following RMSNorm folded into the consumer GEMM: ``sumsq_out`` (fp32 [T]) receives every row's sum of
+    squares and ``scaled_out`` ([T, H]) the row times ``gamma``."""
+    _lib.require_cuda()
+    if not table.is_contiguous() or table.dim() != 2:
+        raise ValueError("embedding table must be a contiguous [V, H] tensor")
+    flat = ids.reshape(-1).to(torch.int64).contiguous()
+    V, H = table.shape
+    if out is None:
+        out = torch.empty((flat.numel(), H), dtype=table.dtype, device=table.device)
+    _lib.call("b200_embedding", ptr(flat), ptr(table), ptr(out), flat.numel(), ctypes.c_longlong(V), H, dtype_code(table.dtype),
+              ptr(gamma), ptr(scaled_out), ptr(sumsq_out), stream_ptr())
+    _count()
+    return out.reshape(*ids.shape, H)
 
 
 def silu_mul(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -209,7 +300,9 @@ def choose_kv_splits(batch: int, num_kv_heads: int, group: int, max_kv_len: int,
     return int(max(1, min(by_machine, by_len, 64)))
 
 
-_FUSED_COMBINE_DEFAULT = os.environ.get("B200DIST_ATTN_FUSED_COMBINE", "1") != "0"
+# measured on the end-to-end decode step (one GPU, CUDA graph): the in-kernel merge costs 0.3 ms per step more than the
+# separate combine launch, whose start overlaps the split kernel under programmatic dependent launch
+_FUSED_COMBINE_DEFAULT = os.environ.get("B200DIST_ATTN_FUSED_COMBINE", "0") == "1"
 
 
 def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_lens: torch.Tensor,

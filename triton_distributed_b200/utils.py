@@ -167,16 +167,23 @@ def flush_l2() -> None:
     _l2_flush_buf.zero_()
 
 
-def perf_func_cold(func: Callable, iters: int, warmup_iters: int):
+def perf_func_cold(func: Callable, iters: int, warmup_iters: int, head_start_us: float = 200.0):
     """Like perf_func but with an L2 flush before every timed call; each call is timed separately.
-    Returns (last output, mean ms, list of per-call ms)."""
+    Returns (last output, mean ms, list of per-call ms).
+
+    The device spins for `head_start_us` before the first event, so the host has enqueued the call by the time the
+    device reaches it: the interval then holds device time only, not the host's launch latency (which otherwise
+    puts a floor of tens of microseconds under every small kernel)."""
     out = None
     for _ in range(warmup_iters):
         out = func()
     times = []
+    spin = int(head_start_us * 1.9e3)  # cycles at the boost clock; the exact length does not matter
     for _ in range(iters):
         flush_l2()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if spin > 0:
+            torch.cuda._sleep(spin)
         a.record()
         out = func()
         b.record()
