@@ -63,6 +63,12 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def wait_first_sample(self, timeout_s: float) -> None:
+        """Block until nvidia-smi has printed its first line (its initialisation is over) or `timeout_s` has passed."""
+        t0 = time.time()
+        while self.proc is not None and not self.lines and time.time() - t0 < timeout_s:
+            time.sleep(0.02)
+
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -263,11 +269,14 @@ def main() -> None:
         pinned_out = torch.empty((args.batch, 1), dtype=torch.int64).pin_memory()
         pinned_in.copy_(first.cpu())
         eng.kv_cache.kv_offset.copy_(kv_after_prefill)
+        # the sampler starts BEFORE the warm-up steps: nvidia-smi's start-up (driver queries from one process per rank at
+        # once) stalls kernel launches for tens of milliseconds, which must not land inside the timed steps
+        sampler = ClockSampler(torch.cuda.current_device())
+        sampler.start()
+        sampler.wait_first_sample(3.0)
         for _ in range(args.warmup):
             eng.decode_one()
         sync_all()
-        sampler = ClockSampler(torch.cuda.current_device())
-        sampler.start()
         marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
         marks[0].record()
         for i in range(args.steps):

@@ -108,6 +108,40 @@ def primitives_put_get_notify():
 
 
 @case
+def shmem_device_api():
+    """broadcast / fcollect / putmem_signal_warp / int_p / barrier_all_warp / team queries in one collective kernel."""
+    rank, world = _rank_world()
+    heap = get_heap()
+    n4 = 512
+    n = n4 * 4
+    bcast = heap.create_tensor((n,), torch.float32)
+    coll = heap.create_tensor((world, n), torch.float32)
+    ring = heap.create_tensor((n,), torch.float32)
+    sig = heap.create_tensor((2,), torch.int32)
+    word = heap.create_tensor((world,), torch.int32)
+    flags = heap.create_tensor((16,), torch.int32)
+    ok = torch.zeros(1, dtype=torch.int32, device="cuda")
+    base = torch.arange(n, device="cuda", dtype=torch.float32)
+    for it in range(1, 4):
+        root = it % world
+        src = base + 1000.0 * rank + it
+        heap.barrier_all()
+        _lib.call("b200_test_shmem_api", heap.ctx, _lib.ptr(src), _lib.ptr(bcast), _lib.ptr(coll), _lib.ptr(ring), _lib.ptr(sig),
+                  _lib.ptr(word), _lib.ptr(flags), n4, root, it, _lib.ptr(ok), _lib.stream_ptr())
+        torch.cuda.synchronize()
+        assert int(ok.item()) == 1, "shmem api probe reported a failed wait"
+        assert torch.equal(bcast, base + 1000.0 * root + it), "broadcast"
+        for r in range(world):
+            assert torch.equal(coll[r], base + 1000.0 * r + it), f"fcollect slot {r}"
+        assert torch.equal(ring, base + 1000.0 * ((rank - 1) % world) + it), "putmem_signal_warp"
+        assert word.tolist() == [it + r for r in range(world)], "int_p"
+        heap.barrier_all()
+    torch.cuda.synchronize()
+    for t in (flags, word, sig, ring, coll, bcast):
+        heap.free(t)
+
+
+@case
 def fast_allgather_modes():
     rank, world = _rank_world()
     heap = get_heap()

@@ -241,3 +241,52 @@ def test_packet_allreduce_single_buffer_is_caught():
         except Violation:
             failures += 1
     assert failures > 0
+
+
+# ---------------------------------------------------------------------------------------------- AG pull gather
+def _ag_pull_model(world, calls, rng, compare="ge", use_parity=True):
+    """Pull gather of AG-GEMM / AG grouped GEMM: every rank copies its shard into its own symmetric buffer (by epoch
+    parity), publishes ready[rank] = epoch on every peer, and pulls a peer's shard once that peer's flag compares true.
+    A rank leaves a call as soon as it has pulled everything it needs: it does not wait for anybody to pull from it."""
+    npar = 2 if use_parity else 1
+    buf = [[None] * npar for _ in range(world)]            # buf[rank][parity] = (epoch, rank) of the shard held there
+    ready = [[0] * world for _ in range(world)]            # ready[on rank][source] = last epoch published by source
+
+    def rank_thread(r):
+        for e in range(1, calls + 1):
+            par = e % npar
+            buf[r][par] = (e, r)
+            yield True
+            for peer in range(world):                       # fence, then a release store of the epoch to every peer
+                ready[peer][r] = e
+                yield True
+            for k in range(1, world):
+                src = (r + k) % world
+                while not (ready[r][src] == e if compare == "eq" else ready[r][src] >= e):
+                    yield False
+                got = buf[src][par]
+                if got != (e, src):
+                    raise Violation(f"rank {r} call {e}: pulled {got} from rank {src}")
+                yield True
+
+    _run([rank_thread(r) for r in range(world)], rng)
+
+
+@pytest.mark.parametrize("world", [2, 3, 4])
+def test_ag_pull_gather_is_safe_with_at_least_compare_and_parity(world):
+    for seed in range(300):
+        _ag_pull_model(world, calls=6, rng=random.Random(seed))
+
+
+def test_ag_pull_gather_with_equality_compare_deadlocks():
+    """A peer that has pulled everything it needs may publish the next epoch before a slow rank has looked at the flag;
+    waiting for equality then never ends (on the GPU: until the wait's time budget runs out). Seen at eight ranks."""
+    with pytest.raises(Violation, match="deadlock"):
+        for seed in range(300):
+            _ag_pull_model(3, calls=6, rng=random.Random(seed), compare="eq")
+
+
+def test_ag_pull_gather_without_parity_is_caught():
+    with pytest.raises(Violation):
+        for seed in range(300):
+            _ag_pull_model(3, calls=6, rng=random.Random(seed), use_parity=False)

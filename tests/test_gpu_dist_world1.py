@@ -201,3 +201,26 @@ def test_sp_ag_attention_world1(dist1, zigzag):
             is_causal=True, enable_gqa=True)[0].transpose(0, 1)
         torch.testing.assert_close(out[s].float(), want, rtol=3e-2, atol=3e-2)
     ctx.finalize()
+
+
+def test_shmem_device_api_world1(dist1):
+    """broadcast / fcollect / putmem_signal_warp / int_p / barrier_all_warp with the GPU as its own only peer."""
+    from triton_distributed_b200 import _lib
+    from triton_distributed_b200.runtime.heap import get_heap
+    heap = get_heap()
+    n4 = 256
+    n = n4 * 4
+    bcast, ring = heap.create_tensor((n,), torch.float32), heap.create_tensor((n,), torch.float32)
+    coll = heap.create_tensor((1, n), torch.float32)
+    sig, word, flags = heap.create_tensor((2,), torch.int32), heap.create_tensor((1,), torch.int32), heap.create_tensor((16,), torch.int32)
+    ok = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for it in (1, 2):
+        src = torch.arange(n, device="cuda", dtype=torch.float32) + it
+        _lib.call("b200_test_shmem_api", heap.ctx, _lib.ptr(src), _lib.ptr(bcast), _lib.ptr(coll), _lib.ptr(ring), _lib.ptr(sig),
+                  _lib.ptr(word), _lib.ptr(flags), n4, 0, it, _lib.ptr(ok), _lib.stream_ptr())
+        torch.cuda.synchronize()
+        assert int(ok.item()) == 1
+        assert torch.equal(bcast, src) and torch.equal(coll[0], src) and torch.equal(ring, src) and int(word[0]) == it
+    heap.check_status()
+    for t in (flags, word, sig, coll, ring, bcast):
+        heap.free(t)

@@ -5,6 +5,10 @@ Every kernel executes its real code path (flag epochs, slot buffers, communicati
 traffic. Sizes are small (a few hundred MB at most) so that a ``--set full`` capture ends by itself.
 
 Example: ``python -m triton_distributed_b200.benchmark.bench_kernels --op ag_gemm --iters 3``
+
+``--op decode_step`` is different: it builds the first ``--layers`` layers of Qwen3-32B, captures one decode step of
+``Engine`` (batch 8, prompt 2048) in a CUDA graph and prints the device time per kernel name from ``torch.profiler``
+over a few replays (a timeline, not ncu). It also runs under torchrun on several GPUs.
 """
 from __future__ import annotations
 
@@ -18,7 +22,7 @@ import torch
 from .. import ops, utils
 from ..utils import perf_func_cold
 
-OPS = ["ag_gemm", "gemm_rs", "grouped_gemm", "grouped_gemm_fp8", "ag_group_gemm", "moe_reduce_rs", "allreduce_rmsnorm", "ep_dispatch_combine",
+OPS = ["decode_step", "prefill_attn", "gemm_skinny_fused", "ag_gemm", "gemm_rs", "grouped_gemm", "grouped_gemm_fp8", "ag_group_gemm", "moe_reduce_rs", "allreduce_rmsnorm", "ep_dispatch_combine",
        "decode_attn", "sp_decode", "moe_sort", "sampling", "rmsnorm", "qk_norm_rope"]
 
 
@@ -32,7 +36,11 @@ def main() -> None:
     ap.add_argument("--k", type=int, default=0, help="ag_gemm / gemm_rs: K (0 = the Llama-3-70B TP8 default)")
     ap.add_argument("--kv-len", type=int, default=16384, help="KV length of the decode_attn / sp_decode problem")
     ap.add_argument("--splits", type=int, default=0, help="decode_attn: KV splits (0 = the library's choice)")
+    ap.add_argument("--layers", type=int, default=8, help="decode_step: transformer layers to build (64 = the full model)")
+    ap.add_argument("--out", default=None, help="decode_step: text file for the table (rank 0)")
     args = ap.parse_args()
+    if args.op == "decode_step":
+        return decode_step_table(args)
     os.environ.setdefault("RANK", "0"), os.environ.setdefault("LOCAL_RANK", "0"), os.environ.setdefault("WORLD_SIZE", "1")
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1"), os.environ.setdefault("MASTER_PORT", "29571")
     group = utils.initialize_distributed(seed=0, heap_bytes=2 << 30)
@@ -102,6 +110,30 @@ def main() -> None:
             layer.dispatch(x, ids)
             return layer.combine(back, wt)
         info = {"bytes": T * H * 2.0 + T * topk * H * 1.0 + T * topk * H * 2.0 * 2 + T * H * 2.0}
+    elif args.op == "prefill_attn":
+        B, S, Hq, Hkv, D = 8, args.kv_len if args.kv_len <= 8192 else 2048, 64, 8, 128
+        q = torch.randn(B * S, Hq, D, device=dev, dtype=dt)
+        k = torch.randn(B * S, Hkv, D, device=dev, dtype=dt)
+        v = torch.randn_like(k)
+        cu = torch.arange(0, (B + 1) * S, S, device=dev, dtype=torch.int32)
+        fn = lambda: ops.prefill_attention(q, k, v, cu, cu, S, S, 1 / math.sqrt(D), True)
+        info = {"flops": 4.0 * B * Hq * S * S * D / 2}
+    elif args.op == "gemm_skinny_fused":
+        M, H, Hq, Hkv, D = 8, 5120, 64, 8, 128
+        x = torch.randn(M, H, device=dev, dtype=dt)
+        w = torch.randn((Hq + 2 * Hkv) * D, H, device=dev, dtype=dt) * 0.02
+        pos = torch.randint(0, 2000, (M,), device=dev, dtype=torch.int32)
+        inv = 1.0 / (1e6 ** (torch.arange(0, D, 2, device=dev, dtype=torch.float32) / D))
+        ang = torch.arange(4096, device=dev, dtype=torch.float32)[:, None] * inv[None, :]
+        cs = torch.cat([ang.cos(), ang.sin()], -1).contiguous()
+        kcache = torch.zeros(64, Hkv, D, device=dev, dtype=dt)
+        vcache = torch.zeros_like(kcache)
+        qo = torch.zeros(M, Hq, D, device=dev, dtype=dt)
+        g = torch.ones(D, device=dev, dtype=dt)
+        ss = torch.full((16,), float(H), device=dev)
+        ep = ops.skinny_row_scale(ss, H, 1e-6, base=ops.skinny_qkv_heads(pos, None, cs, Hq, Hkv, qo, kcache, vcache, g, g, 1e-6))
+        fn = lambda: ops.gemm_skinny(x, w, epilogue=ep)
+        info = {"bytes": 2.0 * w.numel()}
     elif args.op in ("decode_attn", "sp_decode"):
         B, Hq, Hkv, D, page, L = 8, 64, 8, 128, 64, args.kv_len
         nb = L // page
@@ -153,7 +185,51 @@ def main() -> None:
     if "splits" in info:
         out["splits"] = info["splits"]
     print(json.dumps(out), flush=True)
-    os._exit(0)
+    utils.finalize_distributed()
+
+
+def decode_step_table(args) -> None:
+    """Device time per kernel of one captured decode step (see the module docstring)."""
+    import torch.distributed as dist
+
+    from ..models import Engine, ModelConfig
+    for k, v in (("RANK", "0"), ("LOCAL_RANK", "0"), ("WORLD_SIZE", "1"), ("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", "29547")):
+        os.environ.setdefault(k, v)
+    group = utils.initialize_distributed(seed=0, heap_bytes=1 << 30)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    cfg = ModelConfig(model_name="Qwen/Qwen3-32B", max_length=2048 + 256, rank=rank, world_size=world,
+                      num_layers_override=args.layers)
+    eng = Engine(cfg, temperature=0.6, top_p=0.95, group=group)
+    prompt = torch.randint(0, 151936, (8, 2048), device="cuda")
+    eng.prepare_decode(eng.prefill(prompt))
+    for _ in range(4):
+        eng.decode_one()
+    torch.cuda.synchronize()
+    from torch.profiler import ProfilerActivity, profile
+    steps = max(args.iters, 4)
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        for _ in range(steps):
+            eng.decode_one()
+        torch.cuda.synchronize()
+    if rank == 0:
+        rows = []
+        for e in prof.key_averages():
+            t = getattr(e, "device_time_total", 0) or getattr(e, "cuda_time_total", 0)
+            if t > 0 and e.device_type.name == "CUDA":
+                rows.append((t / steps, e.count / steps, e.key[:90]))
+        rows.sort(reverse=True)
+        lines = [f"world={world} layers={args.layers}: total kernel us/step {sum(r[0] for r in rows):.1f}"]
+        lines += [f"{t:10.1f} us/step  {c:7.1f} calls/step  {t / max(c, 1e-9):8.2f} us/call  {k}" for t, c, k in rows[:25]]
+        print("\n".join(lines), flush=True)
+        if args.out:
+            os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
+            with open(args.out, "w") as f:
+                f.write("\n".join(lines) + "\n")
+    if eng.graph is not None:
+        eng.graph.reset()
+        eng.graph = None
+    torch.cuda.synchronize()
+    utils.finalize_distributed()
 
 
 if __name__ == "__main__":

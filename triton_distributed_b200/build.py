@@ -90,6 +90,24 @@ def build(force: bool = False, verbose: bool = False, ptxas_v: bool = False, job
     return LIB_PATH
 
 
+def compile_extension(source: str | Path, out_dir: str | Path | None = None, extra_flags: list[str] | None = None) -> Path:
+    """Compile ONE user ``.cu`` file written against ``b200/primitives.cuh`` (and ``tcgen05.cuh``) into a shared object
+    for sm_100a and return its path (load it with ``ctypes.CDLL``). Recompiled only when the source or a header is
+    newer than the output. This is how a kernel that uses ``wait`` / ``notify`` / ``symm_at`` / ``putmem_signal_block``
+    is built outside the library, the counterpart of JIT-compiling a ``@triton.jit`` function in the reference."""
+    src = Path(source).resolve()
+    out_dir = Path(out_dir) if out_dir is not None else BUILD / "ext"
+    out_dir.mkdir(parents=True, exist_ok=True)
+    out = out_dir / (src.stem + ".so")
+    if out.exists() and out.stat().st_mtime >= max(src.stat().st_mtime, _headers_mtime()):
+        return out
+    cmd = [_nvcc(), *NVCC_FLAGS, "-shared", str(src), "-o", str(out), *(extra_flags or [])]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {src.name}:\n{proc.stdout}\n{proc.stderr}")
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--force", action="store_true")

@@ -409,6 +409,145 @@ __device__ __forceinline__ void epoch_end(uint32_t* epoch_ptr, uint32_t* done_co
 }
 
 // ----------------------------------------------------------------------------------------------
+// Remainder of the SHMEM-style device API (shmem/nvshmem_bind/runtime/nvshmem_wrapper.cu:26-695,
+// python/triton_dist/language/extra/libshmem_device.py:28-337). One NVSwitch node is one team.
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ int my_pe(const SymmCtx& c) { return c.rank; }
+__device__ __forceinline__ int n_pes(const SymmCtx& c) { return c.world; }
+// Team queries: the only team is the node (TEAM_WORLD == TEAM_NODE), so team ranks are global ranks.
+__device__ __forceinline__ int team_my_pe(const SymmCtx& c) { return c.rank; }
+__device__ __forceinline__ int team_n_pes(const SymmCtx& c) { return c.world; }
+__device__ __forceinline__ int team_translate_pe(const SymmCtx& c, int pe) { return pe >= 0 && pe < c.world ? pe : -1; }
+// remote_ptr / remote_mc_ptr of the reference
+template <typename T>
+__device__ __forceinline__ T* remote_ptr(const SymmCtx& c, T* local_ptr, int pe) { return symm_at(c, local_ptr, pe); }
+template <typename T>
+__device__ __forceinline__ T* remote_mc_ptr(const SymmCtx& c, T* local_ptr) { return c.mc_base ? mc_ptr(c, local_ptr) : nullptr; }
+// int_p: one 32-bit store into `pe`'s copy of a symmetric word
+__device__ __forceinline__ void int_p(const SymmCtx& c, int32_t* dst_local, int32_t value, int pe) {
+  st_relaxed_sys(reinterpret_cast<uint32_t*>(symm_at(c, dst_local, pe)), static_cast<uint32_t>(value));
+}
+
+// Non-blocking puts / gets. The copies above are already plain loads and stores that retire asynchronously, so the
+// _nbi forms issue the same instructions; completion (and ordering against a later signal) is what quiet() / fence()
+// give, exactly as for the blocking forms followed by a signal.
+__device__ __forceinline__ void putmem_nbi_block(const SymmCtx& c, void* dst_local, const void* src, size_t nbytes, int pe) {
+  putmem_block(c, dst_local, src, nbytes, pe);
+}
+__device__ __forceinline__ void putmem_nbi_warp(const SymmCtx& c, void* dst_local, const void* src, size_t nbytes, int pe) {
+  putmem_warp(c, dst_local, src, nbytes, pe);
+}
+__device__ __forceinline__ void putmem_nbi(const SymmCtx& c, void* dst_local, const void* src, size_t nbytes, int pe) {
+  putmem(c, dst_local, src, nbytes, pe);
+}
+__device__ __forceinline__ void getmem_nbi_block(const SymmCtx& c, void* dst, const void* src_local, size_t nbytes, int pe) {
+  getmem_block(c, dst, src_local, nbytes, pe);
+}
+__device__ __forceinline__ void getmem_nbi_warp(const SymmCtx& c, void* dst, const void* src_local, size_t nbytes, int pe) {
+  getmem_warp(c, dst, src_local, nbytes, pe);
+}
+__device__ __forceinline__ void getmem(const SymmCtx& c, void* dst, const void* src_local, size_t nbytes, int pe) {
+  copy_bytes_strided(dst, symm_at(c, reinterpret_cast<const uint8_t*>(src_local), pe), nbytes, 0, 1);
+}
+// putmem_signal for a warp and for one thread (the block form is above). The signal follows the data: the issuing
+// lanes fence at system scope before the one signalling thread updates the peer's flag.
+__device__ __forceinline__ void putmem_signal_warp(const SymmCtx& c, void* dst_local, const void* src, size_t nbytes,
+                                                   uint32_t* sig_local, uint32_t sig_value, SigOp op, int pe) {
+  putmem_warp(c, dst_local, src, nbytes, pe);
+  fence_acq_rel_sys();
+  __syncwarp();
+  if (lane_id() == 0) signal_op(c, sig_local, sig_value, op, pe);
+}
+__device__ __forceinline__ void putmem_signal(const SymmCtx& c, void* dst_local, const void* src, size_t nbytes,
+                                              uint32_t* sig_local, uint32_t sig_value, SigOp op, int pe) {
+  putmem(c, dst_local, src, nbytes, pe);
+  fence_acq_rel_sys();
+  signal_op(c, sig_local, sig_value, op, pe);
+}
+__device__ __forceinline__ void putmem_signal_nbi_block(const SymmCtx& c, void* dst_local, const void* src, size_t nbytes,
+                                                        uint32_t* sig_local, uint32_t sig_value, SigOp op, int pe) {
+  putmem_signal_block(c, dst_local, src, nbytes, sig_local, sig_value, op, pe);
+}
+
+// barrier_all executed by ONE warp per rank (lane k < world talks to peer k). Same flag protocol as
+// barrier_all_block; `flags` must not be shared with a concurrent block-level barrier.
+__device__ __forceinline__ bool barrier_all_warp(const SymmCtx& c, uint32_t* flags, uint32_t epoch) {
+  __syncwarp();
+  const int l = lane_id();
+  bool ok = true;
+  if (l < c.world) {
+    fence_acq_rel_sys();
+    st_release_sys(symm_at(c, flags + c.rank, l), epoch);
+    ok = wait_flag<WaitCmp::GE, true>(c, flags + l, epoch, l, __LINE__);
+    if (!ok) report_status(c, kStatusBarrierTimeout, l, epoch, 0, __LINE__);
+  }
+  return __all_sync(0xffffffffu, ok);
+}
+// sync_all: the barrier without the guarantee that earlier puts have completed (NVSHMEM's distinction). Stores here
+// are ordinary memory operations that the release in the flag store already orders, so the two coincide.
+__device__ __forceinline__ bool sync_all_block(const SymmCtx& c, uint32_t* flags, uint32_t epoch) { return barrier_all_block(c, flags, epoch); }
+__device__ __forceinline__ bool sync_all_warp(const SymmCtx& c, uint32_t* flags, uint32_t epoch) { return barrier_all_warp(c, flags, epoch); }
+
+// broadcast: `root` writes nbytes of `src` into `dst_local` of every rank (its own included). With an NVLS mapping
+// one multimem.st per 16 bytes reaches all ranks through the switch; otherwise one store per peer. The caller
+// synchronises before the data is read (barrier_all_block / a signal), as with NVSHMEM's collective.
+// nbytes, dst and src 16-byte aligned.
+__device__ __forceinline__ void broadcast_block(const SymmCtx& c, void* dst_local, const void* src, size_t nbytes, int root) {
+  if (c.rank != root) return;
+  const int tid = flat_tid(), nth = blockDim.x * blockDim.y * blockDim.z;
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+  uint4* d = reinterpret_cast<uint4*>(dst_local);
+  for (size_t i = tid; i < nbytes / 16; i += nth) {
+    const uint4 v = s[i];
+    if (c.mc_base != 0) {
+      multimem_st_v4(mc_ptr(c, d + i), v);
+    } else {
+      for (int k = 0; k < c.world; ++k) st_v4_relaxed_sys(symm_at(c, d + i, k), v);
+    }
+  }
+}
+__device__ __forceinline__ void broadcast_warp(const SymmCtx& c, void* dst_local, const void* src, size_t nbytes, int root) {
+  if (c.rank != root) return;
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+  uint4* d = reinterpret_cast<uint4*>(dst_local);
+  for (size_t i = lane_id(); i < nbytes / 16; i += 32) {
+    const uint4 v = s[i];
+    if (c.mc_base != 0) {
+      multimem_st_v4(mc_ptr(c, d + i), v);
+    } else {
+      for (int k = 0; k < c.world; ++k) st_v4_relaxed_sys(symm_at(c, d + i, k), v);
+    }
+  }
+}
+// fcollect (all-gather): every rank writes its nbytes of `src` into slot `rank` of `dst_local` ([world][nbytes]) on
+// every rank. Same synchronisation contract as broadcast.
+__device__ __forceinline__ void fcollect_block(const SymmCtx& c, void* dst_local, const void* src, size_t nbytes) {
+  const int tid = flat_tid(), nth = blockDim.x * blockDim.y * blockDim.z;
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+  uint4* d = reinterpret_cast<uint4*>(static_cast<uint8_t*>(dst_local) + static_cast<size_t>(c.rank) * nbytes);
+  for (size_t i = tid; i < nbytes / 16; i += nth) {
+    const uint4 v = s[i];
+    if (c.mc_base != 0) {
+      multimem_st_v4(mc_ptr(c, d + i), v);
+    } else {
+      for (int k = 0; k < c.world; ++k) st_v4_relaxed_sys(symm_at(c, d + i, k), v);
+    }
+  }
+}
+__device__ __forceinline__ void fcollect_warp(const SymmCtx& c, void* dst_local, const void* src, size_t nbytes) {
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+  uint4* d = reinterpret_cast<uint4*>(static_cast<uint8_t*>(dst_local) + static_cast<size_t>(c.rank) * nbytes);
+  for (size_t i = lane_id(); i < nbytes / 16; i += 32) {
+    const uint4 v = s[i];
+    if (c.mc_base != 0) {
+      multimem_st_v4(mc_ptr(c, d + i), v);
+    } else {
+      for (int k = 0; k < c.world; ++k) st_v4_relaxed_sys(symm_at(c, d + i, k), v);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
 // LL (low-latency) packets: 8 bytes = {data32, flag32}; the receiver polls the payload itself.
 // (python/triton_dist/kernels/nvidia/low_latency_allgather.py:530-566)
 // ----------------------------------------------------------------------------------------------
@@ -426,7 +565,10 @@ __device__ __forceinline__ bool ll_load(const SymmCtx& c, const uint64_t* src, u
       *data = static_cast<uint32_t>(v);
       return true;
     }
-    if ((++spins & 63u) == 0u) {
+    // back off once the packet is clearly not there yet: tens of thousands of threads re-reading their packet lines at
+    // system scope otherwise compete in L2 with the very stores they are waiting for
+    if (++spins > 4u) __nanosleep(spins > 32u ? 200u : 40u);
+    if ((spins & 63u) == 0u) {
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
       if (now - t0 > c.timeout_ns) {

@@ -99,7 +99,8 @@ __global__ void __launch_bounds__(kLLThreads) allreduce_ll_kernel(const ArLLPara
 #pragma unroll
           for (int s = 0; s < kMaxRanks; ++s)
             if (((pending >> s) & 1u) && static_cast<uint32_t>(v[s] >> 32) == epoch) pending &= ~(1u << s);
-          if (pending != 0u && (++spins & 31u) == 0u) {
+          if (pending != 0u && ++spins > 4u) __nanosleep(40);
+          if (pending != 0u && (spins & 31u) == 0u) {
             const uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;
             if (now - t0 > ctx.timeout_ns) {

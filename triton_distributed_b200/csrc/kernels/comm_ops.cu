@@ -173,6 +173,35 @@ __global__ void multimem_probe_kernel(const SymmCtx ctx, float* buf, uint32_t n4
   if (threadIdx.x == 0) *ok_out = ok ? 1u : 0u;
 }
 
+// Collective micro-test of the SHMEM-style API. One CTA per rank. `bcast` [n4 * 4 floats], `coll` [world][n4 * 4 floats],
+// `ring` [n4 * 4 floats], `sig` u32[2], `word` int32[world] and `flags` u32[2][world] are symmetric; `src` is local.
+//   1. broadcast_block from `root`           -> bcast holds root's src on every rank
+//   2. fcollect_warp (warp 0)                -> coll[r] holds rank r's src
+//   3. putmem_signal_warp to rank + 1        -> ring holds rank - 1's src once sig[0] == epoch
+//   4. int_p of (epoch + rank) into word[rank] of every rank, then barrier_all_warp
+__global__ void shmem_api_probe_kernel(const SymmCtx ctx, const float* src, float* bcast, float* coll, float* ring,
+                                       uint32_t* sig, int32_t* word, uint32_t* flags, uint32_t n4, int root,
+                                       uint32_t epoch, uint32_t* ok_out) {
+  const size_t nbytes = static_cast<size_t>(n4) * 16;
+  bool ok = team_my_pe(ctx) == my_pe(ctx) && team_n_pes(ctx) == n_pes(ctx) && team_translate_pe(ctx, root) == root &&
+            remote_ptr(ctx, bcast, ctx.rank) == bcast;
+  broadcast_block(ctx, bcast, src, nbytes, root);
+  const int warp = threadIdx.x >> 5;
+  if (warp == 0) {
+    fcollect_warp(ctx, coll, src, nbytes);
+  } else if (warp == 1) {
+    putmem_signal_warp(ctx, ring, src, nbytes, sig, epoch, SigOp::SET, (ctx.rank + 1) % ctx.world);
+  } else if (warp == 2 && lane_id() < static_cast<uint32_t>(ctx.world)) {
+    int_p(ctx, word + ctx.rank, static_cast<int32_t>(epoch) + ctx.rank, lane_id());
+  }
+  // every put of this CTA is released by the barrier's fence + flag store; after it all ranks' data has landed
+  ok = barrier_all_block(ctx, flags, epoch) && ok;
+  if (warp == 3) ok = barrier_all_warp(ctx, flags + kMaxRanks, epoch) && ok;
+  if (warp == 1 && lane_id() == 0) ok = signal_wait_until(ctx, sig, WaitCmp::EQ, epoch) && ok;
+  ok = __syncthreads_and(ok);
+  if (threadIdx.x == 0) *ok_out = ok ? 1u : 0u;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -247,10 +276,9 @@ B200_API int b200_test_grid_barrier(const void* symm_ctx, void* counter, void* a
                                     uint32_t base_round, void* bad, void* stream) {
   LOAD_CTX(ctx);
   B200_REQUIRE(ctas >= 1 && ctas <= sm_count(), "grid barrier needs a co-resident grid (<= %d CTAs)", sm_count());
-  grid_barrier_kernel<<<ctas, 128, 0, static_cast<cudaStream_t>(stream)>>>(ctx, static_cast<uint32_t*>(counter),
-                                                                          static_cast<uint32_t*>(acc), rounds, base_round,
-                                                                          static_cast<uint32_t*>(bad));
-  B200_CHECK_CUDA(cudaGetLastError());
+  B200_CHECK_CUDA(launch_cooperative(grid_barrier_kernel, dim3(ctas), dim3(128), 0, static_cast<cudaStream_t>(stream), ctx,
+                                     static_cast<uint32_t*>(counter), static_cast<uint32_t*>(acc), rounds, base_round,
+                                     static_cast<uint32_t*>(bad)));
   return kOk;
 }
 B200_API int b200_test_multimem(const void* symm_ctx, void* buf, uint32_t n4, void* flags, uint32_t epoch, void* out,
@@ -261,6 +289,18 @@ B200_API int b200_test_multimem(const void* symm_ctx, void* buf, uint32_t n4, vo
                                                                          static_cast<uint32_t*>(flags), epoch,
                                                                          static_cast<float*>(out),
                                                                          static_cast<uint32_t*>(ok_out));
+  B200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+B200_API int b200_test_shmem_api(const void* symm_ctx, const void* src, void* bcast, void* coll, void* ring, void* sig,
+                                 void* word, void* flags, uint32_t n4, int root, uint32_t epoch, void* ok_out, void* stream) {
+  LOAD_CTX(ctx);
+  B200_REQUIRE(root >= 0 && root < ctx.world, "root (%d) out of range", root);
+  shmem_api_probe_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      ctx, static_cast<const float*>(src), static_cast<float*>(bcast), static_cast<float*>(coll), static_cast<float*>(ring),
+      static_cast<uint32_t*>(sig), static_cast<int32_t*>(word), static_cast<uint32_t*>(flags), n4, root, epoch,
+      static_cast<uint32_t*>(ok_out));
   B200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }

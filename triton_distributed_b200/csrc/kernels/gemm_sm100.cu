@@ -443,7 +443,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
                     nrows * row_bytes, ct);
         } else {
           if (ct == 0) {
-            bool ok = wait_flag<WaitCmp::EQ, true>(ctx, p.ready + src, epoch, src, __LINE__);
+            // at least this epoch: a peer that has finished this call may already have published the next one (its
+            // buffer of this call's parity stays intact until the call after that, which needs this rank's next shard)
+            bool ok = wait_flag<WaitCmp::GE, true>(ctx, p.ready + src, epoch, src, __LINE__);
             *bcast = ok ? 1u : 0u;
           }
           comm_bar();

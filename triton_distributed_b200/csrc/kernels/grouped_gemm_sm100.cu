@@ -226,7 +226,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
         if (step == 0) {
           from = static_cast<const uint8_t*>(p.a_local) + static_cast<size_t>(r0) * row_bytes;
         } else {
-          if (ct == 0) *bcast = wait_flag<WaitCmp::EQ, true>(ctx, p.ready + src, epoch, src, __LINE__) ? 1u : 0u;
+          // at least this epoch: a peer that has finished this call may already have published the next one (its
+          // buffer of this call's parity stays intact until the call after that, which needs this rank's next shard)
+          if (ct == 0) *bcast = wait_flag<WaitCmp::GE, true>(ctx, p.ready + src, epoch, src, __LINE__) ? 1u : 0u;
           gcomm_bar();
           const bool ok = *bcast != 0u;
           gcomm_bar();
@@ -486,6 +488,13 @@ static int launch_grouped_bn(const CUtensorMap& tw, const GroupedParams& p, cons
     B200_CHECK_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<kMode, kBN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          GTile<kBN>::kSmem));
     configured[dev & 63] = true;
+  }
+  if (kMode == kGRS) {
+    // this mode crosses a grid-wide barrier between the GEMM and the reduce-scatter: launched cooperatively, so the
+    // driver guarantees (or refuses) the co-residency the barrier needs
+    B200_CHECK_CUDA(launch_cooperative(grouped_gemm_kernel<kMode, kBN>, dim3(grid), dim3(kGThreads), GTile<kBN>::kSmem, stream,
+                                       tw, p, ctx));
+    return kOk;
   }
   grouped_gemm_kernel<kMode, kBN><<<grid, kGThreads, GTile<kBN>::kSmem, stream>>>(tw, p, ctx);
   B200_CHECK_CUDA(cudaGetLastError());

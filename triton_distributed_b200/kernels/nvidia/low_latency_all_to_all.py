@@ -68,9 +68,14 @@ def fast_all_to_all(ctx: AllToAllContext, send_tensor: torch.Tensor, send_split_
                     send_scale: torch.Tensor | None = None):
     """send_tensor [n, hidden] sorted by global expert; send_split_cumsum int32 [E + 1]; send_scale fp32 [n] or
     [n, scale_per_row]. Returns [recv_splits [world, E_local], recv_buf [world * max_m, hidden], recv_scale | None]
-    (views of the buffer half used by this call; valid until the call after next)."""
+    (views of the buffer half used by this call; valid until the call after next). A rank may send at most
+    ``ctx.max_m`` rows to one peer: rows beyond that are dropped by the kernel and reported through the heap's status
+    word (``SymmHeap.check_status`` raises), never written past the peer's receive area."""
     if not send_tensor.is_contiguous() or send_tensor.dtype != ctx.dtype or send_tensor.shape[1] != ctx.hidden:
         raise ValueError("send_tensor must be contiguous [n, hidden] in the context dtype")
+    if torch.cuda.is_current_stream_capturing():
+        raise RuntimeError("fast_all_to_all cannot be captured in a CUDA graph: the returned views name the buffer half "
+                           "of this call, which the host selects from its call counter")
     cum = send_split_cumsum.to(torch.int32).contiguous()
     ctx.calls += 1
     par = ctx.calls & 1

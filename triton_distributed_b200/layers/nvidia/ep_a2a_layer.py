@@ -61,6 +61,11 @@ class EPAll2AllLayer:
         T = input.shape[0]
         if T > self.max_tokens or exp_indices.shape != (T, self.topk):
             raise ValueError("batch does not fit the layer")
+        if torch.cuda.is_current_stream_capturing():
+            # the receive half is chosen on the host from a call counter; a replayed graph would keep the captured
+            # half while the device-side epoch moves on, and the consumers would read the stale one
+            raise RuntimeError("EPAll2AllLayer.dispatch cannot be captured in a CUDA graph: its double-buffer half is "
+                               "selected on the host per call")
         ids = exp_indices.to(torch.int32).contiguous()
         plan = self._plan(T)
         moe_sort(ids, plan)

@@ -31,7 +31,7 @@ from .kv_cache import KV_Cache
 from .utils import logger
 from .weights import RandomSource, SafetensorsSource, WeightSource
 
-_FUSED_DECODE = os.environ.get("B200DIST_FUSED_DECODE", "1") != "0"
+_FUSED_DECODE = os.environ.get("B200DIST_FUSED_DECODE", "1") != "0"   # single-GPU decode: epilogue-fused GEMMs
 
 
 class Qwen3Layer:
@@ -58,15 +58,8 @@ class Qwen3Layer:
             k_norm=src.get(p + "self_attn.k_norm.weight") if src.has(p + "self_attn.k_norm.weight") else None,
             num_heads=arch.num_attention_heads, num_kv_heads=arch.num_key_value_heads, eps=arch.rms_norm_eps)
         if arch.num_experts:
-            # MoE block: every expert's intermediate dimension is sharded over the ranks
-            Im = slice(rank * arch.moe_intermediate_size // world, (rank + 1) * arch.moe_intermediate_size // world)
-            self.mlp = TP_MoE(rank, world, self.attn.group, arch.num_experts_per_tok, arch.norm_topk_prob)
-            gu, dn = [], []
-            for e in range(arch.num_experts):
-                q = p + f"mlp.experts.{e}."
-                gu.append(torch.cat([src.get(q + "gate_proj.weight", rows=Im), src.get(q + "up_proj.weight", rows=Im)], dim=0))
-                dn.append(src.get(q + "down_proj.weight", cols=Im))
-            self.mlp._init_parameters(src.get(p + "mlp.gate.weight"), torch.stack(gu), torch.stack(dn))
+            from .qwen_moe import build_moe_block  # (imports this module, hence not at the top)
+            self.mlp = build_moe_block(src, p, arch, rank, world, self.attn.group)
         else:
             self.mlp._init_parameters(gate=src.get(p + "mlp.gate_proj.weight", rows=Is), up=src.get(p + "mlp.up_proj.weight", rows=Is),
                                       down=src.get(p + "mlp.down_proj.weight", cols=Is))

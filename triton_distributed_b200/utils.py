@@ -167,7 +167,7 @@ def flush_l2() -> None:
     _l2_flush_buf.zero_()
 
 
-def perf_func_cold(func: Callable, iters: int, warmup_iters: int, head_start_us: float = 200.0):
+def perf_func_cold(func: Callable, iters: int, warmup_iters: int, head_start_us: float = 500.0):
     """Like perf_func but with an L2 flush before every timed call; each call is timed separately.
     Returns (last output, mean ms, list of per-call ms).
 
