@@ -151,6 +151,7 @@ def _kernel_extras(args, group, world: int, budget_s: float = 120.0) -> dict:
     from triton_distributed_b200.benchmark import bench_comm_gemm as bg
 
     heap = utils.get_heap()
+    heap.set_timeout_ms(3000)  # a lost signal in one of these rows costs seconds, not the default ten per wait
     out: dict = {}
     t_start = time.time()
     a = types.SimpleNamespace(iters=args.kernel_iters, warmup=3, ar_max_bytes=args.ar_max_bytes, ep_tokens=128,

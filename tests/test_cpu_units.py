@@ -49,6 +49,7 @@ def test_ag_moe_schedule_orders_tiles_by_arrival_stage():
     for rank in range(world):
         gather, tile_expert, s0, s1, order = ref.ag_moe_tile_schedule_ref(ids, E, bm, rank, world)
         stage = (s1.long() - rank) % world
+        stage = torch.where((s0.long() - rank) % world > stage, torch.full_like(stage, world - 1), stage)
         assert torch.all(stage[order.long()][1:] >= stage[order.long()][:-1])
         assert sorted(order.tolist()) == list(range(tile_expert.numel()))
         per = T // world
@@ -131,10 +132,12 @@ def test_allreduce_method_names_and_auto_choice():
     assert to_allreduce_method("two_shot_multimem") is AllReduceMethod.TwoShot_Multimem
     with pytest.raises(ValueError):
         to_allreduce_method("ring")
-    assert get_auto_allreduce_method(8 << 10, has_multicast=True) is AllReduceMethod.OneShot_Multimem
-    assert get_auto_allreduce_method(8 << 20, has_multicast=True) is AllReduceMethod.TwoShot_Multimem
-    assert get_auto_allreduce_method(8 << 10, has_multicast=False) is AllReduceMethod.OneShot
-    assert get_auto_allreduce_method(8 << 20, has_multicast=False) is AllReduceMethod.TwoShot
+    assert get_auto_allreduce_method(8 << 10, has_multicast=True, world=8) is AllReduceMethod.OneShot
+    assert get_auto_allreduce_method(8 << 20, has_multicast=True, world=8) is AllReduceMethod.TwoShot_Multimem
+    assert get_auto_allreduce_method(8 << 20, has_multicast=True, world=2) is AllReduceMethod.OneShot   # same bytes as two-shot
+    assert get_auto_allreduce_method(32 << 20, has_multicast=True, world=2) is AllReduceMethod.TwoShot
+    assert get_auto_allreduce_method(8 << 10, has_multicast=False, world=8) is AllReduceMethod.OneShot
+    assert get_auto_allreduce_method(8 << 20, has_multicast=False, world=8) is AllReduceMethod.TwoShot
 
 
 def test_trace_merge_and_helpers(capsys):
@@ -268,7 +271,8 @@ def test_allreduce_method_resolution_and_split_heuristics():
     assert ar._resolve(AllReduceMethod.TwoShot, 1 << 24, ctx(False)) == 1
     assert ar._resolve(AllReduceMethod.DoubleTree, 1 << 10, ctx(False)) == 0      # small: one-shot
     assert ar._resolve(AllReduceMethod.DoubleTree, 1 << 24, ctx(False)) == 1      # large: two-shot
-    assert ar._resolve(None, 1 << 10, ctx(True)) == 2 and ar._resolve(None, 1 << 24, ctx(True)) == 3
+    assert ar._resolve(None, 1 << 10, ctx(True)) == 0 and ar._resolve(None, 1 << 24, ctx(True)) == 3      # one-shot push, NVLS two-shot
+    assert ar._resolve(None, 1 << 20, ctx(True)) == 0 and ar._resolve(None, (1 << 20) + 16, ctx(True)) == 3
     assert ar._resolve(None, 1 << 10, ctx(False)) == 0 and ar._resolve(None, 1 << 24, ctx(False)) == 1
     with pytest.raises(RuntimeError):
         ar._resolve(AllReduceMethod.TwoShot_Multimem, 1 << 20, ctx(False))

@@ -236,13 +236,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
           from = symm_at(ctx, buf + off, src);
         }
         const size_t nvec = nrows * row_bytes / 16;
-        for (size_t i = ct; i < nvec; i += 64 * 4) {
-          uint4 v[4];
+        // eight 16-byte loads in flight per lane: ~1.2 MB per GPU, what a 2 us NVLink round trip needs at link speed
+        for (size_t i = ct; i < nvec; i += 64 * 8) {
+          uint4 v[8];
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
+          for (int u = 0; u < 8; ++u)
             if (i + u * 64 < nvec) v[u] = ld_v4_relaxed_sys(reinterpret_cast<const uint4*>(from) + i + u * 64);
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
+          for (int u = 0; u < 8; ++u)
             if (i + u * 64 < nvec) st_v4(reinterpret_cast<uint4*>(buf + off) + i + u * 64, v[u]);
         }
         gcomm_bar();
@@ -332,9 +333,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
         const int pair = p.sorted_ids[tile * kGM + rbase + 16 * i];
         const bool valid = pair < p.n_pairs;
         const int src_row = valid ? pair / p.a_div : 0;
+        bool local_row = false;
         if (kMode == kGAG && valid && ok) {
           const int src = src_row / p.Tr;
-          if (src != last_src) {
+          // this rank's own tokens are read where the caller put them: no copy, no flag, so the tiles that need only
+          // local rows start at once (the copy into the symmetric buffer is for the peers only)
+          local_row = src == ctx.rank && !p.push;
+          if (!local_row && src != last_src) {
             // a shard that any thread of this CTA has seen complete is not polled in global memory again
             uint32_t seen;
             asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(seen) : "r"(smem_u32(ready_cache + src)) : "memory");
@@ -350,7 +355,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
             last_src = src;
           }
         }
-        rp[i] = valid ? a_base + (static_cast<size_t>(src_row) * p.lda + chunk * 8) * 2 : nullptr;
+        if (local_row)
+          rp[i] = static_cast<const uint8_t*>(p.a_local) + (static_cast<size_t>(src_row - ctx.rank * p.Tr) * p.lda + chunk * 8) * 2;
+        else
+          rp[i] = valid ? a_base + (static_cast<size_t>(src_row) * p.lda + chunk * 8) * 2 : nullptr;
       }
       if (!ok) *abort_flag = 1;
       for (int kb = 0; kb < num_kb && ok; ++kb) {

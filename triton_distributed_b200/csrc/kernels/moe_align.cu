@@ -10,7 +10,8 @@
 //                3. offsets  one CTA: padded group sizes scanned into group offsets; tile table and pad rows
 //                4. scatter  one CTA per chunk: position = group offset + chunk prefix + rank inside the chunk
 //                Stable, deterministic, E <= 1024.
-//   moe_tile_order  counting sort of the tiles by arrival stage ((seg_end - rank - shift) mod world), stable.
+//   moe_tile_order  counting sort of the tiles by arrival stage (ring step after which every source shard of the tile
+//                   has landed), stable.
 //
 // Role in the reference: csrc/lib/moe_utils.cu:60-353 (moe_ag_scatter_align_block_size, grid 1 or ranks CTAs,
 // cudaMalloc + cudaDeviceSynchronize per call), kernels/nvidia/moe_utils.py:142-248 (single-CTA index kernel),
@@ -280,8 +281,11 @@ __global__ void __launch_bounds__(1024) moe_sort_small_kernel(const MoeSortParam
 }
 
 // Stable counting sort of the tiles by stage; one CTA. order[j] = tile issued j-th.
-__global__ void __launch_bounds__(1024) moe_tile_order_kernel(const int32_t* tile_seg_end, const int32_t* totals, int rank,
-                                                              int world, int shift, int32_t* order) {
+// The stage of a tile is the ring step (starting at `rank`) after which ALL of its source shards have arrived: a tile
+// whose sources seg_start..seg_end run past rank - 1 holds a row of the last shard to arrive.
+__global__ void __launch_bounds__(1024) moe_tile_order_kernel(const int32_t* tile_seg_start, const int32_t* tile_seg_end,
+                                                              const int32_t* totals, int rank, int world, int shift,
+                                                              int32_t* order) {
   __shared__ int warp_sums[32];
   __shared__ int base;
   const int n = totals[1];
@@ -295,6 +299,11 @@ __global__ void __launch_bounds__(1024) moe_tile_order_kernel(const int32_t* til
       if (t < n) {
         int st = (tile_seg_end[t] - rank - shift) % world;
         if (st < 0) st += world;
+        if (tile_seg_start != nullptr) {
+          int first = (tile_seg_start[t] - rank - shift) % world;
+          if (first < 0) first += world;
+          if (first > st) st = world - 1;  // the range wraps around this rank
+        }
         hit = st == s;
       }
       const uint32_t m = __ballot_sync(0xffffffffu, hit);
@@ -384,10 +393,10 @@ B200_API int b200_moe_sort(const int32_t* ids, int n_pairs, int topk, int num_ex
   return kOk;
 }
 
-B200_API int b200_moe_tile_order(const int32_t* tile_seg_end, const int32_t* totals, int rank, int world, int shift,
+B200_API int b200_moe_tile_order(const int32_t* tile_seg_start, const int32_t* tile_seg_end, const int32_t* totals, int rank, int world, int shift,
                                  int32_t* order, void* stream) {
   B200_REQUIRE(world >= 1 && world <= kMaxRanks, "world (%d) out of range", world);
-  moe_tile_order_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(tile_seg_end, totals, rank, world, shift, order);
+  moe_tile_order_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(tile_seg_start, tile_seg_end, totals, rank, world, shift, order);
   B200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }

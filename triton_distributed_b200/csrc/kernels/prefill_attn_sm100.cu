@@ -41,6 +41,13 @@ struct PrefillParams {
   uint32_t* status;     // nullable: set non-zero when a pipeline wait expired
 };
 
+// 2^x on the special-function unit (one instruction; -inf gives 0, which is what a masked score must contribute)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // V [total_k, Hkv, 128] -> Vt [B * Hkv, 128, s_pad] (keys contiguous, zero beyond each sequence's length)
 __global__ void __launch_bounds__(256) transpose_v_kernel(const uint16_t* __restrict__ v, uint16_t* __restrict__ vt,
                                                           const int* __restrict__ cu_k, const int* __restrict__ k_lens,
@@ -219,23 +226,26 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_after_sync();
       const uint32_t s_addr = lane_base + st * kPN;
       const int key0 = j * kPN;
-      // ---- pass 1: row maximum of the scaled, masked scores
+      // ---- pass 1: row maximum of the masked scores (raw; the positive scale is applied to the maximum once)
+      // keys up to `visible` (exclusive) are unmasked for this row: only the diagonal and the last tile ever mask
+      const int visible = min(limit + 1, k_len) - key0;
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < kPN / 16; ++c) {
-        uint32_t r[16];
-        tmem_ld_32x16(s_addr + c * 16, r);
+      for (int c = 0; c < kPN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(s_addr + c * 32, r);
         tmem_ld_wait();
+        if (visible >= (c + 1) * 32) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int key = key0 + c * 16 + i;
-          const float v = (key <= limit && key < k_len) ? __uint_as_float(r[i]) * p.scale_log2e : -INFINITY;
-          mx = fmaxf(mx, v);
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, c * 32 + i < visible ? __uint_as_float(r[i]) : -INFINITY);
         }
       }
-      const float m_new = fmaxf(m_run, mx);
+      const float m_new = fmaxf(m_run, mx * p.scale_log2e);
       const float base = m_new == -INFINITY ? 0.f : m_new;
-      const float corr = exp2f(m_run - base);  // m_run == -inf -> 0
+      const float corr = fast_exp2(m_run - base);  // m_run == -inf -> 0
       // ---- the previous step's P V has finished (which also frees the P tile): fold it into the registers
       if (j > 0 && !accumulate_o(j - 1)) { ok = false; break; }
       // ---- pass 2: probabilities, row sum, P tile (A operand of the second MMA: K-major, 128-byte swizzle)
@@ -246,12 +256,16 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_ld_32x16(s_addr + c * 16, r);
         tmem_ld_wait();
         uint32_t packed[8];
+        const bool all_visible = visible >= (c + 1) * 16;
 #pragma unroll
         for (int i = 0; i < 16; i += 2) {
-          const int key = key0 + c * 16 + i;
-          const float v0 = (key <= limit && key < k_len) ? __uint_as_float(r[i]) * p.scale_log2e : -INFINITY;
-          const float v1 = (key + 1 <= limit && key + 1 < k_len) ? __uint_as_float(r[i + 1]) * p.scale_log2e : -INFINITY;
-          const float p0 = exp2f(v0 - base), p1 = exp2f(v1 - base);
+          // 2^(s * scale - base) as one fused multiply-add and one special-function instruction per score
+          float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2e, -base));
+          float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2e, -base));
+          if (!all_visible) {
+            p0 = c * 16 + i < visible ? p0 : 0.f;
+            p1 = c * 16 + i + 1 < visible ? p1 : 0.f;
+          }
           sum += p0 + p1;
           packed[i >> 1] = p.bf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
         }

@@ -88,18 +88,24 @@ def create_allreduce_ctx(workspace_nbytes: int, rank: int, world_size: int, loca
     return ctx
 
 
-def get_auto_allreduce_method(nbytes: int, has_multicast: bool | None = None) -> AllReduceMethod:
-    """Small messages are latency-bound (one-shot), large ones bandwidth-bound (two-shot); NVLS when bound."""
+def get_auto_allreduce_method(nbytes: int, has_multicast: bool | None = None, world: int | None = None) -> AllReduceMethod:
+    """Small messages are latency-bound: the one-shot push (one meeting point) wins up to 1 MB at eight ranks and up to
+    8 MB at two, where it moves no more data than a two-shot. Beyond that the two-shot forms are bandwidth-bound, with
+    the reduction in the switch when the heap has an NVLS mapping and more than two ranks share it. (Measured at 2 and
+    8 GPUs; the NVLS one-shot never beat the plain one-shot on this machine.)"""
+    heap = get_heap() if (has_multicast is None or world is None) else None
     if has_multicast is None:
-        has_multicast = get_heap().has_multicast
-    if has_multicast:
-        return AllReduceMethod.TwoShot_Multimem if nbytes > 64 * 1024 else AllReduceMethod.OneShot_Multimem
-    return AllReduceMethod.TwoShot if nbytes > 256 * 1024 else AllReduceMethod.OneShot
+        has_multicast = heap.has_multicast
+    if world is None:
+        world = heap.world
+    if nbytes <= (8 << 20 if world <= 2 else 1 << 20):
+        return AllReduceMethod.OneShot
+    return AllReduceMethod.TwoShot_Multimem if (has_multicast and world > 2) else AllReduceMethod.TwoShot
 
 
 def _resolve(method: AllReduceMethod | None, nbytes: int, ctx: AllReduceContext) -> int:
     if method is None or method == AllReduceMethod.Unknown:
-        method = get_auto_allreduce_method(nbytes, ctx.heap.has_multicast)
+        method = get_auto_allreduce_method(nbytes, ctx.heap.has_multicast, ctx.world_size)
     if method == AllReduceMethod.DoubleTree:
         method = AllReduceMethod.OneShot if nbytes <= 64 * 1024 else AllReduceMethod.TwoShot
     if method in (AllReduceMethod.OneShot_Multimem, AllReduceMethod.TwoShot_Multimem,

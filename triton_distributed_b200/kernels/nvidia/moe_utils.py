@@ -75,8 +75,9 @@ def moe_sort(topk_ids: torch.Tensor, plan: MoeSortPlan, tokens_per_rank: int | N
 
 
 def order_tiles(plan: MoeSortPlan, rank: int, world: int, shift: int = 0) -> torch.Tensor:
-    """Issue order of the tiles by arrival stage ``(seg_end - rank - shift) mod world`` (stable)."""
-    _lib.call("b200_moe_tile_order", ptr(plan.tile_seg_end), ptr(plan.totals), rank, world, shift, ptr(plan.tile_order),
+    """Issue order of the tiles by arrival stage (stable): the ring step, starting at ``rank + shift``, after which every
+    source shard seg_start..seg_end of the tile has arrived."""
+    _lib.call("b200_moe_tile_order", ptr(plan.tile_seg_start), ptr(plan.tile_seg_end), ptr(plan.totals), rank, world, shift, ptr(plan.tile_order),
               stream_ptr())
     ops._count()
     return plan.tile_order

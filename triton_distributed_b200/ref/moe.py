@@ -87,8 +87,9 @@ def moe_align_block_size_ref(topk_ids: torch.Tensor, num_experts: int, block_m: 
 
 def ag_moe_tile_schedule_ref(topk_ids: torch.Tensor, num_experts: int, block_m: int, rank: int, world: int):
     """AG+MoE metadata: pairs sorted by expert (stable, so by source rank inside an expert), runs padded to `block_m`.
-    A tile needs the token shards of ranks seg_start..seg_end; its stage is ``(seg_end - rank) mod world``: the
-    step of a ring starting at `rank` after which all its rows have arrived. Tiles are issued stage-major, in their
+    A tile needs the token shards of ranks seg_start..seg_end; its stage is the step of a ring starting at `rank` after
+    which all of them have arrived: ``(seg_end - rank) mod world``, or ``world - 1`` when the range runs past
+    ``rank - 1`` (the last shard to arrive). Tiles are issued stage-major, in their
     original (expert-major) order inside a stage.
 
     Returns (gather_index [M_pad], tile_expert [tiles], tile_seg_start, tile_seg_end, tile_order [tiles])."""
@@ -101,6 +102,7 @@ def ag_moe_tile_schedule_ref(topk_ids: torch.Tensor, num_experts: int, block_m: 
     seg_end = src.max(dim=1).values
     seg_start = torch.where(valid, src, torch.full_like(src, world)).min(dim=1).values
     stage = (seg_end - rank) % world
+    stage = torch.where((seg_start - rank) % world > stage, torch.full_like(stage, world - 1), stage)
     order = torch.argsort(stage, stable=True)
     dev = topk_ids.device
     return (gather, expert_index, seg_start.to(torch.int32).to(dev), seg_end.to(torch.int32).to(dev),

