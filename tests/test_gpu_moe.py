@@ -175,3 +175,22 @@ def test_ep_moe_layer_world1(dist1, fp8, fp8_experts):
         get_heap().check_status("ep_moe")
         torch.testing.assert_close(got.float(), want.float(), rtol=0.12 if fp8 else 5e-2, atol=0.3 if fp8 else 0.1)
     ep.finalize()
+
+
+@pytest.mark.parametrize("T,I", [(5, 128), (300, 384), (4096, 1536)])
+def test_silu_mul_fp8_matches_gate_then_block_quant(T, I):
+    """The fused SwiGLU + e4m3 block quantisation against silu_mul followed by the PyTorch quantiser: scales agree to
+    rounding, and the dequantised values agree within one e4m3 step."""
+    from triton_distributed_b200 import ops
+    from triton_distributed_b200.kernels.nvidia import quantize_fp8_rows
+    torch.manual_seed(14)
+    x = torch.randn(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+    q, s = ops.silu_mul_fp8(x)
+    xf = x.float()
+    act = torch.nn.functional.silu(xf[:, :I]) * xf[:, I:]
+    q_ref, s_ref = quantize_fp8_rows(act)
+    torch.testing.assert_close(s, s_ref, rtol=1e-4, atol=1e-8)
+    deq = (q.float().view(T, I // 128, 128) * s[:, :, None]).view(T, I)
+    torch.testing.assert_close(deq, act, rtol=0.07, atol=1e-3)
+    deq_ref = (q_ref.float().view(T, I // 128, 128) * s_ref[:, :, None]).view(T, I)
+    assert (deq - deq_ref).abs().max() <= 0.07 * act.abs().max()

@@ -13,6 +13,7 @@
 #include "b200/primitives.cuh"
 
 #include <cstring>
+#include <cuda_fp8.h>
 
 namespace b200 {
 
@@ -171,6 +172,54 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const uint4* __restrict__
 #pragma unroll
     for (int e = 0; e < 8; ++e) o[e] = g[e] / (1.f + __expf(-g[e])) * u[e];
     out[idx] = pack8<BF16>(o);
+  }
+}
+
+// SwiGLU gate fused with the block quantisation of its result: out8[t, i] = e4m3(silu(x[t, i]) * x[t, inter + i] / s) with
+// one fp32 scale s = amax / 448 per 128 channels (the activation format of the block-scaled fp8 grouped GEMM), so the
+// down-projection of an fp8 expert reads a quarter of the bytes a bf16 intermediate would cost. One half-warp owns a
+// 128-channel block (a lane holds 8 channels), as in the dispatch kernel of ep_a2a.cu.
+template <bool BF16>
+__global__ void __launch_bounds__(256) silu_mul_fp8_kernel(const uint4* __restrict__ x, uint2* __restrict__ out8,
+                                                           float* __restrict__ out_scale, int T, int inter, int ldx) {
+  griddep_launch_dependents();
+  griddep_wait();
+  const int nblk = inter / 128;
+  const int lane = threadIdx.x & 31, hl = lane & 15;
+  const long long half_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
+  const long long n_half = (static_cast<long long>(gridDim.x) * blockDim.x) >> 4;
+  const long long total = static_cast<long long>(T) * nblk;
+  // every lane runs the same number of iterations (the shuffles below need the whole warp): round the bound up to
+  // whole warps of work and predicate the memory accesses instead
+  const long long rounds = (total + n_half - 1) / n_half;
+  for (long long r = 0; r < rounds; ++r) {
+    const long long w = half_id + r * n_half;
+    const bool in = w < total;
+    const int t = in ? static_cast<int>(w / nblk) : 0, blk = in ? static_cast<int>(w - static_cast<long long>(t) * nblk) : 0;
+    float g[8], u[8], o[8];
+    const size_t base = static_cast<size_t>(t) * (ldx / 8) + static_cast<size_t>(blk) * 16 + hl;
+    unpack8<BF16>(in ? x[base] : make_uint4(0, 0, 0, 0), g);
+    unpack8<BF16>(in ? x[base + inter / 8] : make_uint4(0, 0, 0, 0), u);
+    float amax = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      o[e] = g[e] / (1.f + __expf(-g[e])) * u[e];
+      amax = fmaxf(amax, fabsf(o[e]));
+    }
+#pragma unroll
+    for (int s = 8; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+    const float scale = amax / 448.f;
+    const float den = scale > 0.f ? scale : 1.f;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      lo |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(__fdiv_rn(o[q], den), __NV_SATFINITE, __NV_E4M3)) << (8 * q);
+      hi |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(__fdiv_rn(o[4 + q], den), __NV_SATFINITE, __NV_E4M3)) << (8 * q);
+    }
+    if (in) {
+      out8[(static_cast<size_t>(t) * inter + static_cast<size_t>(blk) * 128) / 8 + hl] = make_uint2(lo, hi);
+      if (hl == 0) out_scale[static_cast<size_t>(t) * nblk + blk] = scale;
+    }
   }
 }
 
@@ -364,6 +413,22 @@ B200_API int b200_silu_mul(const void* x, void* out, int T, int inter, int ldx, 
   else
     B200_CHECK_CUDA(launch_pdl(silu_mul_kernel<false>, grid, 256, 0, s, static_cast<const uint4*>(x), static_cast<uint4*>(out), T, inter, ldx));
   B200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+// x [T, 2 * inter] (row pitch ldx elements, gate | up); out8 e4m3 [T, inter]; out_scale fp32 [T, inter / 128].
+B200_API int b200_silu_mul_fp8(const void* x, void* out8, float* out_scale, int T, int inter, int ldx, int dtype, void* stream) {
+  B200_REQUIRE(dtype == kBF16 || dtype == kF16, "silu_mul_fp8 reads bf16 / f16");
+  B200_REQUIRE(inter % 128 == 0 && ldx % 8 == 0, "the intermediate size (%d) must be a multiple of 128", inter);
+  if (T == 0) return kOk;
+  const long long halves = static_cast<long long>(T) * (inter / 128);
+  const long long blocks = (halves * 16 + 255) / 256;
+  const int grid = static_cast<int>(blocks < 8LL * sm_count() ? blocks : 8LL * sm_count());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == kBF16)
+    B200_CHECK_CUDA(launch_pdl(silu_mul_fp8_kernel<true>, grid, 256, 0, s, static_cast<const uint4*>(x), static_cast<uint2*>(out8), out_scale, T, inter, ldx));
+  else
+    B200_CHECK_CUDA(launch_pdl(silu_mul_fp8_kernel<false>, grid, 256, 0, s, static_cast<const uint4*>(x), static_cast<uint2*>(out8), out_scale, T, inter, ldx));
   return kOk;
 }
 

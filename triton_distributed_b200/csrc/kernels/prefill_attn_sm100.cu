@@ -6,10 +6,10 @@
 //   warp 0     TMA producer: the Q tile once, then K and V^T tiles through two-stage rings (128-byte swizzle)
 //   warp 1     one elected thread issues tcgen05.mma: S = Q K^T into one of two 128-column TMEM buffers (so the
 //              scores of step j + 1 are computed while step j is in the softmax), then O_step = P V into a third
-//   warps 4-7  softmax, one thread per query row (row max and sum need no shuffles): read S twice from TMEM (max, then
-//              exp2), write P as 16-bit into a swizzled shared-memory tile that is the A operand of the second MMA,
-//              and keep the running output row in 128 fp32 registers: O = O * exp2(m_old - m_new) + O_step, so tensor
-//              memory never has to be rescaled
+//   warps 4-11 softmax, two threads per query row (each owns 64 of the 128 score / output columns; the row maximum is
+//              exchanged through shared memory): read S twice from TMEM (max, then exp2), write P as 16-bit into a
+//              swizzled shared-memory tile that is the A operand of the second MMA, and keep the running output row
+//              in 2 x 64 fp32 registers: O = O * exp2(m_old - m_new) + O_step, so tensor memory never has to be rescaled
 // V is the B operand of the second MMA and has to be K-major ([d, keys]); a small kernel transposes it once per call
 // into a zero-padded [batch x kv head, 128, padded keys] buffer, O(S d) work against the O(S^2 d) of the attention.
 // Every barrier wait is bounded; on expiry the CTA unwinds through an abort flag and reports a status.
@@ -28,8 +28,8 @@ constexpr int kPD = 128;                    // head dim
 constexpr int kPM = 128, kPN = 128;         // query rows per CTA, keys per step
 constexpr int kPAtom = 128 * 64 * 2;        // one 128-row x 64-column 16-bit swizzle atom: 16 KB
 constexpr int kPTile = 2 * kPAtom;          // a 128 x 128 tile: 32 KB
-constexpr int kPSmem = kPTile /*Q*/ + 2 * kPTile /*K*/ + 2 * kPTile /*V^T*/ + kPTile /*P*/ + 1024 + 256;
-constexpr int kPThreads = 256;
+constexpr int kPSmem = kPTile /*Q*/ + 2 * kPTile /*K*/ + 2 * kPTile /*V^T*/ + kPTile /*P*/ + 1024 + 256 + 3072 /*max / sum exchange*/;
+constexpr int kPThreads = 384;
 
 struct PrefillParams {
   int Hq, Hkv, causal, bf16;
@@ -47,6 +47,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+
+// barrier of the 256 softmax threads (warps 4-11) only
+__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // V [total_k, Hkv, 128] -> Vt [B * Hkv, 128, s_pad] (keys contiguous, zero beyond each sequence's length)
 __global__ void __launch_bounds__(256) transpose_v_kernel(const uint16_t* __restrict__ v, uint16_t* __restrict__ vt,
@@ -100,6 +103,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* o_empty = bars + 15;    // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  float* xmax = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);  // [2 step parities][2 halves][128 rows]
+  float* xsum = xmax + 4 * kPM;                                                    // [2 halves][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint64_t timeout_ns = 4000000000ull;
@@ -112,11 +117,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(v_full + i, 1);
       mbar_init(v_empty + i, 1);
       mbar_init(s_full + i, 1);
-      mbar_init(s_empty + i, 4);
+      mbar_init(s_empty + i, 8);
     }
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
     mbar_init(o_full, 1);
-    mbar_init(o_empty, 4);
+    mbar_init(o_empty, 8);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -191,28 +196,34 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     __syncwarp();
   } else if (warp >= 4) {
-    // ------------------------------------------------------------------ softmax + output accumulation, one row per thread
-    const int w4 = warp - 4;  // == warp % 4: the TMEM lane quarter this warp may read
+    // ------------------------------------------------------------------ softmax + output accumulation
+    // Two threads per query row: warps 4-7 own score / output columns [0, 64) of the 128-wide tile, warps 8-11 columns
+    // [64, 128) (two warps per scheduler instead of one, and half the serial chain per thread). The halves exchange
+    // their row maxima through shared memory once per step and their row sums once at the end.
+    const int sw = warp - 4;
+    const int w4 = sw & 3;    // == warp % 4: the TMEM lane quarter this warp may read
+    const int half = sw >> 2;
+    const int col0 = half * 64;
     const int row = w4 * 32 + lane;
     const int q_pos = m_blk * kPM + row;
     const int limit = p.causal ? q_pos + offset : k_len - 1;  // last key this row may attend
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(w4 * 32) << 16);
     float m_run = -INFINITY, l_run = 0.f, corr_prev = 1.f;
-    float o[kPD];
+    float o[64];
 #pragma unroll
-    for (int i = 0; i < kPD; ++i) o[i] = 0.f;
+    for (int i = 0; i < 64; ++i) o[i] = 0.f;
     bool ok = true;
 
     auto accumulate_o = [&](int j) -> bool {  // O = O * corr(j) + O_step(j), once the second MMA of step j has finished
-      if (!mbar_wait(o_full, j & 1, abort_flag, timeout_ns)) return false;
+      if (!__all_sync(0xffffffffu, mbar_wait(o_full, j & 1, abort_flag, timeout_ns))) return false;
       tc_fence_after_sync();
 #pragma unroll
-      for (int c = 0; c < kPD / 16; ++c) {
-        uint32_t r[16];
-        tmem_ld_32x16(lane_base + 2 * kPN + c * 16, r);
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(lane_base + 2 * kPN + col0 + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) o[c * 16 + i] = fmaf(o[c * 16 + i], corr_prev, __uint_as_float(r[i]));
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], corr_prev, __uint_as_float(r[i]));
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -220,38 +231,48 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       return true;
     };
 
-    for (int j = 0; j < n_steps && ok; ++j) {
+    // Every softmax thread runs all n_steps iterations and meets its partner at the barrier of every step, also after
+    // a pipeline wait has failed (then it skips the work and the waits): the barrier count stays the same for all.
+    for (int j = 0; j < n_steps; ++j) {
       const int st = j & 1;
-      if (!mbar_wait(s_full + st, (j >> 1) & 1, abort_flag, timeout_ns)) { ok = false; break; }
+      if (ok) ok = mbar_wait(s_full + st, (j >> 1) & 1, abort_flag, timeout_ns);
+      ok = __all_sync(0xffffffffu, ok);  // the TMEM loads below need the whole warp
       tc_fence_after_sync();
-      const uint32_t s_addr = lane_base + st * kPN;
-      const int key0 = j * kPN;
-      // ---- pass 1: row maximum of the masked scores (raw; the positive scale is applied to the maximum once)
-      // keys up to `visible` (exclusive) are unmasked for this row: only the diagonal and the last tile ever mask
-      const int visible = min(limit + 1, k_len) - key0;
+      const uint32_t s_addr = lane_base + st * kPN + col0;
+      // keys of this thread's half below `visible` are unmasked for its row: only the diagonal and the last tile mask
+      const int visible = min(limit + 1, k_len) - (j * kPN + col0);
+      // ---- pass 1: maximum of this half of the row (raw scores; the positive scale is applied to the maximum once)
       float mx = -INFINITY;
+      if (ok) {
 #pragma unroll
-      for (int c = 0; c < kPN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_addr + c * 32, r);
-        tmem_ld_wait();
-        if (visible >= (c + 1) * 32) {
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(s_addr + c * 32, r);
+          tmem_ld_wait();
+          if (visible >= (c + 1) * 32) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+          } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, c * 32 + i < visible ? __uint_as_float(r[i]) : -INFINITY);
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, c * 32 + i < visible ? __uint_as_float(r[i]) : -INFINITY);
+          }
         }
       }
+      xmax[(st * 2 + half) * kPM + row] = mx;   // double-buffered by step parity: the partner may run one step ahead
+      softmax_bar();
+      mx = fmaxf(mx, xmax[(st * 2 + (half ^ 1)) * kPM + row]);
       const float m_new = fmaxf(m_run, mx * p.scale_log2e);
       const float base = m_new == -INFINITY ? 0.f : m_new;
       const float corr = fast_exp2(m_run - base);  // m_run == -inf -> 0
       // ---- the previous step's P V has finished (which also frees the P tile): fold it into the registers
-      if (j > 0 && !accumulate_o(j - 1)) { ok = false; break; }
+      if (ok && j > 0) ok = accumulate_o(j - 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) continue;
       // ---- pass 2: probabilities, row sum, P tile (A operand of the second MMA: K-major, 128-byte swizzle)
       float sum = 0.f;
+      uint8_t* atom = sP + half * kPAtom + row * 128;   // keys [64 half, 64 half + 64) of the row are atom `half`
 #pragma unroll
-      for (int c = 0; c < kPN / 16; ++c) {  // 16 keys at a time keeps the register count under the limit
+      for (int c = 0; c < 4; ++c) {  // 16 keys at a time
         uint32_t r[16];
         tmem_ld_32x16(s_addr + c * 16, r);
         tmem_ld_wait();
@@ -269,11 +290,9 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           sum += p0 + p1;
           packed[i >> 1] = p.bf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
         }
-        // keys [16 c, 16 c + 16) of the row: atom c / 4, 16-byte chunks 2 (c % 4) and 2 (c % 4) + 1 of its 128-byte row
-        uint8_t* atom = sP + (c >> 2) * kPAtom + row * 128;
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
-          const int chunk = (c & 3) * 2 + q;
+          const int chunk = c * 2 + q;
           *reinterpret_cast<uint4*>(atom + ((chunk ^ (row & 7)) * 16)) =
               make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
         }
@@ -285,17 +304,20 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         mbar_arrive(s_empty + st);
         mbar_arrive(p_full);
       }
-      l_run = l_run * corr + sum;
+      l_run = l_run * corr + sum;   // this half's share of the row sum; both halves use the same maxima
       m_run = m_new;
       corr_prev = corr;
     }
     if (ok && n_steps > 0) ok = accumulate_o(n_steps - 1);
-    // ---- normalise and store the row
+    // ---- total row sum = sum of the two halves, then normalise and store this half of the row
+    xsum[half * kPM + row] = l_run;
+    softmax_bar();
+    l_run += xsum[(half ^ 1) * kPM + row];
     if (ok && q_pos < q_len) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      uint8_t* dst = static_cast<uint8_t*>(p.out) + (static_cast<size_t>(q_start + q_pos) * p.Hq + h) * kPD * 2;
+      uint8_t* dst = static_cast<uint8_t*>(p.out) + ((static_cast<size_t>(q_start + q_pos) * p.Hq + h) * kPD + col0) * 2;
 #pragma unroll
-      for (int c = 0; c < kPD / 8; ++c) {
+      for (int c = 0; c < 8; ++c) {
         float f[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) f[i] = o[c * 8 + i] * inv;

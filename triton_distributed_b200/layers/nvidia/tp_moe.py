@@ -127,7 +127,8 @@ class EP_MoE:
     def __init__(self, rank: int, world_size: int, group, num_experts: int, topk: int, hidden: int, max_tokens: int,
                  dtype=torch.bfloat16, norm_topk_prob: bool = True, fp8_dispatch: bool = False, fp8_experts: bool = False):
         """fp8_dispatch: tokens travel as e4m3 + one fp32 scale per 128 channels. fp8_experts (needs fp8_dispatch):
-        the up-projection runs on those bytes with block-quantised weights instead of dequantising the rows first."""
+        both expert projections run on the block-scaled fp8 grouped GEMM: the up-projection directly on the dispatched
+        bytes, the down-projection on the SwiGLU output that one kernel gates and quantises (intermediate % 128 == 0)."""
         if fp8_experts and not fp8_dispatch:
             raise ValueError("fp8_experts needs fp8_dispatch")
         self.fp8_experts = fp8_experts
@@ -145,6 +146,9 @@ class EP_MoE:
         if self.fp8_experts:
             from ...kernels.nvidia.grouped_gemm_fp8 import quantize_fp8_weight_blocks
             self.w_gate_up8, self.w_gate_up_scale = quantize_fp8_weight_blocks(self.w_gate_up)
+            self.fp8_down = self.w_down.shape[2] % 128 == 0
+            if self.fp8_down:
+                self.w_down8, self.w_down_scale = quantize_fp8_weight_blocks(self.w_down)
 
     def _grouped(self, a: torch.Tensor, w: torch.Tensor, n_rows: int) -> torch.Tensor:
         sorted_ids, tile_expert, totals, _ = self.a2a.recv_plan()
@@ -176,8 +180,14 @@ class EP_MoE:
                 rows = res
             n_rows = rows.shape[0]
             up = self._grouped(rows, self.w_gate_up, n_rows)
-        act = ops.silu_mul(up)
-        down = self._grouped(act, self.w_down, n_rows)
+        if self.fp8_experts and self.fp8_down:
+            act8, act_scale = ops.silu_mul_fp8(up)
+            down = torch.zeros((n_rows, self.w_down8.shape[1]), dtype=self.dtype, device=up.device)
+            grouped_gemm_fp8_planned(act8, act_scale, self.w_down8, self.w_down_scale, sorted_ids, tile_expert, totals,
+                                     self.a2a.recv_cap // 128, n_rows, 1, None, down)
+        else:
+            act = ops.silu_mul(up)
+            down = self._grouped(act, self.w_down, n_rows)
         return self.a2a.combine(down, w)
 
     @torch.no_grad()

@@ -256,6 +256,21 @@ def silu_mul(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     return out.reshape(*x.shape[:-1], inter)
 
 
+def silu_mul_fp8(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """SwiGLU gate fused with block quantisation: x [T, 2 * I] (gate | up, I % 128 == 0) -> (e4m3 [T, I], fp32 scales
+    [T, I / 128]) with scale = amax / 448 per 128 channels, the activation format of ``grouped_gemm_fp8``."""
+    _lib.require_cuda()
+    x2 = x.reshape(-1, x.shape[-1])
+    _check_2d(x2, "x")
+    inter = x2.shape[1] // 2
+    out8 = torch.empty((x2.shape[0], inter), dtype=torch.float8_e4m3fn, device=x.device)
+    scale = torch.empty((x2.shape[0], inter // 128), dtype=torch.float32, device=x.device)
+    _lib.call("b200_silu_mul_fp8", ptr(x2), ptr(out8), ptr(scale), x2.shape[0], inter, x2.stride(0), dtype_code(x.dtype),
+              stream_ptr())
+    _count()
+    return out8, scale
+
+
 def topk_softmax(logits: torch.Tensor, k: int, renormalize: bool = False):
     """Router: softmax over experts then top-k. Returns (ids int32 [T,k], weights fp32 [T,k])."""
     _lib.require_cuda()
