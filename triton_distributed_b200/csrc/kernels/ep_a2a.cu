@@ -54,6 +54,12 @@ struct EpParams {
   uint8_t* comb[2];         // symmetric [world * max_m, H] bf16
   const float* topk_weight; // [T, topk] or null (plain sum)
   void* out;                // [T, H] bf16
+  // dispatch, optional: grouped-GEMM metadata of the received rows, built by CTA 0 once every source has delivered
+  int32_t* plan_sorted_ids;       // null = no plan
+  int32_t* plan_tile_expert;
+  int32_t* plan_totals;
+  int32_t* plan_rows_per_expert;
+  int plan_cap_rows, plan_block_m;
 };
 
 // cum[e] = pairs of experts < e; every CTA computes it for itself (E <= 1024): coalesced load, then warp 0 scans
@@ -121,6 +127,11 @@ __device__ __forceinline__ void copy_row_warp(uint8_t* dst, const uint8_t* src, 
   }
   for (; i < bytes; i += 512) st_v4(dst + i, ld_v4_relaxed_sys(src + i));
 }
+
+__device__ __forceinline__ void ep_recv_plan_body(const int32_t* splits, int world, int E_local, int max_m, int block_m,
+                                                  int32_t* sorted_ids, int32_t* tile_expert, int32_t* totals,
+                                                  int32_t* rows_per_expert, int cap_rows, int* estart,
+                                                  int (*src_off)[kEpMaxExperts + 1]);
 
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kEpThreads) ep_row_a2a_kernel(const EpParams p, const SymmCtx ctx) {
@@ -254,7 +265,16 @@ __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const EpParams 
       }
     }
   }
-  signal_and_wait(ctx, p.flags + par * kMaxRanks, p.sync + 2, epoch, false);
+  const bool all_in = signal_and_wait(ctx, p.flags + par * kMaxRanks, p.sync + 2, epoch, false);
+  if (blockIdx.x == 0 && p.plan_sorted_ids != nullptr && all_in) {
+    // every source's splits have landed (the wait above acquired them): CTA 0 lays out the grouped-GEMM plan of the
+    // received rows here, which saves the separate one-CTA launch that used to follow every dispatch
+    __shared__ int estart[kEpMaxExperts + 1];
+    __shared__ int src_off[kMaxRanks][kEpMaxExperts + 1];
+    ep_recv_plan_body(p.recv_splits[par], ctx.world, p.E_local, p.max_m, p.plan_block_m, p.plan_sorted_ids, p.plan_tile_expert,
+                      p.plan_totals, p.plan_rows_per_expert, p.plan_cap_rows, estart, src_off);
+  }
+  __syncthreads();
   if (threadIdx.x == 0) epoch_end(p.sync, p.sync + 1, epoch, gridDim.x);
 }
 
@@ -339,27 +359,27 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const EpParams p
 }
 
 // Build grouped-GEMM metadata from recv_splits [world, E_local]: rows grouped by local expert, then source.
-// sorted_ids[i] = row index in the receive buffer (s * max_m + offset), pad = world * max_m. One CTA.
-__global__ void __launch_bounds__(1024) ep_recv_plan_kernel(const int32_t* splits, int world, int E_local, int max_m, int block_m,
-                                                            int32_t* sorted_ids, int32_t* tile_expert, int32_t* totals,
-                                                            int32_t* rows_per_expert, int cap_rows) {
-  __shared__ int estart[kEpMaxExperts + 1];              // padded start row of every local expert
-  __shared__ int src_off[kMaxRanks][kEpMaxExperts + 1];  // offset of (s, e) inside source s's area; [E_local] = total
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  // warp 0: padded expert starts; warps 1..world: offsets inside each source's area (32 experts per step)
-  if (warp <= world) {
+// sorted_ids[i] = row index in the receive buffer (s * max_m + offset), pad = world * max_m. Executed by ONE CTA of any
+// size (a multiple of 32 threads); `estart` and `src_off` are shared memory.
+__device__ __forceinline__ void ep_recv_plan_body(const int32_t* splits, int world, int E_local, int max_m, int block_m,
+                                                  int32_t* sorted_ids, int32_t* tile_expert, int32_t* totals,
+                                                  int32_t* rows_per_expert, int cap_rows, int* estart,
+                                                  int (*src_off)[kEpMaxExperts + 1]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  // role 0: padded expert starts; roles 1..world: offsets inside each source's area (32 experts per step)
+  for (int role = warp; role <= world; role += nwarps) {
     int carry = 0;
     for (int base = 0; base < E_local; base += 32) {
       const int e = base + lane;
       int v = 0;
       if (e < E_local) {
-        if (warp == 0) {
+        if (role == 0) {
           int c = 0;
           for (int s = 0; s < world; ++s) c += splits[s * E_local + e];
           rows_per_expert[e] = c;
           v = (c + block_m - 1) / block_m * block_m;
         } else {
-          v = splits[(warp - 1) * E_local + e];
+          v = splits[(role - 1) * E_local + e];
         }
       }
       int incl = v;
@@ -369,18 +389,18 @@ __global__ void __launch_bounds__(1024) ep_recv_plan_kernel(const int32_t* split
         if (lane >= o) incl += u;
       }
       if (e < E_local) {
-        if (warp == 0) estart[e] = carry + incl - v;
-        else src_off[warp - 1][e] = carry + incl - v;
+        if (role == 0) estart[e] = carry + incl - v;
+        else src_off[role - 1][e] = carry + incl - v;
       }
       carry += __shfl_sync(0xffffffffu, incl, 31);
     }
     if (lane == 0) {
-      if (warp == 0) {
+      if (role == 0) {
         estart[E_local] = carry;
         totals[0] = carry;
         totals[1] = carry / block_m;
       } else {
-        src_off[warp - 1][E_local] = carry;
+        src_off[role - 1][E_local] = carry;
       }
     }
   }
@@ -388,16 +408,25 @@ __global__ void __launch_bounds__(1024) ep_recv_plan_kernel(const int32_t* split
   const int pad = world * max_m;
   for (int i = threadIdx.x; i < min(estart[E_local], cap_rows); i += blockDim.x) sorted_ids[i] = pad;
   __syncthreads();
-  for (int e = 0; e < E_local; ++e) {
+  for (int e = warp; e < E_local; e += nwarps) {  // one warp per local expert: the experts are independent
     int dst = estart[e];
     for (int s = 0; s < world; ++s) {
       const int n = src_off[s][e + 1] - src_off[s][e];
-      for (int i = threadIdx.x; i < n; i += blockDim.x)
+      for (int i = lane; i < n; i += 32)
         if (dst + i < cap_rows) sorted_ids[dst + i] = s * max_m + src_off[s][e] + i;
       dst += n;
     }
-    for (int t = estart[e] / block_m + threadIdx.x; t < estart[e + 1] / block_m; t += blockDim.x) tile_expert[t] = e;
+    for (int t = estart[e] / block_m + lane; t < estart[e + 1] / block_m; t += 32) tile_expert[t] = e;
   }
+}
+
+__global__ void __launch_bounds__(1024) ep_recv_plan_kernel(const int32_t* splits, int world, int E_local, int max_m, int block_m,
+                                                            int32_t* sorted_ids, int32_t* tile_expert, int32_t* totals,
+                                                            int32_t* rows_per_expert, int cap_rows) {
+  __shared__ int estart[kEpMaxExperts + 1];              // padded start row of every local expert
+  __shared__ int src_off[kMaxRanks][kEpMaxExperts + 1];  // offset of (s, e) inside source s's area; [E_local] = total
+  ep_recv_plan_body(splits, world, E_local, max_m, block_m, sorted_ids, tile_expert, totals, rows_per_expert, cap_rows, estart,
+                    src_off);
 }
 
 static int ep_grid(int rows) {
@@ -452,6 +481,33 @@ B200_API int b200_ep_dispatch(const void* symm_ctx, const void* x, int T, int H,
   p.recv[0] = static_cast<uint8_t*>(recv0); p.recv[1] = static_cast<uint8_t*>(recv1);
   p.recv_scale[0] = static_cast<float*>(recv_scale0); p.recv_scale[1] = static_cast<float*>(recv_scale1);
   p.recv_splits[0] = splits0; p.recv_splits[1] = splits1; p.flags = flags; p.sync = sync;
+  ep_dispatch_kernel<<<ep_grid(T), kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(p, ctx);
+  B200_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+// b200_ep_dispatch that also builds the grouped-GEMM plan of the received rows (see b200_ep_recv_plan) in the same launch.
+B200_API int b200_ep_dispatch_planned(const void* symm_ctx, const void* x, int T, int H, int topk, const int32_t* topk_ids,
+                                      const int32_t* pair_pos, const int32_t* counts, int E, int E_local, int max_m, int quant,
+                                      void* recv0, void* recv1, void* recv_scale0, void* recv_scale1, int32_t* splits0,
+                                      int32_t* splits1, uint32_t* flags, uint32_t* sync, int block_m, int32_t* sorted_ids,
+                                      int32_t* tile_expert, int32_t* totals, int32_t* rows_per_expert, int cap_rows,
+                                      void* stream) {
+  EP_CTX();
+  B200_REQUIRE(H % 128 == 0, "hidden (%d) must be a multiple of 128", H);
+  B200_REQUIRE(topk >= 1 && topk <= 32, "top-k (%d) must be in [1, 32]", topk);
+  B200_REQUIRE(E <= kEpMaxExperts && E == E_local * ctx.world, "experts (%d) must equal E_local * world and be <= %d", E, kEpMaxExperts);
+  B200_REQUIRE(sorted_ids && tile_expert && totals && rows_per_expert && block_m >= 1, "missing plan buffers");
+  EpParams p;
+  memset(&p, 0, sizeof(p));
+  p.T = T; p.H = H; p.topk = topk; p.E = E; p.E_local = E_local; p.max_m = max_m; p.quant = quant;
+  p.row_bytes = quant ? H : 2 * H; p.scale_floats = quant ? H / 128 : 0;
+  p.x = x; p.topk_ids = topk_ids; p.pair_pos = pair_pos; p.counts = counts;
+  p.recv[0] = static_cast<uint8_t*>(recv0); p.recv[1] = static_cast<uint8_t*>(recv1);
+  p.recv_scale[0] = static_cast<float*>(recv_scale0); p.recv_scale[1] = static_cast<float*>(recv_scale1);
+  p.recv_splits[0] = splits0; p.recv_splits[1] = splits1; p.flags = flags; p.sync = sync;
+  p.plan_sorted_ids = sorted_ids; p.plan_tile_expert = tile_expert; p.plan_totals = totals;
+  p.plan_rows_per_expert = rows_per_expert; p.plan_cap_rows = cap_rows; p.plan_block_m = block_m;
   ep_dispatch_kernel<<<ep_grid(T), kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(p, ctx);
   B200_CHECK_CUDA(cudaGetLastError());
   return kOk;

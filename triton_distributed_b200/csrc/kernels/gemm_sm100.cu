@@ -83,8 +83,6 @@ struct GemmParams {
   int Mr_cap;
   int rs_blocks;
   void* out;             // [Mr, N]
-  void* rs_stage;        // opt-in: local [M, N] staging. The epilogue writes other owners' rows here and warps 2-3
-                         // forward finished tiles over NVLink, so the accumulator is released at local-store speed
 };
 
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int t, int& m_blk, int& n_blk) {
@@ -278,83 +276,6 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
     }
     __syncwarp();
   } else if (warp < 4) {
-    // ------------------------------------------------------------------ forwarding warps (RS with local staging)
-    if (kMode == kRS && p.rs_stage != nullptr) {
-      // For every tile of this CTA, in issue order: wait for the four epilogue warps, copy the rows that belong to
-      // other ranks from the local staging buffer into the owners' slots (eight 16-byte loads in flight per thread),
-      // then fence and bump the owners' counters. Posted NVLink stores that back up stall these two warps only.
-      const int ct = threadIdx.x - 64;
-      const uint8_t* stage = static_cast<const uint8_t*>(p.rs_stage);
-      uint32_t it = 0;
-      bool ok = true;
-      for (int t = unit; t < total_tiles && ok; t += num_units, ++it) {
-        int m_blk, n_blk;
-        tile_coords(p, t, m_blk, n_blk);
-        if (kPair) m_blk = 2 * m_blk + static_cast<int>(cta_rank);
-        const uint32_t want = 4u * (it + 1u);
-        uint64_t t0 = 0;
-        uint32_t spins = 0;
-        while (true) {
-          uint32_t seen;
-          asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(seen) : "r"(smem_u32(epi_done)) : "memory");
-          if (seen >= want) break;
-          __nanosleep(64);
-          if ((++spins & 63u) == 0u) {
-            const uint64_t now = globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            if (*abort_flag != 0u || now - t0 > pipe_timeout) { ok = false; break; }
-          }
-        }
-        // every forwarding thread must take the same decision, or the named barriers below would not match up
-        if (!ok) *abort_flag = 1u;
-        comm_bar();
-        if (ct == 0) *bcast = *abort_flag != 0u ? 0u : 1u;
-        comm_bar();
-        const bool go = *bcast != 0u;
-        comm_bar();
-        if (!go) { ok = false; break; }
-        const int r_lo = m_blk * kBM, r_hi = min(r_lo + kBM, p.M);
-        if (r_lo < r_hi) {
-          const int col0 = n_blk * kBN;
-          const int vec_per_row = min(kBN, p.N - col0) / 8;
-          const int total_v = (r_hi - r_lo) * vec_per_row;
-          for (int v0 = ct; v0 < total_v; v0 += kCommThreads * 8) {
-            uint4 x[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-              const int v = v0 + u * kCommThreads;
-              if (v < total_v) {
-                const int row = r_lo + v / vec_per_row, c = v % vec_per_row;
-                if (row / p.Mr != ctx.rank)
-                  x[u] = ld_v4_relaxed_sys(stage + (static_cast<size_t>(row) * p.N + col0 + c * 8) * 2);
-              }
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-              const int v = v0 + u * kCommThreads;
-              if (v < total_v) {
-                const int row = r_lo + v / vec_per_row, c = v % vec_per_row;
-                const int owner = row / p.Mr;
-                if (owner != ctx.rank) {
-                  uint8_t* slot = static_cast<uint8_t*>(p.slots[par]) +
-                                  ((static_cast<size_t>(ctx.rank) * p.Mr_cap + (row - owner * p.Mr)) * p.N + col0 + c * 8) * 2;
-                  st_v4(symm_at(ctx, slot, owner), x[u]);
-                }
-              }
-            }
-          }
-          comm_bar();  // all forwarded stores of this tile are issued before anybody signals
-          const int o_lo = r_lo / p.Mr, o_hi = (r_hi - 1) / p.Mr;
-          for (int o = o_lo + ct; o <= o_hi; o += kCommThreads) {
-            fence_acq_rel_sys();
-            const int s0 = max(r_lo, o * p.Mr), s1 = min(r_hi, (o + 1) * p.Mr);
-            const int j = m_blk - (o * p.Mr) / kBM;
-            uint32_t* cnt = p.rs_cnt + ctx.rank * p.rs_blocks + j;
-            red_add_release_sys(symm_at(ctx, cnt, o), static_cast<uint32_t>(s1 - s0));
-          }
-        }
-      }
-    } else
     // ------------------------------------------------------------------ signalling warp (RS)
     if (kMode == kRS && warp == 2) {
       // For every tile of this CTA, in issue order: wait until the four epilogue warps have stored their rows into
@@ -523,13 +444,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
             if (kMode == kRS) {
               const int owner = grow / p.Mr;
               const int lrow = grow - owner * p.Mr;
-              if (p.rs_stage != nullptr && owner != ctx.rank) {
-                st_v4(static_cast<uint8_t*>(p.rs_stage) + (static_cast<size_t>(grow) * p.N + gcol) * 2, v);
-              } else {
-                uint8_t* slot = static_cast<uint8_t*>(p.slots[par]) +
-                                ((static_cast<size_t>(ctx.rank) * p.Mr_cap + lrow) * p.N + gcol) * 2;
-                st_v4(symm_at(ctx, slot, owner), v);
-              }
+              uint8_t* slot = static_cast<uint8_t*>(p.slots[par]) +
+                              ((static_cast<size_t>(ctx.rank) * p.Mr_cap + lrow) * p.N + gcol) * 2;
+              st_v4(symm_at(ctx, slot, owner), v);
             } else {
               st_v4(static_cast<uint8_t*>(p.C) + (static_cast<size_t>(grow) * p.ldc + gcol) * 2, v);
             }
@@ -811,7 +728,7 @@ B200_API int b200_ag_gemm(const void* symm_ctx, const void* a_local, void* ag_bu
 // u32[world][rs_blocks]; sync: local u32[4]; all zero-initialised once.
 static int gemm_rs_impl(const void* symm_ctx, const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb,
                         int dtype, void* slots0, void* slots1, uint32_t* rs_cnt, uint32_t* rs_base, uint32_t* sync,
-                        int Mr_cap, int rs_blocks, int group_m, int max_ctas, void* stage, void* stream) {
+                        int Mr_cap, int rs_blocks, int group_m, int max_ctas, void* stream) {
   SymmCtx ctx;
   memcpy(&ctx, symm_ctx, sizeof(ctx));
   B200_REQUIRE(M % ctx.world == 0, "M (%d) must be divisible by the world size (%d)", M, ctx.world);
@@ -830,7 +747,6 @@ static int gemm_rs_impl(const void* symm_ctx, const void* A, const void* B, void
   p.Mr_cap = Mr_cap;
   p.rs_blocks = rs_blocks;
   p.out = out;
-  p.rs_stage = stage;
   const bool pair = use_pair(M);
   set_tiles(p, pair, ((ctx.rank + 1) % ctx.world) * p.Mr);
   CUtensorMap ta, tb;
@@ -847,18 +763,7 @@ B200_API int b200_gemm_rs(const void* symm_ctx, const void* A, const void* B, vo
                           int ldb, int dtype, void* slots0, void* slots1, uint32_t* rs_cnt, uint32_t* rs_base,
                           uint32_t* sync, int Mr_cap, int rs_blocks, int group_m, int max_ctas, void* stream) {
   return gemm_rs_impl(symm_ctx, A, B, out, M, N, K, lda, ldb, dtype, slots0, slots1, rs_cnt, rs_base, sync, Mr_cap, rs_blocks,
-                      group_m, max_ctas, nullptr, stream);
-}
-
-// GEMM-RS with local staging (opt-in): `stage` is a local [M, N] buffer of the output dtype. The epilogue writes the
-// rows of other ranks there and the two otherwise idle warps of every CTA forward finished tiles to the owners.
-B200_API int b200_gemm_rs_staged(const void* symm_ctx, const void* A, const void* B, void* out, int M, int N, int K, int lda,
-                                 int ldb, int dtype, void* slots0, void* slots1, uint32_t* rs_cnt, uint32_t* rs_base,
-                                 uint32_t* sync, int Mr_cap, int rs_blocks, int group_m, int max_ctas, void* stage,
-                                 void* stream) {
-  B200_REQUIRE(stage != nullptr, "the staged GEMM-RS needs its staging buffer");
-  return gemm_rs_impl(symm_ctx, A, B, out, M, N, K, lda, ldb, dtype, slots0, slots1, rs_cnt, rs_base, sync, Mr_cap, rs_blocks,
-                      group_m, max_ctas, stage, stream);
+                      group_m, max_ctas, stream);
 }
 
 // 1 = CTA pairs (256x256 tiles, cta_group::2), 0 = single CTAs (128x256), -1 = follow B200DIST_GEMM_2CTA.

@@ -60,8 +60,6 @@ struct GroupedParams {
   uint32_t* rank_flag;        // local u32[world]: == epoch once the shard of that rank is complete
   uint32_t* sync;             // local u32[4]: epoch, done counter, local chunk counter, grid barrier counter
   int Tr;                     // tokens per rank
-  int push;                   // AG by push (opt-in): `ready` holds rows-landed counters [2][kMaxRanks] (symmetric, only
-                              // ever grow) and `rank_cnt` their bases [2][kMaxRanks] (local) instead of flags / counters
   // ---- RS ----
   int topk, Tr_cap;
   void* slots[2];             // symmetric [world][Tr_cap][N]
@@ -187,35 +185,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
       uint8_t* buf = static_cast<uint8_t*>(p.ag_buf[par]);
       constexpr int kRows = 8;
       const int nch = (p.Tr + kRows - 1) / kRows;
-      if (p.push) {
-        // Push: step s stores this rank's tokens into the gather buffer of rank - s (step 0: its own) and adds the
-        // rows to that rank's counter for this source. Posted stores, so the gather is not bound by load latency.
-        uint32_t* cnt = p.ready + par * kMaxRanks;
-        for (int g = blockIdx.x; g < nch * ctx.world; g += gridDim.x) {
-          const int step = g / nch, c = g - step * nch;
-          int dst = ctx.rank - step;
-          if (dst < 0) dst += ctx.world;
-          const int r0 = c * kRows, nrows = min(kRows, p.Tr - r0);
-          const size_t off = (static_cast<size_t>(ctx.rank) * p.Tr + r0) * row_bytes;
-          const uint8_t* from = static_cast<const uint8_t*>(p.a_local) + static_cast<size_t>(r0) * row_bytes;
-          uint8_t* to = step == 0 ? buf + off : symm_at(ctx, buf + off, dst);
-          const size_t nvec = nrows * row_bytes / 16;
-          for (size_t i = ct; i < nvec; i += 64 * 8) {
-            uint4 v[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-              if (i + u * 64 < nvec) v[u] = ld_v4_relaxed_sys(reinterpret_cast<const uint4*>(from) + i + u * 64);
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-              if (i + u * 64 < nvec) st_v4(reinterpret_cast<uint4*>(to) + i + u * 64, v[u]);
-          }
-          gcomm_bar();
-          if (ct == 0) {
-            fence_acq_rel_sys();
-            red_add_release_sys(symm_at(ctx, cnt + ctx.rank, dst), static_cast<uint32_t>(nrows));
-          }
-        }
-      } else
       for (int g = blockIdx.x; g < nch * ctx.world; g += gridDim.x) {
         const int step = g / nch, c = g - step * nch;
         int src = ctx.rank + step;
@@ -338,18 +307,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
           const int src = src_row / p.Tr;
           // this rank's own tokens are read where the caller put them: no copy, no flag, so the tiles that need only
           // local rows start at once (the copy into the symmetric buffer is for the peers only)
-          local_row = src == ctx.rank && !p.push;
+          local_row = src == ctx.rank;
           if (!local_row && src != last_src) {
             // a shard that any thread of this CTA has seen complete is not polled in global memory again
             uint32_t seen;
             asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(seen) : "r"(smem_u32(ready_cache + src)) : "memory");
             if (seen != epoch) {
-              if (p.push) {
-                const int idx = par * kMaxRanks + src;
-                ok = wait_flag<WaitCmp::GE, true>(ctx, p.ready + idx, p.rank_cnt[idx] + static_cast<uint32_t>(p.Tr), src, __LINE__);
-              } else {
-                ok = wait_flag<WaitCmp::EQ, false>(ctx, p.rank_flag + src, epoch, src, __LINE__);
-              }
+              ok = wait_flag<WaitCmp::EQ, false>(ctx, p.rank_flag + src, epoch, src, __LINE__);
               if (ok) asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(ready_cache + src)), "r"(epoch) : "memory");
             }
             last_src = src;
@@ -478,8 +442,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
         p.sync[1] = 0;
         if (kMode == kGRS)
           for (int s = 0; s < ctx.world; ++s) p.rs_base[s] += static_cast<uint32_t>(p.Tr);
-        if (kMode == kGAG && p.push)
-          for (int s = 0; s < ctx.world; ++s) p.rank_cnt[par * kMaxRanks + s] += static_cast<uint32_t>(p.Tr);
         __threadfence();
         p.sync[0] = epoch;
       }
@@ -571,7 +533,7 @@ B200_API int b200_grouped_gemm(const void* A, int lda, int a_div, const void* W,
 static int ag_grouped_impl(const void* symm_ctx, const void* a_local, void* ag_buf0, void* ag_buf1, int Tr, int topk,
                            const void* W, int E, int N, int K, const int32_t* sorted_ids, const int32_t* tile_expert,
                            const int32_t* tile_order, const int32_t* totals, int max_tiles, void* out, int ldo,
-                           uint32_t* ready, uint32_t* rank_cnt, uint32_t* rank_flag, uint32_t* sync, int dtype, int push,
+                           uint32_t* ready, uint32_t* rank_cnt, uint32_t* rank_flag, uint32_t* sync, int dtype,
                            void* stream) {
   SymmCtx ctx;
   memcpy(&ctx, symm_ctx, sizeof(ctx));
@@ -582,7 +544,7 @@ static int ag_grouped_impl(const void* symm_ctx, const void* a_local, void* ag_b
                         nullptr, dtype);
   if (rc != kOk) return rc;
   p.lda = K; p.a_local = a_local; p.ag_buf[0] = ag_buf0; p.ag_buf[1] = ag_buf1; p.ready = ready;
-  p.rank_cnt = rank_cnt; p.rank_flag = rank_flag; p.sync = sync; p.Tr = Tr; p.push = push;
+  p.rank_cnt = rank_cnt; p.rank_flag = rank_flag; p.sync = sync; p.Tr = Tr;
   return launch_grouped<kGAG>(tw, p, ctx, sm_count(), static_cast<cudaStream_t>(stream));
 }
 
@@ -592,18 +554,7 @@ B200_API int b200_ag_grouped_gemm(const void* symm_ctx, const void* a_local, voi
                                   uint32_t* ready, uint32_t* rank_cnt, uint32_t* rank_flag, uint32_t* sync, int dtype,
                                   void* stream) {
   return ag_grouped_impl(symm_ctx, a_local, ag_buf0, ag_buf1, Tr, topk, W, E, N, K, sorted_ids, tile_expert, tile_order, totals,
-                         max_tiles, out, ldo, ready, rank_cnt, rank_flag, sync, dtype, 0, stream);
-}
-
-// Same operation with the push gather (opt-in). `ready` (symmetric u32[16]) and `rank_cnt` (local u32[16]) are then
-// rows-landed counters and their bases, [2][8] by epoch parity; a context must use one gather for its whole life.
-B200_API int b200_ag_grouped_gemm_push(const void* symm_ctx, const void* a_local, void* ag_buf0, void* ag_buf1, int Tr,
-                                       int topk, const void* W, int E, int N, int K, const int32_t* sorted_ids,
-                                       const int32_t* tile_expert, const int32_t* tile_order, const int32_t* totals,
-                                       int max_tiles, void* out, int ldo, uint32_t* ready, uint32_t* rank_cnt,
-                                       uint32_t* rank_flag, uint32_t* sync, int dtype, void* stream) {
-  return ag_grouped_impl(symm_ctx, a_local, ag_buf0, ag_buf1, Tr, topk, W, E, N, K, sorted_ids, tile_expert, tile_order, totals,
-                         max_tiles, out, ldo, ready, rank_cnt, rank_flag, sync, dtype, 1, stream);
+                         max_tiles, out, ldo, ready, rank_cnt, rank_flag, sync, dtype, stream);
 }
 
 // Grouped GEMM + topk-reduce + reduce-scatter: A [n_pairs, K_local] (row per pair), W [E, N, K_local],

@@ -10,7 +10,6 @@ reference's ``[E, K, N_per_rank]`` layout is accepted and transposed once per we
 from __future__ import annotations
 
 import dataclasses
-import os
 
 import torch
 
@@ -62,10 +61,6 @@ class MoEAllGatherGroupGEMMTensorParallelContext:
         self.symm_workspaces = []
 
 
-# B200DIST_AG_GROUP_PUSH=1 (opt-in, process-wide: a context keeps one gather for its whole life) stores the tokens into the
-# peers' buffers instead of pulling them; the same flag words then serve as rows-landed counters.
-_AG_ENTRY = "b200_ag_grouped_gemm_push" if os.environ.get("B200DIST_AG_GROUP_PUSH", "0") == "1" else "b200_ag_grouped_gemm"
-
 
 def create_ag_group_gemm_context(max_ntokens: int, N_per_rank: int, K: int, num_experts: int, topk: int,
                                  dtype: torch.dtype, rank: int, num_ranks: int, num_local_ranks: int | None = None,
@@ -85,6 +80,17 @@ def create_ag_group_gemm_context(max_ntokens: int, N_per_rank: int, K: int, num_
     return ctx
 
 
+def _reorder_pays(ctx, T: int, E: int, N: int, K: int, es: int) -> bool:
+    world = ctx.num_ranks
+    if world == 1:
+        return False
+    tiles_per_expert = max(1, (T * ctx.topk) // (E * 128))
+    restreams = min(world, tiles_per_expert) - 1                 # extra passes over the weights
+    weight_time = restreams * E * N * K * es / 6.5e12            # at the measured HBM copy rate
+    gather_time = (world - 1) / world * T * K * es / 6.0e11      # at what the pulling warps sustain per GPU
+    return weight_time < 0.5 * gather_time
+
+
 def ag_group_gemm(a: torch.Tensor, b: torch.Tensor, ctx: MoEAllGatherGroupGEMMTensorParallelContext,
                   full_topk_ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """a [ntokens / r, K]; b [E, N / r, K] (or [E, K, N / r]); full_topk_ids int32 [ntokens, topk] (all ranks' tokens).
@@ -97,10 +103,14 @@ def ag_group_gemm(a: torch.Tensor, b: torch.Tensor, ctx: MoEAllGatherGroupGEMMTe
     E, N, _ = w.shape
     plan = ctx.plan_for(T)
     moe_sort(full_topk_ids.to(torch.int32).contiguous(), plan, tokens_per_rank=Tr)
-    order = order_tiles(plan, ctx.rank, ctx.num_ranks, 0)
+    # Issuing tiles in the order their source shards arrive lets the GEMM start under the gather, but it also splits
+    # every expert's tiles over several arrival stages, and each stage streams the expert's weights again. Reorder only
+    # when those extra weight bytes cost clearly less HBM time than the gather takes on the links; otherwise keep the
+    # expert-major order (each tile still waits only for the shards its own rows come from).
+    order = order_tiles(plan, ctx.rank, ctx.num_ranks, 0) if _reorder_pays(ctx, T, E, N, K, a.element_size()) else None
     if out is None:
         out = torch.empty((T * ctx.topk, N), dtype=a.dtype, device=a.device)
-    _lib.call(_AG_ENTRY, ctx.heap.ctx, ptr(a.contiguous()), ptr(ctx.symm_workspaces[0]),
+    _lib.call("b200_ag_grouped_gemm", ctx.heap.ctx, ptr(a.contiguous()), ptr(ctx.symm_workspaces[0]),
               ptr(ctx.symm_workspaces[1]), Tr, ctx.topk, ptr(w), E, N, K, ptr(plan.sorted_ids), ptr(plan.tile_expert),
               ptr(order), ptr(plan.totals), plan.max_tiles, ptr(out), out.stride(0), ptr(ctx.symm_ready), ptr(ctx.rank_cnt),
               ptr(ctx.rank_flag), ptr(ctx.sync), dtype_code(a.dtype), stream_ptr())

@@ -10,7 +10,6 @@ The sum order is fixed (slot 0..r-1), so results are reproducible run to run.
 from __future__ import annotations
 
 import dataclasses
-import os
 
 import torch
 
@@ -18,8 +17,6 @@ from ... import _lib, ops
 from ..._lib import dtype_code, ptr, stream_ptr
 from ...runtime.heap import SymmHeap, get_heap
 
-
-_RS_STAGED = os.environ.get("B200DIST_RS_STAGED", "0") == "1"
 
 
 @dataclasses.dataclass
@@ -42,7 +39,6 @@ class GEMMReduceScatterTensorParallelContext:
     stages: int = 4
     group_m: int = 8
     max_ctas: int = 0
-    stage: torch.Tensor | None = None   # local [max_M, N] staging of the opt-in forwarding variant
 
     def finalize(self) -> None:
         self.heap.sync_and_check(type(self).__name__)
@@ -93,15 +89,6 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, ctx: GEMMReduceScatterTensorParall
         out = torch.empty((M // ctx.world_size, N), dtype=ctx.output_dtype, device=a.device)
     elif tuple(out.shape) != (M // ctx.world_size, N) or out.dtype != ctx.output_dtype or not out.is_contiguous():
         raise ValueError("out must be a contiguous [M / world, N] tensor of the context's dtype")
-    if _RS_STAGED and ctx.world_size > 1:
-        # opt-in: the epilogue stages other ranks' rows locally and the idle warps forward them (see gemm_sm100.cu)
-        if ctx.stage is None:
-            ctx.stage = torch.empty((ctx.max_M, ctx.N), dtype=ctx.output_dtype, device=a.device)
-        _lib.call("b200_gemm_rs_staged", ctx.heap.ctx, ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0),
-                  dtype_code(a.dtype), ptr(ctx.slots[0]), ptr(ctx.slots[1]), ptr(ctx.rs_cnt), ptr(ctx.rs_base), ptr(ctx.sync),
-                  ctx.max_M // ctx.world_size, ctx.rs_blocks, ctx.group_m, ctx.max_ctas, ptr(ctx.stage), stream_ptr())
-        ops._count()
-        return out
     _lib.call("b200_gemm_rs", ctx.heap.ctx, ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0),
               dtype_code(a.dtype), ptr(ctx.slots[0]), ptr(ctx.slots[1]), ptr(ctx.rs_cnt), ptr(ctx.rs_base), ptr(ctx.sync),
               ctx.max_M // ctx.world_size, ctx.rs_blocks, ctx.group_m, ctx.max_ctas, stream_ptr())

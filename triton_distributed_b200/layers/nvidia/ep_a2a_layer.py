@@ -71,16 +71,15 @@ class EPAll2AllLayer:
         moe_sort(ids, plan)
         self._dispatch_calls += 1  # mirrors the device-resident epoch without reading it back
         par = self._dispatch_calls & 1
-        _lib.call("b200_ep_dispatch", self.heap.ctx, ptr(input.contiguous()), T, self.hidden, self.topk, ptr(ids),
+        # one launch: permute (+ quantise) + send, and CTA 0 lays out the grouped-GEMM plan of the received rows
+        _lib.call("b200_ep_dispatch_planned", self.heap.ctx, ptr(input.contiguous()), T, self.hidden, self.topk, ptr(ids),
                   ptr(plan.pair_pos), ptr(plan.group_count), self.num_tot_experts, self.experts_per_rank, self.max_m,
                   1 if self.fp8 else 0, ptr(self.recv[0]), ptr(self.recv[1]), ptr(self.recv_scale[0]), ptr(self.recv_scale[1]),
-                  ptr(self.recv_splits[0]), ptr(self.recv_splits[1]), ptr(self.dflags), ptr(self.dsync), stream_ptr())
-        ops._count()
-        self._last = (T, ids, plan, par)
-        _lib.call("b200_ep_recv_plan", ptr(self.recv_splits[par]), self.world_size, self.experts_per_rank, self.max_m, 128,
+                  ptr(self.recv_splits[0]), ptr(self.recv_splits[1]), ptr(self.dflags), ptr(self.dsync), 128,
                   ptr(self.recv_sorted_ids), ptr(self.recv_tile_expert), ptr(self.recv_totals), ptr(self.recv_rows_per_expert),
                   self.recv_cap, stream_ptr())
         ops._count()
+        self._last = (T, ids, plan, par)
         buf = self.recv[par].view(torch.float8_e4m3fn) if self.fp8 else self.recv[par]
         return (buf, self.recv_scale[par]) if self.fp8 else buf
 

@@ -38,6 +38,9 @@ ARCHS: dict[str, ArchConfig] = {
                                      moe_intermediate_size=768),
     "Qwen/Qwen3-235B-A22B": ArchConfig(4096, 12288, 94, 64, 4, num_experts=128, num_experts_per_tok=8,
                                        moe_intermediate_size=1536),
+    # what ONE rank of a tensor-parallel Qwen3-32B computes at TP = 8 (heads, KV heads and intermediate size divided by
+    # eight, vocabulary shard): a single-GPU stand-in for tuning the per-rank kernel chain without the collectives
+    "Qwen3-32B-tp8-shard": ArchConfig(5120, 3200, 64, 8, 1, vocab_size=18992),
     # test shapes: same structure, divisible by 8 ranks
     "tiny-qwen3": ArchConfig(512, 1024, 2, 8, 8, vocab_size=1024),
     "tiny-qwen3-gqa": ArchConfig(1024, 2048, 3, 16, 8, vocab_size=2048),
