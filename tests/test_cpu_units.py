@@ -283,7 +283,7 @@ def test_allreduce_method_resolution_and_split_heuristics():
         to_allreduce_method("ring")
     for batch, hkv, group, kv in [(1, 1, 8, 128), (8, 8, 8, 2048), (8, 1, 8, 2048), (32, 8, 8, 1 << 20), (1, 8, 8, 1 << 20)]:
         s = ops.choose_kv_splits(batch, hkv, group, kv)
-        assert 1 <= s <= 128 and (s == 1 or kv // s >= 256)
+        assert 1 <= s <= 64 and (s == 1 or kv // s >= 128)
 
 
 def test_bench_withholds_its_result_when_a_wait_expired(capsys):

@@ -82,6 +82,7 @@ struct SkinnyParams {
   float* scratch;     // [tiles][dual ? 2 : 1][MB][128] fp32, zero on entry and on exit
   uint32_t* tickets;  // [tiles], zero on entry and on exit
   SkinnyEpilogue ep;
+  unsigned long long* trace;  // optional [gridDim.x][8] %globaltimer checkpoints of every CTA (tuning aid), else null
 };
 
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
@@ -134,6 +135,16 @@ __device__ __forceinline__ void finish_tile16(const SkinnyParams& p, int tile, i
     const int head = tile;
     const bool is_q = head < ep.Hq, is_k = !is_q && head < ep.Hq + ep.Hkv;
     const void* gamma = is_q ? ep.q_gamma : is_k ? ep.k_gamma : nullptr;
+    // rotary factors are fetched first so that their two dependent loads overlap the per-head norm
+    float cj[16], sj[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      cj[j] = 1.f, sj[j] = 0.f;
+      if ((is_q || is_k) && j < p.M) {
+        const float* cs = ep.cos_sin + static_cast<size_t>(__ldg(ep.positions + j)) * 128;
+        cj[j] = __ldg(cs + (et & 63)), sj[j] = __ldg(cs + 64 + (et & 63));
+      }
+    }
     if (gamma != nullptr) {  // per-head RMSNorm over the 128 features of the tile
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
@@ -154,12 +165,8 @@ __device__ __forceinline__ void finish_tile16(const SkinnyParams& p, int tile, i
       epi_bar();
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        if (j < p.M) {
-          const float other = xch[j * kSkBN + (et ^ 64)];
-          const float* cs = ep.cos_sin + static_cast<size_t>(ep.positions[j]) * 128;
-          const float c = cs[et & 63], sn = cs[64 + (et & 63)];
-          g[j] = et < 64 ? g[j] * c - other * sn : g[j] * c + other * sn;
-        }
+        const float other = xch[j * kSkBN + (et ^ 64)];
+        g[j] = et < 64 ? g[j] * cj[j] - other * sj[j] : g[j] * cj[j] + other * sj[j];
       }
     }
 #pragma unroll
@@ -179,12 +186,18 @@ __device__ __forceinline__ void finish_tile16(const SkinnyParams& p, int tile, i
   }
   if (ep.kind == kEpResidual) {
     const float gm = (ep.next_gamma != nullptr && n < p.N) ? ld_elem(ep.next_gamma, n, bf16) : 0.f;
+    // every residual element is loaded before the first store: residual_in may alias residual_out, so the compiler
+    // keeps loads behind earlier stores, which would make this one memory round trip per token
+    float res[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      res[j] = (j < p.M && n < p.N) ? ld_elem(ep.residual_in, static_cast<size_t>(j) * p.ldc + n, bf16) : 0.f;
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       float sq = 0.f;
       if (j < p.M && n < p.N) {
         const size_t o = static_cast<size_t>(j) * p.ldc + n;
-        const float h = round_elem(g[j] + ld_elem(ep.residual_in, o, bf16), bf16);  // the stream is kept in storage type
+        const float h = round_elem(g[j] + res[j], bf16);  // the stream is kept in storage type
         st_elem(ep.residual_out, o, h, bf16);
         if (ep.scaled_out != nullptr) st_elem(ep.scaled_out, o, h * gm, bf16);
         sq = h * h;
@@ -229,6 +242,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const int u_begin = blockIdx.x * p.units_per_cta;
   const int u_end = min(p.units_total, u_begin + p.units_per_cta);
   griddep_launch_dependents();  // the next kernel may set itself up while this one streams
+  auto stamp = [&](int slot) {
+    if (p.trace != nullptr) p.trace[blockIdx.x * 8 + slot] = globaltimer_ns();
+  };
+  if (threadIdx.x == 0) stamp(0);  // CTA start
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < p.stages; ++i) {
@@ -249,6 +266,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
+  if (threadIdx.x == 0) stamp(1);  // barriers initialised, TMEM allocated
 
   if (warp == 0) {
     if (elect_one()) {
@@ -262,6 +280,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       int def_kb[kSkMaxStages];
       auto flush_deferred = [&]() {
         griddep_wait();
+        stamp(2);  // the previous kernel has completed: activations may be loaded
         fence_proxy_async();
         waited = true;
         for (int j = 0; j < ndef; ++j)
@@ -313,6 +332,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (ok) umma_commit(tfull_bar + acc);
         ++it;
       }
+      stamp(3);  // last MMA issued
     }
     __syncwarp();
   } else if (warp >= 4) {
@@ -333,6 +353,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const int contributors = last_cta - first_cta + 1;
       if (!mbar_wait(tfull_bar + acc, acc_phase, abort_flag, timeout_ns)) break;
       tc_fence_after_sync();
+      if (et == 0 && u >= u_end) stamp(4);  // accumulator of this CTA's last segment is complete
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(w * 32) << 16) + acc * acc_cols;
       float* scratch = p.scratch + static_cast<size_t>(sg.tile) * kW * p.MB * kSkBN;
       auto store_out = [&](int m, float g, float uu) {
@@ -377,8 +398,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         __threadfence();
         epi_bar();
         if (et == 0) {
+          if (u >= u_end) stamp(5);  // partial sums added and fenced
           const uint32_t t = atomicAdd(p.tickets + sg.tile, 1u);
           last_flag = (t == static_cast<uint32_t>(contributors - 1)) ? 1u : 0u;
+          if (u >= u_end) stamp(6);  // ticket drawn
         }
         epi_bar();
         if (last_flag && fused_ep) {
@@ -402,17 +425,26 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           if (et == 0) p.tickets[sg.tile] = 0;
         } else if (last_flag) {
           __threadfence();
-          for (int m = 0; m < p.M; ++m) {
-            float* gs = scratch + static_cast<size_t>(m) * kSkBN + et;
-            const float g = __ldcg(gs);
-            float uv = 0.f;
-            __stcg(gs, 0.f);
-            if (kDual) {
-              float* us = scratch + static_cast<size_t>(p.MB + m) * kSkBN + et;
-              uv = __ldcg(us);
-              __stcg(us, 0.f);
+          // eight tokens at a time, all loads issued before the first use: one L2 round trip per batch instead of one
+          // per token (this loop is the tail of the kernel; at 8 tokens it used to cost ~4 us, now ~1 us)
+          for (int m0 = 0; m0 < p.M; m0 += 8) {
+            float gv[8], uv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              gv[j] = uv[j] = 0.f;
+              if (m0 + j < p.M) {
+                gv[j] = __ldcg(scratch + static_cast<size_t>(m0 + j) * kSkBN + et);
+                if (kDual) uv[j] = __ldcg(scratch + static_cast<size_t>(p.MB + m0 + j) * kSkBN + et);
+              }
             }
-            store_out(m, g, uv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (m0 + j < p.M) {
+                __stcg(scratch + static_cast<size_t>(m0 + j) * kSkBN + et, 0.f);
+                if (kDual) __stcg(scratch + static_cast<size_t>(p.MB + m0 + j) * kSkBN + et, 0.f);
+                store_out(m0 + j, gv[j], uv[j]);
+              }
+            }
           }
           if (et == 0) p.tickets[sg.tile] = 0;
         }
@@ -424,6 +456,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 2) tmem_dealloc(tmem_base, tmem_cols);
+  if (threadIdx.x == 0) stamp(7);  // CTA done
 }
 
 // Shared memory per CTA for the weight ring. At about half of an SM's shared memory the first CTAs of the next
@@ -469,6 +502,8 @@ B200_API long long b200_gemm_skinny_scratch_floats(int M, int N, int dual) {
 // dual == 0: N = Nw. dual == 1: W = [gate (N rows); up (N rows)], C = silu(X gate^T) * (X up^T).
 // scratch / tickets: zero-initialised once by the caller; every call leaves them zeroed.
 // splits <= 0: one CTA per SM (stream-K); splits > 0 forces tiles * splits CTAs.
+static unsigned long long* g_skinny_trace = nullptr;
+
 static int skinny_impl(const void* X, const void* W, void* C, int M, int N, int K, int ldx, int ldw, int ldc, int dual,
                        int dtype, float* scratch, uint32_t* tickets, int splits, const SkinnyEpilogue* ep, void* stream) {
   B200_REQUIRE(dtype == kBF16 || dtype == kF16, "gemm_skinny supports bf16/f16");
@@ -488,6 +523,7 @@ static int skinny_impl(const void* X, const void* W, void* C, int M, int N, int 
   p.up_row0 = N;
   p.bf16 = dtype == kBF16;
   p.C = C; p.ldc = ldc; p.scratch = scratch; p.tickets = tickets;
+  p.trace = g_skinny_trace;
   if (ep != nullptr) {
     p.ep = *ep;
     const bool fused = ep->kind != kEpNone || ep->sumsq_in != nullptr;
@@ -511,6 +547,9 @@ static int skinny_impl(const void* X, const void* W, void* C, int M, int N, int 
   if (ctas > p.units_total) ctas = p.units_total;
   p.units_per_cta = (p.units_total + ctas - 1) / ctas;
   ctas = (p.units_total + p.units_per_cta - 1) / p.units_per_cta;
+  // no more ring stages than a CTA has k-blocks to stream: a small GEMM then keeps little shared memory, and the first
+  // CTAs of the next kernel of a programmatic-dependent-launch chain can become resident next to it
+  if (p.stages > p.units_per_cta) p.stages = p.units_per_cta < 2 ? 2 : p.units_per_cta;
   B200_REQUIRE(scratch && tickets, "gemm_skinny needs scratch and tickets");
   CUtensorMap tw, tx;
   int rc = make_tma_2d(&tw, W, dtype, static_cast<uint64_t>(kw) * N, K, ldw, kSkBN, kSkBK, true);
@@ -536,6 +575,13 @@ B200_API int b200_gemm_skinny_fused(const void* X, const void* W, void* C, int M
   B200_REQUIRE(epilogue != nullptr, "b200_gemm_skinny_fused needs an epilogue description");
   return skinny_impl(X, W, C, M, N, K, ldx, ldw, ldc, dual, dtype, scratch, tickets, 0,
                      static_cast<const SkinnyEpilogue*>(epilogue), stream);
+}
+// Tuning aid: while `buf` (device memory, 8 x u64 per CTA, at least 148 CTAs) is set, every decode GEMM launch writes
+// %globaltimer checkpoints of each CTA there (0 start, 1 set-up done, 2 previous kernel complete, 3 last MMA issued,
+// 4 last accumulator complete, 5 partial sums fenced, 6 ticket drawn, 7 CTA done). Pass null to switch it off.
+B200_API int b200_gemm_skinny_set_trace(void* buf) {
+  g_skinny_trace = static_cast<unsigned long long*>(buf);
+  return kOk;
 }
 B200_API int b200_gemm_skinny_epilogue_bytes() { return static_cast<int>(sizeof(SkinnyEpilogue)); }
 
