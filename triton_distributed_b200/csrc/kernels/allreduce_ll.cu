@@ -45,25 +45,43 @@ __device__ __forceinline__ uint32_t ll_pack(float a, float b, bool bf16) { retur
 __global__ void __launch_bounds__(kLLThreads) allreduce_ll_kernel(const ArLLParams p, const SymmCtx ctx) {
   __shared__ float red[33];
   griddep_launch_dependents();
-  griddep_wait();
-  const uint32_t epoch = epoch_begin(p.sync);
-  const int par = epoch & 1;
   const int world = ctx.world, me = ctx.rank;
   const int row_words = p.hidden / 2;
   const bool bf16 = p.bf16 != 0;
-  uint64_t* ws = p.ws[par];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // the gain is a weight (never an output of the kernel launched just before this one): fetched before the dependency
+  // wait, past L1, so that it costs no round trip after the sum
+  uint32_t gw[kLLWordsPerThread];
+#pragma unroll
+  for (int u = 0; u < kLLWordsPerThread; ++u) {
+    const int i = tid + u * kLLThreads;
+    gw[u] = i < row_words ? __ldcg(p.gamma + i) : 0u;
+  }
+  griddep_wait();
+  const uint32_t epoch = epoch_begin(p.sync);
+  const int par = epoch & 1;
+  uint64_t* ws = p.ws[par];
   bool ok = true;
 
   for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
     // ---- send: my word goes into slot [me] of every rank (my own copy is taken from the register below)
-    uint32_t mine[kLLWordsPerThread];
+    // all of the row's loads (partial result and residual) are issued before the first packet leaves, so that the
+    // residual's round trip overlaps the exchange instead of following every poll
+    uint32_t mine[kLLWordsPerThread], resw[kLLWordsPerThread];
+#pragma unroll
+    for (int u = 0; u < kLLWordsPerThread; ++u) {
+      const int i = tid + u * kLLThreads;
+      mine[u] = resw[u] = 0u;
+      if (i < row_words) {
+        mine[u] = p.in[static_cast<size_t>(row) * row_words + i];
+        if (p.residual_in) resw[u] = p.residual_in[static_cast<size_t>(row) * row_words + i];
+      }
+    }
 #pragma unroll
     for (int u = 0; u < kLLWordsPerThread; ++u) {
       const int i = tid + u * kLLThreads;
       if (i < row_words) {
-        const uint32_t d = p.in[static_cast<size_t>(row) * row_words + i];
-        mine[u] = d;
+        const uint32_t d = mine[u];
         uint64_t* slot = ws + (static_cast<size_t>(me) * p.rows + row) * row_words + i;
         if (p.use_mc) {
           const uint64_t v = (static_cast<uint64_t>(epoch) << 32) | d;
@@ -120,7 +138,7 @@ __global__ void __launch_bounds__(kLLThreads) allreduce_ll_kernel(const ArLLPara
             a1 += f.y;
           }
         if (p.residual_in) {
-          const float2 r = ll_unpack(p.residual_in[static_cast<size_t>(row) * row_words + i], bf16);
+          const float2 r = ll_unpack(resw[u], bf16);
           a0 += r.x;
           a1 += r.y;
         }
@@ -146,7 +164,7 @@ __global__ void __launch_bounds__(kLLThreads) allreduce_ll_kernel(const ArLLPara
     for (int u = 0; u < kLLWordsPerThread; ++u) {
       const int i = tid + u * kLLThreads;
       if (i < row_words && ok) {
-        const float2 g = ll_unpack(p.gamma[i], bf16);
+        const float2 g = ll_unpack(gw[u], bf16);
         const size_t o = static_cast<size_t>(row) * row_words + i;
         if (p.residual_out) p.residual_out[o] = ll_pack(x[u][0], x[u][1], bf16);
         p.normed_out[o] = ll_pack(x[u][0] * inv * g.x, x[u][1] * inv * g.y, bf16);

@@ -12,6 +12,7 @@
 // a CTA each own 16 tokens of the tile and merge their running (max, sum, O) once at the end.
 #include "b200/host.h"
 #include "b200/primitives.cuh"
+#include "b200/attn_merge.cuh"
 
 #include <cstdlib>
 #include <cstring>
@@ -88,20 +89,11 @@ __device__ __forceinline__ void combine_by_last_cta(const DecodeParams& p, int b
   for (int i = threadIdx.x; i < nrows * kD; i += blockDim.x) {
     const int r = i / kD, c = i - r * kD;
     const size_t bh = static_cast<size_t>(b) * p.Hq + head0 + r;
-    float mg = -INFINITY;
-    for (int sp = 0; sp < p.S; ++sp) mg = fmaxf(mg, __ldcg(p.lse_part + bh * p.S + sp));
-    float lg = 0.f, og = 0.f;
-    for (int sp = 0; sp < p.S; ++sp) {
-      const float lse = __ldcg(p.lse_part + bh * p.S + sp);
-      if (lse == -INFINITY) continue;
-      const float w = __expf(lse - mg);
-      lg += w;
-      og += w * __ldcg(p.o_part + (bh * p.S + sp) * kD + c);
-    }
-    const float o = lg > 0.f ? og / lg : 0.f;
+    float o, lse;
+    merge_splits(p.lse_part + bh * p.S, 1, p.o_part + bh * p.S * kD + c, kD, p.S, o, lse);
     if (BF16) static_cast<__nv_bfloat16*>(p.out)[bh * kD + c] = __float2bfloat16(o);
     else static_cast<__half*>(p.out)[bh * kD + c] = __float2half(o);
-    if (c == 0 && p.out_lse) p.out_lse[bh] = lg > 0.f ? mg + logf(lg) : -INFINITY;
+    if (c == 0 && p.out_lse) p.out_lse[bh] = lse;
   }
 }
 
@@ -601,23 +593,14 @@ __global__ void __launch_bounds__(kD) decode_combine_kernel(const float* o_part,
   const int bh = blockIdx.x, c = threadIdx.x;
   griddep_launch_dependents();
   griddep_wait();
-  float mg = -INFINITY;
-  for (int s = 0; s < S; ++s) mg = fmaxf(mg, lse_part[bh * lse_stride_bh + s * lse_stride_s]);
-  float lg = 0.f, og = 0.f;
-  for (int s = 0; s < S; ++s) {
-    const float lse = lse_part[bh * lse_stride_bh + s * lse_stride_s];
-    if (lse == -INFINITY) continue;
-    const float w = __expf(lse - mg);
-    lg += w;
-    og += w * o_part[bh * o_stride_bh + s * o_stride_s + c];
-  }
-  const float o = lg > 0.f ? og / lg : 0.f;
+  float o, lse;
+  merge_splits(lse_part + bh * lse_stride_bh, lse_stride_s, o_part + bh * o_stride_bh + c, o_stride_s, S, o, lse);
   if (out) {
     if (BF16) static_cast<__nv_bfloat16*>(out)[static_cast<size_t>(bh) * kD + c] = __float2bfloat16(o);
     else static_cast<__half*>(out)[static_cast<size_t>(bh) * kD + c] = __float2half(o);
   }
   if (out_f32) out_f32[static_cast<size_t>(bh) * kD + c] = o;
-  if (c == 0 && out_lse) out_lse[bh] = lg > 0.f ? mg + logf(lg) : -INFINITY;
+  if (c == 0 && out_lse) out_lse[bh] = lse;
 }
 
 // Pipeline variant when the caller passes ring < 0: B200DIST_ATTN_V2 = 0 (two-stage CTA-wide pipeline), 3 or 6

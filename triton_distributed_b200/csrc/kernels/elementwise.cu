@@ -41,18 +41,38 @@ __global__ void __launch_bounds__(512) rmsnorm_kernel(const uint4* __restrict__ 
   __shared__ float red[32];
   const int nv = hidden / 8;
   griddep_launch_dependents();
+  // the gain is a weight (not an output of the kernel launched just before this one): it is fetched before the
+  // dependency wait, past L1, and stays in registers for every row
+  uint4 gv[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int i = threadIdx.x + u * blockDim.x;
+    gv[u] = i < nv ? __ldcg(gamma + i) : make_uint4(0, 0, 0, 0);
+  }
   griddep_wait();
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    // every load of the row is issued before the first store: residual_in may alias residual_out, so a load placed
+    // after a store has to wait for it, which would make this one memory round trip per chunk
+    uint4 xv[4], rv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = threadIdx.x + u * blockDim.x;
+      xv[u] = rv[u] = make_uint4(0, 0, 0, 0);
+      if (i < nv) {
+        xv[u] = x[static_cast<size_t>(r) * nv + i];
+        if (residual_in) rv[u] = residual_in[static_cast<size_t>(r) * nv + i];
+      }
+    }
     float v[4][8];
     float ss = 0.f;
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int i = threadIdx.x + u * blockDim.x;
       if (i < nv) {
-        unpack8<BF16>(x[static_cast<size_t>(r) * nv + i], v[u]);
+        unpack8<BF16>(xv[u], v[u]);
         if (residual_in) {
           float q[8];
-          unpack8<BF16>(residual_in[static_cast<size_t>(r) * nv + i], q);
+          unpack8<BF16>(rv[u], q);
 #pragma unroll
           for (int e = 0; e < 8; ++e) v[u][e] += q[e];
           const uint4 packed = pack8<BF16>(v[u]);
@@ -79,7 +99,7 @@ __global__ void __launch_bounds__(512) rmsnorm_kernel(const uint4* __restrict__ 
       const int i = threadIdx.x + u * blockDim.x;
       if (i < nv) {
         float g[8], o[8];
-        unpack8<BF16>(gamma[i], g);
+        unpack8<BF16>(gv[u], g);
 #pragma unroll
         for (int e = 0; e < 8; ++e) o[e] = v[u][e] * inv * g[e];
         y[static_cast<size_t>(r) * nv + i] = pack8<BF16>(o);
@@ -102,14 +122,18 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const uint2* __restri
                                                            int T, int Hq, int Hkv, float eps) {
   const int heads = Hq + 2 * Hkv;
   griddep_launch_dependents();
-  griddep_wait();
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (warp_global >= T * heads) return;
   const int t = warp_global / heads;
   const int h = warp_global - t * heads;
+  const uint2* gamma = h < Hq ? q_gamma : k_gamma;
+  // the gains are weights (not outputs of the kernel launched just before this one): fetched before the wait, past L1
+  const uint2 g = (gamma != nullptr && warp_global < T * heads && h < Hq + Hkv) ? __ldcg(gamma + lane) : make_uint2(0, 0);
+  griddep_wait();
+  if (warp_global >= T * heads) return;
   const uint2 raw = qkv[(static_cast<size_t>(t) * heads + h) * 32 + lane];
   const int64_t slot = slots ? slots[t] : t;
+  const int pos = positions[t];
   if (h >= Hq + Hkv) {  // v: straight copy into the cache
     if (slot >= 0) v_cache[(static_cast<size_t>(slot) * Hkv + (h - Hq - Hkv)) * 32 + lane] = raw;
     return;
@@ -120,12 +144,10 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const uint2* __restri
     const float2 b = BF16 ? unpack_bf16x2(raw.y) : unpack_f16x2(raw.y);
     x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
   }
-  const uint2* gamma = h < Hq ? q_gamma : k_gamma;
   if (gamma) {
     float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
     ss = warp_sum(ss);
     const float inv = rsqrtf(ss / 128.f + eps);
-    const uint2 g = gamma[lane];
     const float2 ga = BF16 ? unpack_bf16x2(g.x) : unpack_f16x2(g.x);
     const float2 gb = BF16 ? unpack_bf16x2(g.y) : unpack_f16x2(g.y);
     // round to the storage dtype after the norm, as a separate norm kernel would
@@ -135,7 +157,6 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const uint2* __restri
     x[0] = r0.x; x[1] = r0.y; x[2] = r1.x; x[3] = r1.y;
   }
   // neox rotation: out[i] = x[i] cos[i] - x[i+64] sin[i] (i < 64); out[i+64] = x[i+64] cos[i] + x[i] sin[i]
-  const int pos = positions[t];
   const int fi = (lane & 15) * 4;  // frequency index of this lane's first element
   const float4 c = *reinterpret_cast<const float4*>(cos_sin + static_cast<size_t>(pos) * 128 + fi);
   const float4 s = *reinterpret_cast<const float4*>(cos_sin + static_cast<size_t>(pos) * 128 + 64 + fi);

@@ -408,17 +408,18 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           __threadfence();
           float gf[16], uf[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
+          for (int j = 0; j < 16; ++j) {  // all loads first (one round trip), then the zeroing stores
             gf[j] = uf[j] = 0.f;
             if (j < p.M) {
-              float* gs = scratch + static_cast<size_t>(j) * kSkBN + et;
-              gf[j] = __ldcg(gs);
-              __stcg(gs, 0.f);
-              if (kDual) {
-                float* us = scratch + static_cast<size_t>(p.MB + j) * kSkBN + et;
-                uf[j] = __ldcg(us);
-                __stcg(us, 0.f);
-              }
+              gf[j] = __ldcg(scratch + static_cast<size_t>(j) * kSkBN + et);
+              if (kDual) uf[j] = __ldcg(scratch + static_cast<size_t>(p.MB + j) * kSkBN + et);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (j < p.M) {
+              __stcg(scratch + static_cast<size_t>(j) * kSkBN + et, 0.f);
+              if (kDual) __stcg(scratch + static_cast<size_t>(p.MB + j) * kSkBN + et, 0.f);
             }
           }
           finish_tile16<kDual>(p, sg.tile, et, gf, uf, ep_xch, ep_red);

@@ -17,6 +17,7 @@
 // low_latency_allgather.py:530-566, 762-777).
 #include "b200/host.h"
 #include "b200/primitives.cuh"
+#include "b200/attn_merge.cuh"
 
 #include <cstring>
 
@@ -42,18 +43,9 @@ __global__ void __launch_bounds__(kSpD) sp_decode_combine_kernel(const SpParams 
   const int bh = blockIdx.x, d = threadIdx.x;
   const int me = ctx.rank, world = ctx.world;
   // 1. local merge over splits
-  float mg = -INFINITY;
-  for (int s = 0; s < p.S; ++s) mg = fmaxf(mg, p.lse_part[static_cast<size_t>(bh) * p.S + s]);
-  float lg = 0.f, og = 0.f;
-  for (int s = 0; s < p.S; ++s) {
-    const float l = p.lse_part[static_cast<size_t>(bh) * p.S + s];
-    if (l == -INFINITY) continue;
-    const float w = __expf(l - mg);
-    lg += w;
-    og += w * p.o_part[(static_cast<size_t>(bh) * p.S + s) * kSpD + d];
-  }
-  const float o_mine = lg > 0.f ? og / lg : 0.f;
-  const float lse_mine = lg > 0.f ? mg + logf(lg) : -INFINITY;
+  float o_mine, lse_mine;
+  merge_splits(p.lse_part + static_cast<size_t>(bh) * p.S, 1, p.o_part + static_cast<size_t>(bh) * p.S * kSpD + d, kSpD, p.S,
+               o_mine, lse_mine);
   // 2. send packets: word d, and the LSE as word 128 (thread 0)
   const size_t base = (static_cast<size_t>(me) * p.BH + bh) * (kSpD + 1);
   if (world > 1) {

@@ -12,7 +12,6 @@ prefill kernel does many-token attention. The ``torch`` mode keeps the library c
 from __future__ import annotations
 
 import math
-import os
 
 import torch
 import torch.distributed as dist
@@ -42,12 +41,6 @@ def _set_cos_sin_cache(inv_freq: torch.Tensor, max_length: int) -> torch.Tensor:
 
 
 _rope_torch = golden.rope_torch
-# Whether the tensor-parallel decode step finishes the heads in the qkv projection's epilogue (B200DIST_FUSED_QKV=1) or
-# in the separate norm / rope / cache-write kernel (default). Measured at eight ranks: with ten 128-feature tiles per
-# rank the epilogue runs on the critical path of the last CTA of every tile and costs 0.24 ms per step more than the
-# extra launch, which programmatic dependent launch hides. (On one GPU the fused step is used, see models/qwen.py.)
-_FUSED_DECODE = os.environ.get("B200DIST_FUSED_QKV", "0") == "1"
-
 
 class TP_Attn:
 
@@ -164,31 +157,8 @@ class TP_Attn:
         return out.view(bsz, seqlen, -1)
 
     @torch.no_grad()
-    def decode_attn_fused(self, x2, cos_sin_cache, kv_cache, layer_idx, step, in_sumsq=None):
-        """Decode step for at most 16 tokens (one per sequence): the qkv projection finishes every head in its epilogue
-        (per-head RMSNorm, RoPE, q to a buffer, k / v into the cache), so attention follows directly. With `in_sumsq`
-        the input is ``h * gain`` of the block's RMSNorm and the projection applies ``rsqrt(sumsq / H + eps)`` itself.
-        Returns the attention output [B, Hq_local * 128] (before o_proj)."""
-        kp, vp = kv_cache.layer(layer_idx)
-        bsz = x2.shape[0]
-        q = torch.empty((bsz, self.q_heads_local, self.head_dim), dtype=x2.dtype, device=x2.device)
-        ep = ops.skinny_qkv_heads(step["pos"], step["slots"], cos_sin_cache, self.q_heads_local, self.kv_heads_local, q,
-                                  kp.view(-1, self.kv_heads_local, self.head_dim), vp.view(-1, self.kv_heads_local, self.head_dim),
-                                  self.q_norm_w, self.k_norm_w, self.eps)
-        if in_sumsq is not None:
-            ops.skinny_row_scale(in_sumsq, self.hidden, self.eps, base=ep)
-        ops.gemm_skinny(x2, self.wqkv, epilogue=ep)
-        splits = step.get("splits") or ops.choose_kv_splits(bsz, self.kv_heads_local, self.q_heads_local // self.kv_heads_local,
-                                                            kv_cache.max_length)
-        out = ops.decode_attention(q, kp, vp, step["kv_lens"], kv_cache.block_table, self.scale, 0.0, splits,
-                                   workspace=self._attn_ws)
-        return out.view(bsz, -1)
-
-    @torch.no_grad()
     def partial_fwd(self, x2, position_ids, cos_sin_cache, kv_cache, layer_idx, bsz, seqlen, step=None):
         """Native path without the final reduction: x2 [B*S, H] -> partial o_proj output [B*S, H]."""
-        if seqlen == 1 and bsz <= 16 and self.head_dim == 128 and step is not None and _FUSED_DECODE:
-            return ops.linear(self.decode_attn_fused(x2, cos_sin_cache, kv_cache, layer_idx, step), self.wo)
         qkv = ops.linear(x2, self.wqkv)
         o = self._attn_native(qkv, position_ids, cos_sin_cache, kv_cache, layer_idx, bsz, seqlen, step)
         return ops.linear(o, self.wo)

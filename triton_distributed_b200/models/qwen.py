@@ -15,7 +15,6 @@ only its slices. The vocabulary is sharded over ranks for ``lm_head`` (logits ar
 """
 from __future__ import annotations
 
-import os
 
 import torch
 import torch.distributed as dist
@@ -31,7 +30,6 @@ from .kv_cache import KV_Cache
 from .utils import logger
 from .weights import RandomSource, SafetensorsSource, WeightSource
 
-_FUSED_DECODE = os.environ.get("B200DIST_FUSED_DECODE", "1") != "0"   # single-GPU decode: epilogue-fused GEMMs
 
 
 class Qwen3Layer:
@@ -232,15 +230,10 @@ class Qwen3:
 
     @torch.no_grad()
     def _inference_AR(self, input_ids, position_ids, kv_cache):
-        """Returns (hidden, sumsq): with sumsq None, hidden [B, S, H] is final-normed; otherwise hidden is
-        ``h * final gain`` [B, 1, H] and the consumer applies ``rsqrt(sumsq / H + eps)`` per row."""
+        """Returns the final-normed hidden states [B, S, H]."""
         bsz, seqlen = input_ids.shape
-        T = bsz * seqlen
         step = {"pos": position_ids.reshape(-1).to(torch.int32), "slots": kv_cache.slots(position_ids),
                 "kv_lens": (position_ids[:, -1] + 1).to(torch.int32)}
-        if (self.world_size == 1 and seqlen == 1 and T <= 16 and self.arch.head_dim == 128 and not self.arch.num_experts
-                and _FUSED_DECODE):
-            return self._decode_fused_single_gpu(input_ids, kv_cache, step)
         residual = ops.embedding(input_ids.reshape(-1), self.embed_tokens)  # [T, H], becomes the residual stream
         x = ops.rmsnorm(residual, self.layers[0].input_norm_w, self.eps)
         for i, layer in enumerate(self.layers):
@@ -249,31 +242,7 @@ class Qwen3:
             part = layer.mlp.partial_fwd(x)
             nxt = self.layers[i + 1].input_norm_w if i + 1 < self.num_layers else self.norm_w
             x = self._reduce_norm(part, residual, nxt)
-        return x.view(bsz, seqlen, -1), None  # already final-normed
-
-    def _decode_fused_single_gpu(self, input_ids, kv_cache, step):
-        """One decode step on one GPU in five launches per layer. No normalisation kernel runs: the producer of the
-        residual stream (embedding, o_proj, down) also emits ``h * gain`` of the next RMSNorm and the row's sum of
-        squares, and the consumer projection multiplies its rows by ``rsqrt(sumsq / H + eps)``; the qkv projection
-        finishes the heads (norm, RoPE, cache write) in its epilogue."""
-        T, H, L = input_ids.numel(), self.arch.hidden_size, self.num_layers
-        dev = self.embed_tokens.device
-        if getattr(self, "_sumsq", None) is None:
-            self._sumsq = torch.zeros((2 * L + 1, 16), dtype=torch.float32, device=dev)
-        S = self._sumsq
-        S.zero_()
-        residual = torch.empty((T, H), dtype=self.dtype, device=dev)
-        xg = torch.empty_like(residual)   # h * gain of the next norm (input of the next projection)
-        ops.embedding(input_ids.reshape(-1), self.embed_tokens, out=residual, gamma=self.layers[0].input_norm_w,
-                      scaled_out=xg, sumsq_out=S[0])
-        for i, layer in enumerate(self.layers):
-            o = layer.attn.decode_attn_fused(xg, self.cos_sin_cache, kv_cache, i, step, in_sumsq=S[2 * i])
-            ops.gemm_skinny(o, layer.attn.wo, epilogue=ops.skinny_residual(residual, S[2 * i + 1], layer.post_norm_w, xg))
-            act = ops.gemm_skinny(xg, layer.mlp.gate_up_proj, swiglu=True,
-                                  epilogue=ops.skinny_row_scale(S[2 * i + 1], H, self.eps))
-            nxt = self.layers[i + 1].input_norm_w if i + 1 < L else self.norm_w
-            ops.gemm_skinny(act, layer.mlp.down_proj, epilogue=ops.skinny_residual(residual, S[2 * i + 2], nxt, xg))
-        return xg.view(T, 1, H), S[2 * L]
+        return x.view(bsz, seqlen, -1)  # already final-normed
 
     @torch.no_grad()
     def inference(self, input_ids: torch.Tensor, position_ids: torch.Tensor, kv_cache: KV_Cache,
@@ -282,12 +251,8 @@ class Qwen3:
         position (or the normed hidden states with ``wo_lm_head``). ``triton_dist`` mode needs B % world == 0."""
         bsz, seqlen = input_ids.shape
         native_gather = self.world_size > 1 and self.gather_ctx is not None and bsz <= self.gather_rows
-        sumsq = None
         if self.mode == "triton_dist_AR":
-            hidden, sumsq = self._inference_AR(input_ids, position_ids, kv_cache)
-            if sumsq is not None and wo_lm_head:
-                inv = torch.rsqrt(sumsq[:bsz] / hidden.shape[-1] + self.eps)
-                hidden, sumsq = (hidden.float() * inv[:, None, None]).to(hidden.dtype), None
+            hidden = self._inference_AR(input_ids, position_ids, kv_cache)
         else:
             native = self.mode == "triton_dist"
             hidden = ops.embedding(input_ids, self.embed_tokens) if native else F.embedding(input_ids, self.embed_tokens)
@@ -321,12 +286,10 @@ class Qwen3:
             # the head writes its vocabulary shard straight into this rank's slot of the symmetric gather buffer
             vloc = self.lm_head.shape[0]
             slot = self.logit_buf.view(-1)[: self.world_size * bsz * vloc].view(self.world_size, bsz, vloc)[self.rank]
-            ops.linear(last, self.lm_head, out=slot)  # (never with a pending row scale: that path is single-GPU)
+            ops.linear(last, self.lm_head, out=slot)
             gathered = self._gather_rows(self.logit_buf, bsz)
             local = gathered.permute(1, 0, 2).reshape(bsz, -1)
             return local[:, : self.arch.vocab_size].float().unsqueeze(1)
-        elif sumsq is not None:
-            local = ops.gemm_skinny(last, self.lm_head, epilogue=ops.skinny_row_scale(sumsq, last.shape[-1], self.eps))
         else:
             local = ops.linear(last, self.lm_head)
         if self.world_size > 1:

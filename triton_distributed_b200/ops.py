@@ -143,7 +143,11 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = Non
 
     With ``swiglu=True``, ``w`` is ``[gate; up]`` (2*I rows) and the result is ``silu(x gate^T) * (x up^T)`` [M, I].
     With ``epilogue`` (M <= 16) the finished tiles go through a fused epilogue instead of (or before) the plain store;
-    the qkv-heads and residual kinds write their own outputs and return None unless ``out`` is given.
+    the qkv-heads and residual kinds write their own outputs and return None unless ``out`` is given. The models do
+    not use the epilogues: a decode step chained through them (5 launches per layer instead of 9) measured 15.6 ms
+    against 13.8 ms on one B200 (Qwen3-32B, batch 8), because the epilogue runs on the one CTA that finishes each tile,
+    on the critical path, while the separate small kernels spread over the machine and start early under programmatic
+    dependent launch. They remain available for callers whose chain is launch-bound (no PDL, no graph).
     """
     _lib.require_cuda()
     _check_2d(x, "x"), _check_2d(w, "w")
