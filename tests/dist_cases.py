@@ -255,10 +255,12 @@ def ag_gemm_straggler():
     _ag_gemm_case(512, 1024, 1024, torch.bfloat16, iters=4, straggler=True)
 
 
-def _gemm_rs_case(M, N, K, dtype, iters=3):
+def _gemm_rs_case(M, N, K, dtype, iters=3, nvls=None):
     rank, world = _rank_world()
     torch.manual_seed(4321 + rank)
     ctx = create_gemm_rs_context(M, N, rank, world, world, dtype)
+    if nvls is not None:
+        ctx.nvls = nvls
     b = torch.randn(N, K, device="cuda", dtype=dtype) * 0.05
     for it in range(iters):
         a = torch.randn(M, K, device="cuda", dtype=dtype) * 0.5 * (rank + 1)
@@ -267,7 +269,7 @@ def _gemm_rs_case(M, N, K, dtype, iters=3):
         dist.reduce_scatter_tensor(ref, full)
         out = gemm_rs(a, b, ctx)
         torch.cuda.synchronize()
-        torch.testing.assert_close(out.float(), ref, rtol=6e-2, atol=6e-2 * world, msg=lambda s: f"gemm_rs M={M} N={N} K={K} it={it}: {s}")
+        torch.testing.assert_close(out.float(), ref, rtol=6e-2, atol=6e-2 * world, msg=lambda s: f"gemm_rs M={M} N={N} K={K} nvls={ctx.nvls} it={it}: {s}")
     ctx.finalize()
 
 
@@ -280,6 +282,12 @@ def gemm_rs_shapes():
     _gemm_rs_case(world, 512, 1024, torch.bfloat16)       # one row per rank (decode-like)
     _gemm_rs_case(64 * world, 512, 256, torch.float16)
     _gemm_rs_case(8192, 8192, 3584, torch.bfloat16, iters=2)
+    if get_heap().has_multicast:  # the same shapes with the reduction inside the switch, and both modes on one context
+        for nvls in (True, False):
+            _gemm_rs_case(512 * world, 1024, 512, torch.bfloat16, nvls=nvls)
+            _gemm_rs_case(100 * world, 776, 520, torch.bfloat16, nvls=nvls)
+            _gemm_rs_case(64 * world, 512, 256, torch.float16, nvls=nvls)
+        _gemm_rs_case(8192, 8192, 3584, torch.bfloat16, iters=2, nvls=True)
 
 
 @case
@@ -390,9 +398,10 @@ def sp_flash_decode_and_allgather_layer():
     group = U.TP_GROUP()
     heap = get_heap()
     Hq, Hkv, D, page = 64, 8, 128, 16
-    for use_mc in ([False, True] if heap.has_multicast else [False]):
+    # packets over plain stores, packets over multimem, and the bulk exchange (forced for every batch size)
+    for use_mc, bulk_rows in ([(False, None), (True, None), (False, 0)] if heap.has_multicast else [(False, None), (False, 0)]):
         layer = SpGQAFlashDecodeAttention(rank, 0, world, 1, Hq, Hkv, D, D, page_size=page, scale=1 / math.sqrt(D),
-                                          max_allowed_batch=8, use_multicast=use_mc)
+                                          max_allowed_batch=8, use_multicast=use_mc, bulk_rows=bulk_rows)
         for B, per_rank_len in ((1, 512), (8, 1000), (3, 37)):
             torch.manual_seed(9)  # same q on every rank
             q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
@@ -410,7 +419,7 @@ def sp_flash_decode_and_allgather_layer():
                 out = layer(q, kc, vc, all_lens, bt)
                 torch.cuda.synchronize()
                 want = ref.sp_flash_decode_ref(q, kc, vc, lens, bt, 1 / math.sqrt(D), 0.0, group)
-                torch.testing.assert_close(out.float(), want, rtol=5e-2, atol=2e-2, msg=lambda s_: f"sp decode B={B} mc={use_mc} it={it}: {s_}")
+                torch.testing.assert_close(out.float(), want, rtol=5e-2, atol=2e-2, msg=lambda s_: f"sp decode B={B} mc={use_mc} bulk={bulk_rows} it={it}: {s_}")
         layer.finalize()
     ag = AllGatherLayer(1, world, rank, max_buffer_size=1 << 20)
     for fn in (ag.forward_pull, ag.forward_push_2d, ag.forward_push_2d_ll, ag.forward_push_2d_ll_multimem, ag.forward_push_numa_2d_ll):

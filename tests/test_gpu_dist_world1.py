@@ -155,14 +155,16 @@ def test_fast_allgather_world1(dist1, mode):
     ctx.finalize()
 
 
-def test_sp_flash_decode_world1(dist1):
+@pytest.mark.parametrize("bulk_rows", [None, 0])
+def test_sp_flash_decode_world1(dist1, bulk_rows):
     import math
     from triton_distributed_b200 import ref
     from triton_distributed_b200.layers.nvidia import SpGQAFlashDecodeAttention
     from triton_distributed_b200.runtime.heap import get_heap
     torch.manual_seed(0)
     B, Hq, Hkv, D, page, L = 4, 32, 4, 128, 16, 700
-    layer = SpGQAFlashDecodeAttention(0, 0, 1, 1, Hq, Hkv, D, D, page_size=page, scale=1 / math.sqrt(D), max_allowed_batch=4)
+    layer = SpGQAFlashDecodeAttention(0, 0, 1, 1, Hq, Hkv, D, D, page_size=page, scale=1 / math.sqrt(D), max_allowed_batch=4,
+                                      bulk_rows=bulk_rows)
     nb = (L + page - 1) // page
     kc = torch.randn(B * nb, page, Hkv, D, device="cuda", dtype=torch.bfloat16)
     vc = torch.randn_like(kc)

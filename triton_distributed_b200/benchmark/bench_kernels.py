@@ -38,6 +38,7 @@ def main() -> None:
     ap.add_argument("--splits", type=int, default=0, help="decode_attn: KV splits (0 = the library's choice)")
     ap.add_argument("--layers", type=int, default=8, help="decode_step: transformer layers to build (64 = the full model)")
     ap.add_argument("--out", default=None, help="decode_step: text file for the table (rank 0)")
+    ap.add_argument("--model", default="Qwen/Qwen3-32B", help="decode_step: architecture name (see models/config.py)")
     args = ap.parse_args()
     if args.op == "decode_step":
         return decode_step_table(args)
@@ -197,10 +198,10 @@ def decode_step_table(args) -> None:
         os.environ.setdefault(k, v)
     group = utils.initialize_distributed(seed=0, heap_bytes=1 << 30)
     rank, world = dist.get_rank(), dist.get_world_size()
-    cfg = ModelConfig(model_name="Qwen/Qwen3-32B", max_length=2048 + 256, rank=rank, world_size=world,
+    cfg = ModelConfig(model_name=args.model, max_length=2048 + 256, rank=rank, world_size=world,
                       num_layers_override=args.layers)
     eng = Engine(cfg, temperature=0.6, top_p=0.95, group=group)
-    prompt = torch.randint(0, 151936, (8, 2048), device="cuda")
+    prompt = torch.randint(0, eng.model.arch.vocab_size, (8, 2048), device="cuda")
     eng.prepare_decode(eng.prefill(prompt))
     for _ in range(4):
         eng.decode_one()

@@ -108,6 +108,11 @@ __device__ __forceinline__ bool signal_and_wait(const SymmCtx& ctx, uint32_t* fl
   return __syncthreads_and(ok);
 }
 
+// Chunks per token row in the dispatch kernel: eight 128-channel blocks when quantising, 2 KB of bf16 otherwise.
+__host__ __device__ __forceinline__ int ep_dispatch_chunks(int H, int quant) {
+  return quant ? (H / 128 + 7) / 8 : (H * 2 + 2047) / 2048;
+}
+
 // One warp copies one row; eight (then four) independent 16-byte loads in flight per lane.
 __device__ __forceinline__ void copy_row_warp(uint8_t* dst, const uint8_t* src, int bytes, int lane) {
   int i = lane * 16;
@@ -178,7 +183,12 @@ __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const EpParams 
       *symm_at(ctx, p.recv_splits[par] + ctx.rank * p.E_local + (e - d * p.E_local), d) = p.counts[e];
     }
   const uint8_t* x = static_cast<const uint8_t*>(p.x);
-  for (int t = blockIdx.x * warps + warp; t < p.T; t += gridDim.x * warps) {
+  // A work item is one chunk of one token's row (1024 channels when quantising, 2 KB otherwise), so that a small batch
+  // still spreads over the whole grid and no warp walks a row in a chain of dependent round trips.
+  const int nchunk = ep_dispatch_chunks(p.H, p.quant);
+  const int items = p.T * nchunk;
+  for (int it = blockIdx.x * warps + warp; it < items; it += gridDim.x * warps) {
+    const int t = it / nchunk, chunk = it - t * nchunk;
     // destination of each of the k copies (lane k holds copy k)
     uint8_t* my_dst = nullptr;
     float* my_sdst = nullptr;
@@ -200,8 +210,8 @@ __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const EpParams 
     }
     const uint8_t* row = x + static_cast<size_t>(t) * p.H * 2;
     if (!p.quant) {
-      for (int base = 0; base < p.H * 2; base += 4 * 512) {  // four loads in flight, then k stores each; the trip
-        const int i0 = base + lane * 16;                      // count is the same for every lane (shuffles inside)
+      {  // four loads in flight, then k stores each
+        const int i0 = chunk * (4 * 512) + lane * 16;
         uint4 v[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u)
@@ -218,7 +228,8 @@ __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const EpParams 
       // each half-warp owns one 128-channel block per step (a lane holds 8 channels); four steps are loaded at once
       const int half = lane >> 4, hl = lane & 15;
       const int nblk = p.H / 128;
-      for (int b0 = 0; b0 < nblk; b0 += 8) {
+      {
+        const int b0 = chunk * 8;
         uint4 raw[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -293,21 +304,30 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const EpParams p
     src_rows[threadIdx.x] = n < p.max_m ? n : p.max_m;  // a sender that overflowed its area dropped the excess rows
   }
   __syncthreads();
-  // phase 1: return every received row's output to the rank it came from, same slot numbering
+  // phase 1: return every received row's output to the rank it came from, same slot numbering. The rows of all
+  // sources form one index space, so that every warp of the grid has a row (a loop over the sources with a warp
+  // stride inside would keep only rows-per-source warps busy at a time)
   const uint8_t* eo = static_cast<const uint8_t*>(p.expert_out);
   const int row_bytes = p.H * 2;
-  for (int s = 0; s < ctx.world; ++s) {
-    const int n = src_rows[s];
-    for (int i = blockIdx.x * warps + warp; i < n; i += gridDim.x * warps) {
-      const size_t from = (static_cast<size_t>(s) * p.max_m + i) * row_bytes;
-      const size_t to = (static_cast<size_t>(ctx.rank) * p.max_m + i) * row_bytes;
-      copy_row_warp(symm_at(ctx, p.comb[par] + to, s), eo + from, row_bytes, lane);
-    }
+  int total_rows = 0;
+  for (int s = 0; s < ctx.world; ++s) total_rows += src_rows[s];
+  for (int f = blockIdx.x * warps + warp; f < total_rows; f += gridDim.x * warps) {
+    int s = 0, i = f;
+    while (i >= src_rows[s]) i -= src_rows[s++];
+    const size_t from = (static_cast<size_t>(s) * p.max_m + i) * row_bytes;
+    const size_t to = (static_cast<size_t>(ctx.rank) * p.max_m + i) * row_bytes;
+    copy_row_warp(symm_at(ctx, p.comb[par] + to, s), eo + from, row_bytes, lane);
   }
   const bool ok = signal_and_wait(ctx, p.flags + par * kMaxRanks, p.sync + 2, epoch, true);
-  // phase 2: weighted sum of the k returned rows of every token
+  // phase 2: weighted sum of the k returned rows of every token. A work item is one 1 KB column chunk of one token
+  // (two 512-byte steps, the 2 x topk loads of a lane issued together): a whole row per warp would be row_bytes / 512
+  // dependent memory round trips on only T warps.
   if (ok) {
-    for (int t = blockIdx.x * warps + warp; t < p.T; t += gridDim.x * warps) {
+    constexpr int kChunk = 1024;
+    const int nchunk = (row_bytes + kChunk - 1) / kChunk;
+    const int items = p.T * nchunk;
+    for (int it = blockIdx.x * warps + warp; it < items; it += gridDim.x * warps) {
+      const int t = it / nchunk, c0 = (it - t * nchunk) * kChunk;
       const uint8_t* my_src = nullptr;
       float my_w = 1.f;
       if (lane < p.topk) {  // copies that the dispatch dropped (bad expert id, full receive area) contribute nothing
@@ -321,36 +341,47 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(const EpParams p
           }
         }
       }
-      for (int base = 0; base < row_bytes; base += 512) {  // same trip count for every lane (shuffles inside)
-        const int i = base + lane * 16;
-        const bool in = i < row_bytes;
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int k0 = 0; k0 < p.topk; k0 += 8) {  // up to eight copies in flight before the first add
-          uint4 v[8];
-          float wk[8];
+      float acc[2][8];
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const int k = k0 + u < p.topk ? k0 + u : k0;
-            const uint8_t* src = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_src), k));
-            const float w = __shfl_sync(0xffffffffu, my_w, k);
-            const bool use = in && k0 + u < p.topk && src != nullptr;
-            wk[u] = use ? w : 0.f;
-            v[u] = use ? ld_v4_relaxed_sys(src + i) : make_uint4(0, 0, 0, 0);
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[h][q] = 0.f;
+      for (int k0 = 0; k0 < p.topk; k0 += 8) {  // same trip count for every lane (shuffles inside)
+        uint4 v[2][8];
+        float wk[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int k = k0 + u < p.topk ? k0 + u : k0;
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_src), k));
+          const float w = __shfl_sync(0xffffffffu, my_w, k);
+          const bool use = k0 + u < p.topk && src != nullptr;
+          wk[u] = use ? w : 0.f;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int i = c0 + h * 512 + lane * 16;
+            v[h][u] = (use && i < row_bytes) ? ld_v4_relaxed_sys(src + i) : make_uint4(0, 0, 0, 0);
           }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
-            const uint32_t w4[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+            const uint32_t w4[4] = {v[h][u].x, v[h][u].y, v[h][u].z, v[h][u].w};
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const float2 f = unpack_bf16x2(w4[q]);
-              acc[2 * q] += wk[u] * f.x;
-              acc[2 * q + 1] += wk[u] * f.y;
+              acc[h][2 * q] += wk[u] * f.x;
+              acc[h][2 * q + 1] += wk[u] * f.y;
             }
           }
-        }
-        if (in)
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int i = c0 + h * 512 + lane * 16;
+        if (i < row_bytes)
           st_v4(static_cast<uint8_t*>(p.out) + static_cast<size_t>(t) * row_bytes + i,
-                make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7])));
+                make_uint4(pack_bf16x2(acc[h][0], acc[h][1]), pack_bf16x2(acc[h][2], acc[h][3]),
+                           pack_bf16x2(acc[h][4], acc[h][5]), pack_bf16x2(acc[h][6], acc[h][7])));
       }
     }
   }
@@ -481,7 +512,7 @@ B200_API int b200_ep_dispatch(const void* symm_ctx, const void* x, int T, int H,
   p.recv[0] = static_cast<uint8_t*>(recv0); p.recv[1] = static_cast<uint8_t*>(recv1);
   p.recv_scale[0] = static_cast<float*>(recv_scale0); p.recv_scale[1] = static_cast<float*>(recv_scale1);
   p.recv_splits[0] = splits0; p.recv_splits[1] = splits1; p.flags = flags; p.sync = sync;
-  ep_dispatch_kernel<<<ep_grid(T), kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(p, ctx);
+  ep_dispatch_kernel<<<ep_grid(T * ep_dispatch_chunks(H, quant)), kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(p, ctx);
   B200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }
@@ -508,7 +539,7 @@ B200_API int b200_ep_dispatch_planned(const void* symm_ctx, const void* x, int T
   p.recv_splits[0] = splits0; p.recv_splits[1] = splits1; p.flags = flags; p.sync = sync;
   p.plan_sorted_ids = sorted_ids; p.plan_tile_expert = tile_expert; p.plan_totals = totals;
   p.plan_rows_per_expert = rows_per_expert; p.plan_cap_rows = cap_rows; p.plan_block_m = block_m;
-  ep_dispatch_kernel<<<ep_grid(T), kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(p, ctx);
+  ep_dispatch_kernel<<<ep_grid(T * ep_dispatch_chunks(H, quant)), kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(p, ctx);
   B200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }

@@ -82,6 +82,8 @@ struct GemmParams {
   uint32_t* rs_base;     // local u32[world][rs_blocks]: counter value before this call
   int Mr_cap;
   int rs_blocks;
+  int rs_nvls;           // 1: partial tiles stay in this rank's own slots [owner][row][col]; the owner sums the
+                         // `world` copies with one multimem.ld_reduce per vector (the switch does the additions)
   void* out;             // [Mr, N]
 };
 
@@ -444,9 +446,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
             if (kMode == kRS) {
               const int owner = grow / p.Mr;
               const int lrow = grow - owner * p.Mr;
-              uint8_t* slot = static_cast<uint8_t*>(p.slots[par]) +
-                              ((static_cast<size_t>(ctx.rank) * p.Mr_cap + lrow) * p.N + gcol) * 2;
-              st_v4(symm_at(ctx, slot, owner), v);
+              if (p.rs_nvls) {
+                st_v4(static_cast<uint8_t*>(p.slots[par]) + ((static_cast<size_t>(owner) * p.Mr_cap + lrow) * p.N + gcol) * 2, v);
+              } else {
+                uint8_t* slot = static_cast<uint8_t*>(p.slots[par]) +
+                                ((static_cast<size_t>(ctx.rank) * p.Mr_cap + lrow) * p.N + gcol) * 2;
+                st_v4(symm_at(ctx, slot, owner), v);
+              }
             } else {
               st_v4(static_cast<uint8_t*>(p.C) + (static_cast<size_t>(grow) * p.ldc + gcol) * 2, v);
             }
@@ -496,6 +502,26 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constan
         }
         if (!__syncthreads_and(ok)) { failed = true; break; }
         ready_blk = j;
+      }
+      if (p.rs_nvls) {
+        // in-switch reduction: every rank kept its partial rows for this owner at the same heap offset, so one
+        // multimem load of that offset returns the sum over the ranks (fp32 accumulation inside the switch)
+        const uint8_t* mine = slots + (static_cast<size_t>(ctx.rank) * p.Mr_cap + lrow) * p.N * 2;
+        for (int v0 = threadIdx.x; v0 < vec_per_row; v0 += 4 * blockDim.x) {
+          uint4 x[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int v = v0 + u * blockDim.x;
+            if (v < vec_per_row)
+              x[u] = p.bf16 ? multimem_ld_reduce_bf16x8(mc_ptr(ctx, mine + v * 16)) : multimem_ld_reduce_f16x8(mc_ptr(ctx, mine + v * 16));
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int v = v0 + u * blockDim.x;
+            if (v < vec_per_row) st_v4(static_cast<uint8_t*>(p.out) + (static_cast<size_t>(lrow) * p.N + v * 8) * 2, x[u]);
+          }
+        }
+        continue;
       }
       for (int v0 = threadIdx.x; v0 < vec_per_row; v0 += 4 * blockDim.x) {
         uint4 x[4][kMaxRanks];
@@ -728,10 +754,11 @@ B200_API int b200_ag_gemm(const void* symm_ctx, const void* a_local, void* ag_bu
 // u32[world][rs_blocks]; sync: local u32[4]; all zero-initialised once.
 static int gemm_rs_impl(const void* symm_ctx, const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb,
                         int dtype, void* slots0, void* slots1, uint32_t* rs_cnt, uint32_t* rs_base, uint32_t* sync,
-                        int Mr_cap, int rs_blocks, int group_m, int max_ctas, void* stream) {
+                        int Mr_cap, int rs_blocks, int group_m, int max_ctas, int nvls, void* stream) {
   SymmCtx ctx;
   memcpy(&ctx, symm_ctx, sizeof(ctx));
   B200_REQUIRE(M % ctx.world == 0, "M (%d) must be divisible by the world size (%d)", M, ctx.world);
+  B200_REQUIRE(!nvls || ctx.mc_base != 0, "the in-switch reduction needs an NVLS multicast mapping");
   GemmParams p;
   memset(&p, 0, sizeof(p));
   int rc = fill_common(p, M, N, K, dtype, group_m);
@@ -746,6 +773,7 @@ static int gemm_rs_impl(const void* symm_ctx, const void* A, const void* B, void
   p.sync = sync;
   p.Mr_cap = Mr_cap;
   p.rs_blocks = rs_blocks;
+  p.rs_nvls = nvls ? 1 : 0;
   p.out = out;
   const bool pair = use_pair(M);
   set_tiles(p, pair, ((ctx.rank + 1) % ctx.world) * p.Mr);
@@ -759,11 +787,13 @@ static int gemm_rs_impl(const void* symm_ctx, const void* A, const void* B, void
   return launch_gemm<kRS>(pair, ta, ta, tb, p, ctx, grid, static_cast<cudaStream_t>(stream));
 }
 
+// nvls != 0: reduce in the switch (multimem.ld_reduce by the owner over every rank's local partial rows) instead of
+// storing the rows into the owner's per-source slots and summing them there.
 B200_API int b200_gemm_rs(const void* symm_ctx, const void* A, const void* B, void* out, int M, int N, int K, int lda,
                           int ldb, int dtype, void* slots0, void* slots1, uint32_t* rs_cnt, uint32_t* rs_base,
-                          uint32_t* sync, int Mr_cap, int rs_blocks, int group_m, int max_ctas, void* stream) {
+                          uint32_t* sync, int Mr_cap, int rs_blocks, int group_m, int max_ctas, int nvls, void* stream) {
   return gemm_rs_impl(symm_ctx, A, B, out, M, N, K, lda, ldb, dtype, slots0, slots1, rs_cnt, rs_base, sync, Mr_cap, rs_blocks,
-                      group_m, max_ctas, stream);
+                      group_m, max_ctas, nvls, stream);
 }
 
 // 1 = CTA pairs (256x256 tiles, cta_group::2), 0 = single CTAs (128x256), -1 = follow B200DIST_GEMM_2CTA.

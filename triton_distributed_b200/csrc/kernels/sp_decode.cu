@@ -112,9 +112,121 @@ __global__ void __launch_bounds__(kSpD) sp_decode_combine_kernel(const SpParams 
   if (threadIdx.x == 0) epoch_end(p.sync, p.sync + 1, epoch, gridDim.x);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Bulk variant for many rows (large batches). The packet protocol above sends one 8-byte packet per output word and
+// polls each of them; beyond about a thousand rows per rank the packet rate through the switch, not the bytes, sets the
+// time (2048 rows: 264 K packets per rank and call). Here the merged rows travel as plain coalesced 4-byte stores
+// (128 bytes per warp and peer, half the bytes of the packets), one release flag per rank follows them, and the
+// cross-rank combine runs after every rank's flag has arrived. Rows are 132 floats apart (128 outputs, the LSE, pad).
+// The grid is launched cooperatively (every CTA waits for the flags, so all of them must be resident) and walks the rows.
+constexpr int kSpRow = 132;
+
+struct SpBulkParams {
+  const float* o_part;
+  const float* lse_part;
+  int S, BH;
+  float* buf[2];     // symmetric, per parity: [world][BH][132] floats
+  uint32_t* flags;   // symmetric u32[2][kMaxRanks]: flags[parity][source] = epoch
+  uint32_t* sync;    // local u32[4]: epoch, done counter, arrival counter
+  void* out;
+  float* out_lse;
+  int bf16;
+};
+
+__global__ void __launch_bounds__(kSpD) sp_decode_combine_bulk_kernel(const SpBulkParams p, const SymmCtx ctx) {
+  __shared__ float lse_of[kMaxRanks];
+  const uint32_t epoch = epoch_begin(p.sync);
+  const int par = epoch & 1;
+  float* buf = p.buf[par];
+  uint32_t* flags = p.flags + par * kMaxRanks;
+  const int d = threadIdx.x;
+  const int me = ctx.rank, world = ctx.world;
+  // 1. merge this rank's splits of every row and store the result into slot [me] on every rank
+  for (int bh = blockIdx.x; bh < p.BH; bh += gridDim.x) {
+    float o_mine, lse_mine;
+    merge_splits(p.lse_part + static_cast<size_t>(bh) * p.S, 1, p.o_part + static_cast<size_t>(bh) * p.S * kSpD + d, kSpD, p.S,
+                 o_mine, lse_mine);
+    float* row = buf + (static_cast<size_t>(me) * p.BH + bh) * kSpRow;
+    for (int k = 0; k < world; ++k) {
+      const int peer = (me + k) % world;
+      float* dst = symm_at(ctx, row, peer);
+      dst[d] = o_mine;
+      if (d == 0) dst[kSpD] = lse_mine;
+    }
+  }
+  // 2. the last CTA to arrive releases flag[me] = epoch on every rank; every CTA then waits for all sources
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    fence_acq_rel_sys();
+    if (atom_add_acqrel_gpu(p.sync + 2, 1u) == gridDim.x - 1) {
+      p.sync[2] = 0;
+      fence_acq_rel_sys();
+      for (int r = 0; r < world; ++r) st_release_sys(symm_at(ctx, flags + me, r), epoch);
+    }
+  }
+  bool ok = true;
+  if (threadIdx.x < world) ok = wait_flag<WaitCmp::GE, true>(ctx, flags + threadIdx.x, epoch, threadIdx.x, __LINE__);
+  ok = __syncthreads_and(ok);
+  // 3. cross-rank combine from this rank's own memory (past L1: the rows were written by other GPUs)
+  if (ok) {
+    for (int bh = blockIdx.x; bh < p.BH; bh += gridDim.x) {
+      if (d < world) lse_of[d] = __ldcg(buf + (static_cast<size_t>(d) * p.BH + bh) * kSpRow + kSpD);
+      float o_r[kMaxRanks];
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        o_r[r] = r < world ? __ldcg(buf + (static_cast<size_t>(r) * p.BH + bh) * kSpRow + d) : 0.f;
+      __syncthreads();
+      float m = -INFINITY;
+      for (int r = 0; r < world; ++r) m = fmaxf(m, lse_of[r]);
+      float den = 0.f, num = 0.f;
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r) {
+        if (r < world && lse_of[r] != -INFINITY) {
+          const float w = __expf(lse_of[r] - m);
+          den += w;
+          num += w * o_r[r];
+        }
+      }
+      const float o = den > 0.f ? num / den : 0.f;
+      if (p.bf16) static_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(bh) * kSpD + d] = __float2bfloat16(o);
+      else static_cast<__half*>(p.out)[static_cast<size_t>(bh) * kSpD + d] = __float2half(o);
+      if (d == 0 && p.out_lse) p.out_lse[bh] = den > 0.f ? m + logf(den) : -INFINITY;
+      __syncthreads();  // lse_of is reused by the next row
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) epoch_end(p.sync, p.sync + 1, epoch, gridDim.x);
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+// Bulk exchange (see the kernel): buf0 / buf1 are the symmetric parity areas of at least world * BH * 132 floats each
+// (the packet areas of b200_sp_decode_combine are large enough), flags symmetric u32[2 * 8] zero-initialised once and
+// used by bulk calls only, sync local u32[4] zero-initialised once and used by bulk calls only.
+B200_API int b200_sp_decode_combine_bulk(const void* symm_ctx, const float* o_part, const float* lse_part, int BH, int S,
+                                         void* buf0, void* buf1, uint32_t* flags, uint32_t* sync, void* out, float* out_lse,
+                                         int dtype, void* stream) {
+  SymmCtx ctx;
+  memcpy(&ctx, symm_ctx, sizeof(ctx));
+  B200_REQUIRE(dtype == kBF16 || dtype == kF16, "sp decode combine writes bf16/f16");
+  if (BH == 0) return kOk;
+  SpBulkParams p;
+  memset(&p, 0, sizeof(p));
+  p.o_part = o_part; p.lse_part = lse_part; p.S = S; p.BH = BH;
+  p.buf[0] = static_cast<float*>(buf0); p.buf[1] = static_cast<float*>(buf1);
+  p.flags = flags; p.sync = sync; p.out = out; p.out_lse = out_lse; p.bf16 = dtype == kBF16;
+  int per_sm = 0;
+  B200_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sp_decode_combine_bulk_kernel, kSpD, 0));
+  per_sm = per_sm > 8 ? 8 : per_sm;
+  B200_REQUIRE(per_sm >= 1, "sp decode bulk kernel does not fit an SM");
+  const int cap = per_sm * sm_count();
+  const int grid = BH < cap ? BH : cap;
+  B200_CHECK_CUDA(launch_cooperative(sp_decode_combine_bulk_kernel, dim3(grid), dim3(kSpD), 0,
+                                     static_cast<cudaStream_t>(stream), p, ctx));
+  return kOk;
+}
 
 // o_part fp32 [BH, S, 128], lse_part fp32 [BH, S]: this rank's split partials. ll0 / ll1: symmetric u64 areas of
 // world * BH_cap * 129 packets (the kernel indexes them with this call's BH, which every rank must share).

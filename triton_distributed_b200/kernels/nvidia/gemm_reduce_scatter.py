@@ -6,10 +6,17 @@ stream scatters and ring-reduces; here the tcgen05 epilogue stores every output 
 the owner rank's slot over NVLink, bumps the owner's arrival counters with a release, and the same
 kernel finishes with the owner-side fp32 reduction of its rows (``csrc/kernels/gemm_sm100.cu``).
 The sum order is fixed (slot 0..r-1), so results are reproducible run to run.
+
+With an NVLS multicast mapping the reduction can run inside the switch instead (``ctx.nvls``, ``B200DIST_RS_NVLS``):
+the epilogue keeps every partial row in this rank's own memory at the owner's offset, and the owner issues one
+``multimem.ld_reduce`` per 16 bytes that returns the sum over the ranks (fp32 accumulation in the switch), the role of
+the multimem reduce-scatter in ``kernels/nvidia/moe_reduce_rs.py:1128-1152`` of the reference. The owner then receives
+one copy of its rows over NVLink instead of ``world - 1`` and sums nothing itself.
 """
 from __future__ import annotations
 
 import dataclasses
+import os
 
 import torch
 
@@ -17,6 +24,9 @@ from ... import _lib, ops
 from ..._lib import dtype_code, ptr, stream_ptr
 from ...runtime.heap import SymmHeap, get_heap
 
+
+
+_RS_NVLS_DEFAULT = "0"
 
 
 @dataclasses.dataclass
@@ -39,6 +49,7 @@ class GEMMReduceScatterTensorParallelContext:
     stages: int = 4
     group_m: int = 8
     max_ctas: int = 0
+    nvls: bool = False            # reduce in the switch (needs the heap's multicast mapping)
 
     def finalize(self) -> None:
         self.heap.sync_and_check(type(self).__name__)
@@ -63,7 +74,8 @@ def create_gemm_rs_context(max_M: int, N: int, rank: int, world_size: int, local
         rank=rank, world_size=world_size, local_world_size=local_world_size, max_M=max_M, N=N, output_dtype=output_dtype,
         heap=heap, slots=slots, rs_cnt=rs_cnt,
         rs_base=torch.zeros(world_size * rs_blocks, dtype=torch.int32, device="cuda"),
-        sync=torch.zeros(4, dtype=torch.int32, device="cuda"), rs_blocks=rs_blocks, group_m=GROUP_M)
+        sync=torch.zeros(4, dtype=torch.int32, device="cuda"), rs_blocks=rs_blocks, group_m=GROUP_M,
+        nvls=heap.has_multicast and world_size > 1 and os.environ.get("B200DIST_RS_NVLS", _RS_NVLS_DEFAULT) == "1")
     heap.barrier_all()
     torch.cuda.synchronize()
     return ctx
@@ -91,6 +103,6 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, ctx: GEMMReduceScatterTensorParall
         raise ValueError("out must be a contiguous [M / world, N] tensor of the context's dtype")
     _lib.call("b200_gemm_rs", ctx.heap.ctx, ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0),
               dtype_code(a.dtype), ptr(ctx.slots[0]), ptr(ctx.slots[1]), ptr(ctx.rs_cnt), ptr(ctx.rs_base), ptr(ctx.sync),
-              ctx.max_M // ctx.world_size, ctx.rs_blocks, ctx.group_m, ctx.max_ctas, stream_ptr())
+              ctx.max_M // ctx.world_size, ctx.rs_blocks, ctx.group_m, ctx.max_ctas, 1 if ctx.nvls else 0, stream_ptr())
     ops._count()
     return out

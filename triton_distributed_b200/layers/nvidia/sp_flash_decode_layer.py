@@ -6,11 +6,15 @@ page_size, scale, soft_cap, max_allowed_batch, thrink_buffer_threshold, stages)`
 ``forward(q, k_cache, v_cache, global_kv_lens, block_table)``).
 
 Two launches per call: the paged split-KV kernel over this rank's shard, then one kernel that merges the splits,
-exchanges the per-rank (O, LSE) partials as low-latency packets (NVLS multicast when available) and does the
-cross-rank LSE combine. The reference uses four kernels and a staged symmetric buffer that it resizes at run time;
-here the packet areas are sized once from ``max_allowed_batch``.
+exchanges the per-rank (O, LSE) partials and does the cross-rank LSE combine. Up to ``bulk_rows`` rows (batch x query
+heads; default 1024, ``B200DIST_SP_BULK_ROWS``) the exchange uses low-latency packets (NVLS multicast when available);
+above it the rows travel as plain coalesced stores behind one flag per rank, because the packet rate, not the bytes,
+bounds the packet form at large batches. The reference uses four kernels and a staged symmetric buffer that it resizes
+at run time; here the exchange areas are sized once from ``max_allowed_batch``.
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -24,7 +28,7 @@ class SpGQAFlashDecodeAttention:
     def __init__(self, rank: int, node: int, num_ranks: int, num_nodes: int, num_q_heads: int, num_kv_heads: int,
                  q_head_dim: int, v_head_dim: int, page_size: int = 1, scale: float = 1.0, soft_cap: float = 0.0,
                  max_allowed_batch: int = 1, thrink_buffer_threshold: int = 500, stages: int = 20,
-                 use_multicast: bool | None = None):
+                 use_multicast: bool | None = None, bulk_rows: int | None = None):
         if num_nodes != 1:
             raise NotImplementedError("single node only")
         if q_head_dim != 128 or v_head_dim != 128:
@@ -38,6 +42,12 @@ class SpGQAFlashDecodeAttention:
         self.bh_cap = max_allowed_batch * num_q_heads
         self.ll = [self.heap.create_tensor((num_ranks * self.bh_cap * 129,), torch.int64, align=1024) for _ in range(2)]
         self.sync = torch.zeros(4, dtype=torch.int32, device="cuda")
+        self.bulk_rows = int(os.environ.get("B200DIST_SP_BULK_ROWS", "1024")) if bulk_rows is None else bulk_rows
+        self.bulk = []
+        if self.bh_cap > self.bulk_rows:
+            self.bulk = [self.heap.create_tensor((num_ranks * self.bh_cap * 132,), torch.float32, align=1024) for _ in range(2)]
+            self.bulk_flags = self.heap.create_tensor((16,), torch.int32)
+            self.bulk_sync = torch.zeros(4, dtype=torch.int32, device="cuda")
         self._ws: dict = {}
         self.heap.barrier_all()
         torch.cuda.synchronize()
@@ -64,9 +74,14 @@ class SpGQAFlashDecodeAttention:
                   ptr(kv_lens), B, Hq, self.num_kv_heads, D, k_cache.shape[1], c_float(self.scale), c_float(self.soft_cap), S,
                   ptr(o_part), ptr(lse_part), None, None, None, dtype_code(q.dtype), -1, stream_ptr())
         out = torch.empty_like(q)
-        _lib.call("b200_sp_decode_combine", self.heap.ctx, ptr(o_part), ptr(lse_part), B * Hq, S, ptr(self.ll[0]),
-                  ptr(self.ll[1]), ptr(self.sync), ptr(out), None, dtype_code(q.dtype), 1 if self.use_multicast else 0,
-                  stream_ptr())
+        if self.bulk and B * Hq > self.bulk_rows:
+            _lib.call("b200_sp_decode_combine_bulk", self.heap.ctx, ptr(o_part), ptr(lse_part), B * Hq, S, ptr(self.bulk[0]),
+                      ptr(self.bulk[1]), ptr(self.bulk_flags), ptr(self.bulk_sync), ptr(out), None, dtype_code(q.dtype),
+                      stream_ptr())
+        else:
+            _lib.call("b200_sp_decode_combine", self.heap.ctx, ptr(o_part), ptr(lse_part), B * Hq, S, ptr(self.ll[0]),
+                      ptr(self.ll[1]), ptr(self.sync), ptr(out), None, dtype_code(q.dtype), 1 if self.use_multicast else 0,
+                      stream_ptr())
         ops._count(2)
         return out
 
@@ -74,6 +89,6 @@ class SpGQAFlashDecodeAttention:
 
     def finalize(self) -> None:
         self.heap.sync_and_check(type(self).__name__)
-        for t in self.ll:
+        for t in self.ll + self.bulk + ([self.bulk_flags] if self.bulk else []):
             self.heap.free(t)
-        self.ll = []
+        self.ll, self.bulk = [], []
