@@ -321,6 +321,33 @@ def moe_tp_ag_group_gemm_and_reduce_rs():
             torch.testing.assert_close(down.float(), ref.moe_reduce_rs_ref(x, w2, ids, wt, group).float(), rtol=5e-2,
                                        atol=5e-2 * world, msg=lambda s_: f"moe_reduce_rs Tr={Tr} it={it}: {s_}")
         ctx.finalize()
+        if K % 128 == 0 and N % 128 == 0:
+            # block-scaled fp8 forms of both fusions against the bf16 oracles fed with the dequantised operands
+            from triton_distributed_b200.kernels.nvidia import (ag_group_gemm_fp8, create_ag_group_gemm_fp8_context,
+                                                                moe_reduce_rs_fp8, quantize_fp8_rows,
+                                                                quantize_fp8_weight_blocks)
+
+            def deq_w(w8_, sw_):
+                n_ = w8_.shape[1]
+                return (w8_.float() * sw_.repeat_interleave(128, 1)[:, :n_].repeat_interleave(128, 2)).to(torch.bfloat16)
+
+            a8, sa = quantize_fp8_rows(a.float())
+            w18, sw1 = quantize_fp8_weight_blocks(w1.float())
+            w28, sw2 = quantize_fp8_weight_blocks(w2.float())
+            a_deq = ref.fp8_dequant_ref(a8, sa, dtype=torch.bfloat16)
+            fctx = create_ag_group_gemm_fp8_context(T, N, K, E, topk, torch.bfloat16, rank, world)
+            for it in range(3):
+                up8 = ag_group_gemm_fp8(a8, sa, w18, sw1, fctx, ids)
+                torch.cuda.synchronize()
+                torch.testing.assert_close(up8.float(), ref.ag_group_gemm_ref(a_deq, deq_w(w18, sw1), ids, group).float(),
+                                           rtol=3e-2, atol=3e-2, msg=lambda s_: f"ag_group_gemm_fp8 Tr={Tr} it={it}: {s_}")
+                x8, sx = quantize_fp8_rows(up8.float() * (0.5 + rank))
+                x_deq = ref.fp8_dequant_ref(x8, sx, dtype=torch.bfloat16)
+                down8 = moe_reduce_rs_fp8(x8, sx, w28, sw2, ids, wt, rctx)
+                torch.cuda.synchronize()
+                torch.testing.assert_close(down8.float(), ref.moe_reduce_rs_ref(x_deq, deq_w(w28, sw2), ids, wt, group).float(),
+                                           rtol=5e-2, atol=5e-2 * world, msg=lambda s_: f"moe_reduce_rs_fp8 Tr={Tr} it={it}: {s_}")
+            fctx.finalize()
         rctx.finalize()
 
 

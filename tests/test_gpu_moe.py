@@ -93,6 +93,48 @@ def test_ag_group_gemm_and_moe_reduce_rs_world1(dist1):
     rctx.finalize()
 
 
+def _dequant_weight_blocks(w8, sw):
+    E, N, K = w8.shape
+    scale = sw.repeat_interleave(128, 1)[:, :N].repeat_interleave(128, 2)
+    return w8.float() * scale
+
+
+def test_fp8_ag_group_gemm_and_moe_reduce_rs_world1(dist1):
+    """The block-scaled fp8 forms of both tensor-parallel MoE fusions against the dequantised fp32 products."""
+    from triton_distributed_b200 import ref
+    from triton_distributed_b200.kernels.nvidia import (ag_group_gemm_fp8, create_ag_group_gemm_fp8_context,
+                                                        create_moe_rs_context, moe_reduce_rs_fp8, quantize_fp8_rows,
+                                                        quantize_fp8_weight_blocks)
+    from triton_distributed_b200.runtime.heap import get_heap
+    torch.manual_seed(12)
+    T, topk, E, K, N, H = 256, 4, 16, 512, 384, 640
+    a8, sa = quantize_fp8_rows(torch.randn(T, K, device="cuda") * torch.rand(T, 1, device="cuda") * 3)
+    w8, sw = quantize_fp8_weight_blocks(torch.randn(E, N, K, device="cuda") * 0.05)
+    wt, ids = torch.topk(torch.softmax(torch.randn(T, E, device="cuda"), -1), topk, -1)
+    ids = ids.to(torch.int32)
+    a_deq = ref.fp8_dequant_ref(a8, sa, dtype=torch.float32)
+    want_up = ref.grouped_gemm_ref(a_deq.repeat_interleave(topk, 0), _dequant_weight_blocks(w8, sw), ids.reshape(-1).long())
+    ctx = create_ag_group_gemm_fp8_context(T, N, K, E, topk, torch.bfloat16, 0, 1)
+    for _ in range(3):
+        up = ag_group_gemm_fp8(a8, sa, w8, sw, ctx, ids)
+        torch.cuda.synchronize()
+        get_heap().check_status("ag_group_gemm_fp8")
+        torch.testing.assert_close(up.float(), want_up.float(), rtol=2e-2, atol=2e-2)
+    ctx.finalize()
+    x8, sx = quantize_fp8_rows(up.float())
+    w28, sw2 = quantize_fp8_weight_blocks(torch.randn(E, H, N, device="cuda") * 0.05)
+    x_deq = ref.fp8_dequant_ref(x8, sx, dtype=torch.float32)
+    pairs = ref.grouped_gemm_ref(x_deq, _dequant_weight_blocks(w28, sw2), ids.reshape(-1).long()) * wt.reshape(-1, 1)
+    want_down = pairs.view(T, topk, H).sum(1)
+    rctx = create_moe_rs_context(dist1, 1, T, H, E, topk, torch.bfloat16, torch.bfloat16)
+    for _ in range(3):
+        down = moe_reduce_rs_fp8(x8, sx, w28, sw2, ids, wt, rctx)
+        torch.cuda.synchronize()
+        get_heap().check_status("moe_reduce_rs_fp8")
+        torch.testing.assert_close(down.float(), want_down.float(), rtol=3e-2, atol=3e-2)
+    rctx.finalize()
+
+
 def test_ep_dispatch_combine_world1(dist1):
     from triton_distributed_b200 import ref
     from triton_distributed_b200.layers.nvidia import EPAll2AllLayer

@@ -20,6 +20,7 @@
 #include "b200/host.h"
 #include "b200/primitives.cuh"
 #include "b200/tcgen05.cuh"
+#include "b200/moe_rs_phases.cuh"
 
 #include <cstdlib>
 #include <cstring>
@@ -349,85 +350,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
   bool failed = *abort_flag != 0u;
   if (kMode == kGRS && !failed) {
     // all tiles of this rank are in p.out ([n_pairs, N], routing weight applied)
-    failed = !grid_barrier(ctx, p.sync + 3, epoch, gridDim.x);
-    const int vec_per_row = p.N / 8;
-    const uint8_t* out = static_cast<const uint8_t*>(p.out);
-    if (!failed) {
-      // phase 2: for every owner (starting after this rank), sum the k copies of each of its tokens and push the row
-      for (int s = 1; s <= ctx.world; ++s) {
-        int owner = ctx.rank + s;
-        if (owner >= ctx.world) owner -= ctx.world;
-        int my_rows = 0;
-        for (int lrow = blockIdx.x; lrow < p.Tr; lrow += gridDim.x) {
-          ++my_rows;
-          const int t = owner * p.Tr + lrow;
-          uint8_t* dst = static_cast<uint8_t*>(p.slots[par]) + (static_cast<size_t>(ctx.rank) * p.Tr_cap + lrow) * p.N * 2;
-          uint8_t* rdst = symm_at(ctx, dst, owner);
-          for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
-            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            const uint8_t* src = out + (static_cast<size_t>(t) * p.topk * p.ldo + v * 8) * 2;
-            for (int k0 = 0; k0 < p.topk; k0 += 4) {  // four copies in flight before the first add
-              uint4 x[4];
-#pragma unroll
-              for (int u = 0; u < 4; ++u)
-                x[u] = k0 + u < p.topk ? ld_v4_relaxed_sys(src + static_cast<size_t>(k0 + u) * p.ldo * 2) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const uint32_t xs[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  const float2 f = p.bf16 ? unpack_bf16x2(xs[q]) : unpack_f16x2(xs[q]);
-                  acc[2 * q] += f.x;
-                  acc[2 * q + 1] += f.y;
-                }
-              }
-            }
-            uint4 o;
-            if (p.bf16) o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
-            else o = make_uint4(pack_f16x2(acc[0], acc[1]), pack_f16x2(acc[2], acc[3]), pack_f16x2(acc[4], acc[5]), pack_f16x2(acc[6], acc[7]));
-            st_v4(rdst + static_cast<size_t>(v) * 16, o);
-          }
-        }
-        __syncthreads();
-        if (threadIdx.x == 0 && my_rows > 0) {
-          fence_acq_rel_sys();
-          red_add_release_sys(symm_at(ctx, p.rs_cnt + ctx.rank, owner), static_cast<uint32_t>(my_rows));
-        }
-      }
-      // phase 3: this rank's rows have arrived from everyone -> sum the slots
-      bool ok = true;
-      if (threadIdx.x < ctx.world)
-        ok = wait_flag<WaitCmp::GE, true>(ctx, p.rs_cnt + threadIdx.x, p.rs_base[threadIdx.x] + static_cast<uint32_t>(p.Tr),
-                                          threadIdx.x, __LINE__);
-      failed = !__syncthreads_and(ok);
-      if (!failed) {
-        const uint8_t* slots = static_cast<const uint8_t*>(p.slots[par]);
-        for (int lrow = blockIdx.x; lrow < p.Tr; lrow += gridDim.x) {
-          for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
-            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            uint4 x[kMaxRanks];
-#pragma unroll
-            for (int s = 0; s < kMaxRanks; ++s)
-              x[s] = s < ctx.world ? ld_v4_relaxed_sys(slots + ((static_cast<size_t>(s) * p.Tr_cap + lrow) * p.N + v * 8) * 2)
-                                   : make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int s = 0; s < kMaxRanks; ++s) {
-              const uint32_t xs[4] = {x[s].x, x[s].y, x[s].z, x[s].w};
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const float2 f = p.bf16 ? unpack_bf16x2(xs[q]) : unpack_f16x2(xs[q]);
-                acc[2 * q] += f.x;
-                acc[2 * q + 1] += f.y;
-              }
-            }
-            uint4 o;
-            if (p.bf16) o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
-            else o = make_uint4(pack_f16x2(acc[0], acc[1]), pack_f16x2(acc[2], acc[3]), pack_f16x2(acc[4], acc[5]), pack_f16x2(acc[6], acc[7]));
-            st_v4(static_cast<uint8_t*>(p.rs_out) + (static_cast<size_t>(lrow) * p.N + v * 8) * 2, o);
-          }
-        }
-      }
-    }
+    MoeRsArgs rs;
+    rs.gemm_out = p.out; rs.ldo = p.ldo; rs.N = p.N; rs.topk = p.topk; rs.Tr = p.Tr; rs.Tr_cap = p.Tr_cap; rs.bf16 = p.bf16;
+    rs.slots = p.slots[par]; rs.rs_cnt = p.rs_cnt; rs.rs_base = p.rs_base; rs.rs_out = p.rs_out; rs.barrier_ctr = p.sync + 3;
+    failed = !moe_rs_phases(ctx, rs, epoch);
   }
 
   // ---------------------------------------------------------------------- teardown

@@ -9,11 +9,12 @@ from .flash_decode import (get_triton_combine_kv_algo_info, gqa_fwd_batch_decode
                            kernel_inter_rank_gqa_fwd_batch_decode_combine_kv)
 from .gemm_reduce_scatter import create_gemm_rs_context, gemm_rs
 from .low_latency_allgather import create_fast_allgather_context, fast_allgather
-from .allgather_group_gemm import ag_group_gemm, create_ag_group_gemm_context, grouped_gemm
+from .allgather_group_gemm import (ag_group_gemm, ag_group_gemm_fp8, create_ag_group_gemm_context,
+                                   create_ag_group_gemm_fp8_context, grouped_gemm)
 from .grouped_gemm_fp8 import (grouped_gemm_fp8, grouped_gemm_fp8_planned, quantize_fp8_rows,
                                quantize_fp8_weight_blocks)
 from .moe_reduce_rs import (create_moe_rs_context, create_moe_rs_context_colwise, moe_reduce_rs, moe_reduce_rs_colwise,
-                            moe_reduce_rs_rowise, select_experts)
+                            moe_reduce_rs_fp8, moe_reduce_rs_rowise, select_experts)
 from .moe_utils import (calc_gather_index_from_scatter_index, calc_gather_scatter_index, calc_gather_scatter_index_triton,
                         calc_scatter_index_torch, create_sort_plan, histogram_by_expert, histogram_by_expert_torch,
                         histogram_by_expert_triton, moe_sort, order_tiles, reduce_topk, reduce_topk_non_tma, reduce_topk_tma)

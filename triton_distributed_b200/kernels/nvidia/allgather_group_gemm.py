@@ -118,6 +118,93 @@ def ag_group_gemm(a: torch.Tensor, b: torch.Tensor, ctx: MoEAllGatherGroupGEMMTe
     return out
 
 
+@dataclasses.dataclass
+class MoEAllGatherGroupGEMMFp8Context:
+    """Buffers of :func:`ag_group_gemm_fp8`. A token row travels as ``K`` e4m3 bytes followed by its ``K / 128`` fp32
+    scales (``pitch`` bytes, a multiple of 16), so that one gather moves both."""
+    rank: int
+    num_ranks: int
+    max_ntokens: int
+    N_per_rank: int
+    K: int
+    num_experts: int
+    topk: int
+    out_dtype: torch.dtype
+    pitch: int
+    heap: SymmHeap
+    symm_workspaces: list[torch.Tensor]
+    symm_ready: torch.Tensor
+    rank_cnt: torch.Tensor
+    rank_flag: torch.Tensor
+    sync: torch.Tensor
+    staging: torch.Tensor          # local [max_ntokens / r, pitch] bytes: this rank's packed rows
+    plans: dict
+
+    def plan_for(self, ntokens: int) -> MoeSortPlan:
+        if ntokens not in self.plans:
+            self.plans[ntokens] = create_sort_plan(ntokens * self.topk, self.topk, self.num_experts, 128, 1)
+        return self.plans[ntokens]
+
+    def finalize(self) -> None:
+        self.heap.sync_and_check(type(self).__name__)
+        for t in self.symm_workspaces + [self.symm_ready]:
+            self.heap.free(t)
+        self.symm_workspaces = []
+
+
+def create_ag_group_gemm_fp8_context(max_ntokens: int, N_per_rank: int, K: int, num_experts: int, topk: int,
+                                     out_dtype: torch.dtype, rank: int, num_ranks: int) -> MoEAllGatherGroupGEMMFp8Context:
+    heap = get_heap()
+    if num_ranks != heap.world:
+        raise ValueError("AG + grouped GEMM spans the ranks of the symmetric heap (single node)")
+    if K % 128:
+        raise ValueError("K must be a multiple of 128 (one activation scale per 128 channels)")
+    pitch = (K + K // 32 + 15) // 16 * 16
+    ws = [heap.create_tensor((max_ntokens, pitch), torch.uint8, align=1024) for _ in range(2)]
+    ready = heap.create_tensor((16,), torch.int32)
+    z = lambda n: torch.zeros(n, dtype=torch.int32, device="cuda")  # noqa: E731
+    staging = torch.zeros((max_ntokens // num_ranks, pitch), dtype=torch.uint8, device="cuda")
+    ctx = MoEAllGatherGroupGEMMFp8Context(rank, num_ranks, max_ntokens, N_per_rank, K, num_experts, topk, out_dtype, pitch,
+                                          heap, ws, ready, z(16), z(16), z(4), staging, {})
+    heap.barrier_all()
+    torch.cuda.synchronize()
+    return ctx
+
+
+def ag_group_gemm_fp8(a8: torch.Tensor, a_scale: torch.Tensor, w8: torch.Tensor, w_scale: torch.Tensor,
+                      ctx: MoEAllGatherGroupGEMMFp8Context, full_topk_ids: torch.Tensor,
+                      out: torch.Tensor | None = None) -> torch.Tensor:
+    """Block-scaled fp8 form of :func:`ag_group_gemm`: a8 e4m3 [ntokens / r, K] with fp32 scales a_scale
+    [ntokens / r, K / 128] (this rank's tokens), w8 e4m3 [E, N / r, K] with w_scale [E, ceil(N / r / 128), K / 128];
+    full_topk_ids int32 [ntokens, topk]. The gather moves one byte per channel plus the scales, half of what the bf16
+    kernel moves. Returns [ntokens * topk, N / r] in the context's 16-bit dtype."""
+    Tr, K = a8.shape
+    T = Tr * ctx.num_ranks
+    E, N, _ = w8.shape
+    if T > ctx.max_ntokens or K != ctx.K or full_topk_ids.shape != (T, ctx.topk):
+        raise ValueError("problem does not fit the context")
+    if a8.element_size() != 1 or w8.element_size() != 1:
+        raise ValueError("a8 / w8 must be 1-byte tensors")
+    if tuple(a_scale.shape) != (Tr, K // 128) or tuple(w_scale.shape) != (E, (N + 127) // 128, K // 128):
+        raise ValueError("scale shapes do not match the operands")
+    plan = ctx.plan_for(T)
+    moe_sort(full_topk_ids.to(torch.int32).contiguous(), plan, tokens_per_rank=Tr)
+    order = order_tiles(plan, ctx.rank, ctx.num_ranks, 0) if _reorder_pays(ctx, T, E, N, K, 1) else None
+    # pack [row bytes | row scales] once: the peers pull whole packed rows
+    stage = ctx.staging[:Tr]
+    stage[:, :K].copy_(a8.view(torch.uint8))
+    stage[:, K:K + K // 32].copy_(a_scale.contiguous().view(torch.uint8).view(Tr, K // 32))
+    if out is None:
+        out = torch.empty((T * ctx.topk, N), dtype=ctx.out_dtype, device=a8.device)
+    _lib.call("b200_ag_grouped_gemm_fp8", ctx.heap.ctx, ptr(stage), ctx.pitch, ptr(ctx.symm_workspaces[0]),
+              ptr(ctx.symm_workspaces[1]), Tr, ctx.topk, ptr(w8.contiguous()), ptr(w_scale.contiguous()), E, N, K,
+              ptr(plan.sorted_ids), ptr(plan.tile_expert), ptr(order), ptr(plan.totals), plan.max_tiles, ptr(out),
+              out.stride(0), ptr(ctx.symm_ready), ptr(ctx.rank_cnt), ptr(ctx.rank_flag), ptr(ctx.sync), dtype_code(out.dtype),
+              stream_ptr())
+    ops._count()
+    return out
+
+
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, topk_ids: torch.Tensor, a_per_pair: bool = False,
                  row_scale: torch.Tensor | None = None, plan: MoeSortPlan | None = None) -> torch.Tensor:
     """Local grouped GEMM: out[t * topk + k] = a[t (or pair)] @ w[topk_ids[t, k]].T (* row_scale). w [E, N, K]."""

@@ -130,3 +130,34 @@ def create_moe_rs_context_colwise(rank: int, world_size: int, local_world_size: 
 def moe_reduce_rs_colwise(x: torch.Tensor, weights: torch.Tensor, choosed_experts: torch.Tensor, expert_weight: torch.Tensor,
                           ctx: MoEReduceRSContext, n_chunks: int = 2, config=None) -> torch.Tensor:
     return moe_reduce_rs(x, _weights_nk(weights, x.shape[1]), choosed_experts, expert_weight, ctx)
+
+
+def moe_reduce_rs_fp8(x8: torch.Tensor, x_scale: torch.Tensor, w8: torch.Tensor, w_scale: torch.Tensor,
+                      topk_ids: torch.Tensor, topk_weight: torch.Tensor, ctx: MoEReduceRSContext,
+                      out: torch.Tensor | None = None) -> torch.Tensor:
+    """Block-scaled fp8 form of :func:`moe_reduce_rs`: x8 e4m3 [T * topk, K / r] with fp32 scales x_scale
+    [T * topk, K / r / 128] (what ``ops.silu_mul_fp8`` writes), w8 e4m3 [E, N, K / r] with one fp32 scale per 128 x 128
+    block, w_scale [E, ceil(N / 128), K / r / 128]. Same kernel phases after the GEMM (top-k sum, push, owner reduce);
+    the output has the context's 16-bit dtype. Returns [T / r, N]."""
+    n_pairs, K = x8.shape
+    T = n_pairs // ctx.topk
+    E, N, _ = w8.shape
+    if T > ctx.max_token_num or N != ctx.hidden_dim or T % ctx.world_size != 0:
+        raise ValueError("problem does not fit the context")
+    if x8.element_size() != 1 or w8.element_size() != 1 or K % 128:
+        raise ValueError("x8 / w8 must be 1-byte tensors with K a multiple of 128")
+    if tuple(w_scale.shape) != (E, (N + 127) // 128, K // 128) or tuple(x_scale.shape) != (n_pairs, K // 128):
+        raise ValueError("scale shapes do not match the operands")
+    plan = ctx.plan_for(T)
+    moe_sort(topk_ids.to(torch.int32).contiguous(), plan)
+    Tr = T // ctx.world_size
+    if out is None:
+        out = torch.empty((Tr, N), dtype=ctx.dtype, device=x8.device)
+    scale = topk_weight.reshape(-1).float().contiguous()
+    _lib.call("b200_grouped_gemm_fp8_rs", ctx.heap.ctx, ptr(x8), x8.stride(0), ptr(x_scale.contiguous()), x_scale.stride(0),
+              ptr(w8.contiguous()), ptr(w_scale.contiguous()), E, N, K, Tr, ctx.topk, ptr(plan.sorted_ids), ptr(plan.tile_expert),
+              None, ptr(plan.totals), plan.max_tiles, ptr(scale), ptr(ctx.gemm_out), ptr(ctx.slots[0]), ptr(ctx.slots[1]),
+              ctx.max_token_num // ctx.world_size, ptr(ctx.rs_cnt), ptr(ctx.rs_base), ptr(ctx.sync), ptr(out),
+              dtype_code(out.dtype), stream_ptr())
+    ops._count()
+    return out
