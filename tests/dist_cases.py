@@ -495,6 +495,15 @@ def reduce_scatter_op_and_moe_layers():
         torch.cuda.synchronize()
         torch.testing.assert_close(got.float(), want[rank * per:(rank + 1) * per].float(), rtol=5e-2, atol=0.1 * world)
     tp.finalize()
+    # the same layer with both projections on the block-scaled fp8 fused kernels
+    tp8 = TP_MoE(rank, world, group, topk, True, fp8=True)
+    tp8._init_parameters(gate, torch.cat([wgu[:, :I][:, sl], wgu[:, I:][:, sl]], dim=1), wdn[:, :, sl])
+    tp8._init_ctx(T)
+    for it in range(2):
+        got = tp8.dist_triton_fwd(x[rank * per:(rank + 1) * per].contiguous())
+        torch.cuda.synchronize()
+        torch.testing.assert_close(got.float(), want[rank * per:(rank + 1) * per].float(), rtol=0.12, atol=0.3 * world)
+    tp8.finalize()
     # EP-MoE layer: every rank owns E / world whole experts
     for fp8, fp8_experts in ((False, False), (True, False), (True, True)):
         ep = EP_MoE(rank, world, group, E, topk, H, per, torch.bfloat16, True, fp8_dispatch=fp8, fp8_experts=fp8_experts)

@@ -219,6 +219,24 @@ def bench_tp_moe(args, group, rows):
     row["speedup"] = row["grouped_nccl_us"] / row["ours_us"]
     rows.append(row)
     ctx.finalize()
+    # block-scaled fp8 forms (the down-projection needs its K shard to be a multiple of 128)
+    from ..kernels.nvidia import (ag_group_gemm_fp8, create_ag_group_gemm_fp8_context, moe_reduce_rs_fp8, quantize_fp8_rows,
+                                  quantize_fp8_weight_blocks)
+    a8, sa = quantize_fp8_rows(a.float())
+    w18, sw1 = quantize_fp8_weight_blocks(w1.float())
+    fctx = create_ag_group_gemm_fp8_context(T, 2 * il, H, E, topk, torch.bfloat16, rank, world)
+    row = {"op": "ag_group_gemm_fp8", "world": world, "tokens": T, "experts": E, "topk": topk, "N": 2 * il, "K": H}
+    row["ours_us"] = _time(lambda: ag_group_gemm_fp8(a8, sa, w18, sw1, fctx, ids), args.iters, args.warmup, group)
+    row["bf16_fused_us"] = rows[-2]["ours_us"]
+    rows.append(row)
+    fctx.finalize()
+    if il % 128 == 0:
+        x8, sx = quantize_fp8_rows(act.float())
+        w28, sw2 = quantize_fp8_weight_blocks(w2.float())
+        row = {"op": "moe_reduce_rs_fp8", "world": world, "tokens": T, "experts": E, "topk": topk, "N": H, "K": il}
+        row["ours_us"] = _time(lambda: moe_reduce_rs_fp8(x8, sx, w28, sw2, ids, wt, rctx), args.iters, args.warmup, group)
+        row["bf16_fused_us"] = rows[-2]["ours_us"]
+        rows.append(row)
     rctx.finalize()
 
 

@@ -45,10 +45,15 @@ def _experts_torch(x, ids, w, w_gate_up, w_down):
 
 class TP_MoE:
 
-    def __init__(self, rank: int = 0, world_size: int = 8, group=None, topk: int = 8, norm_topk_prob: bool = True):
+    def __init__(self, rank: int = 0, world_size: int = 8, group=None, topk: int = 8, norm_topk_prob: bool = True,
+                 fp8: bool = False):
+        """fp8: the sequence-sharded forward runs both projections on the block-scaled fp8 fused kernels (tokens are
+        quantised per 128 channels and gathered as bytes, the SwiGLU kernel quantises the activations); needs the hidden
+        size and the local intermediate size to be multiples of 128."""
         self.rank, self.world_size, self.group = rank, world_size, group
         self.topk, self.norm_topk_prob = topk, norm_topk_prob
-        self.ag_ctx = self.rs_ctx = self.ar_ctx = None
+        self.fp8 = fp8
+        self.ag_ctx = self.rs_ctx = self.ar_ctx = self.ag_ctx8 = None
         self.ar_method = None
 
     def _init_parameters(self, gate: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor):
@@ -59,18 +64,28 @@ class TP_MoE:
         self.num_experts, _, self.hidden = w_gate_up.shape
         self.inter_local = w_gate_up.shape[1] // 2
         self.dtype = w_gate_up.dtype
+        if self.fp8:
+            if self.hidden % 128 or self.inter_local % 128:
+                raise ValueError("fp8 TP_MoE needs hidden and intermediate / world to be multiples of 128")
+            from ...kernels.nvidia.grouped_gemm_fp8 import quantize_fp8_weight_blocks
+            self.w_gate_up8, self.w_gate_up_scale = quantize_fp8_weight_blocks(self.w_gate_up)
+            self.w_down8, self.w_down_scale = quantize_fp8_weight_blocks(self.w_down)
 
     def _init_ctx(self, max_tokens: int):
         self.ag_ctx = create_ag_group_gemm_context(max_tokens, 2 * self.inter_local, self.hidden, self.num_experts, self.topk,
                                                    self.dtype, self.rank, self.world_size)
         self.rs_ctx = create_moe_rs_context(self.group, self.world_size, max_tokens, self.hidden, self.num_experts, self.topk,
                                             self.dtype, self.dtype)
+        if self.fp8:
+            from ...kernels.nvidia.allgather_group_gemm import create_ag_group_gemm_fp8_context
+            self.ag_ctx8 = create_ag_group_gemm_fp8_context(max_tokens, 2 * self.inter_local, self.hidden, self.num_experts,
+                                                            self.topk, self.dtype, self.rank, self.world_size)
 
     def finalize(self):
-        for c in (self.ag_ctx, self.rs_ctx):
+        for c in (self.ag_ctx, self.rs_ctx, self.ag_ctx8):
             if c is not None:
                 c.finalize()
-        self.ag_ctx = self.rs_ctx = None
+        self.ag_ctx = self.rs_ctx = self.ag_ctx8 = None
 
     def route(self, x: torch.Tensor):
         """Router on the native kernels: (ids int32 [T, topk], weights fp32 [T, topk])."""
@@ -114,6 +129,14 @@ class TP_MoE:
             dist.all_gather_into_tensor(full_ids, ids, group=self.group)
             dist.all_gather_into_tensor(full_w, w, group=self.group)
             ids, w = full_ids, full_w
+        if self.fp8:
+            from ...kernels.nvidia.allgather_group_gemm import ag_group_gemm_fp8
+            from ...kernels.nvidia.grouped_gemm_fp8 import quantize_fp8_rows
+            from ...kernels.nvidia.moe_reduce_rs import moe_reduce_rs_fp8
+            x8, sx = quantize_fp8_rows(x_local)
+            up = ag_group_gemm_fp8(x8, sx, self.w_gate_up8, self.w_gate_up_scale, self.ag_ctx8, ids)
+            act8, act_scale = ops.silu_mul_fp8(up)
+            return moe_reduce_rs_fp8(act8, act_scale, self.w_down8, self.w_down_scale, ids, w, self.rs_ctx)
         up = ag_group_gemm(x_local, self.w_gate_up, self.ag_ctx, ids)
         act = ops.silu_mul(up)
         return moe_reduce_rs(act, self.w_down, ids, w, self.rs_ctx)
