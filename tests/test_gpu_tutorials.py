@@ -14,6 +14,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     ("02_overlapping_allgather_gemm.py", ["--m", "1024", "--n", "2048", "--k", "1024"]),
     ("03_overlapping_gemm_reduce_scatter.py", ["--m", "1024", "--n", "1024", "--k", "2048"]),
     ("04_ep_all2all_fp8.py", []),
+    ("05_allgather.py", []),
+    ("06_reduce_scatter.py", []),
 ])
 def test_tutorial_runs(script, args):
     env = dict(os.environ)
