@@ -228,6 +228,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __shared__ uint32_t tmem_slot;
   __shared__ uint32_t abort_word;
   __shared__ uint32_t last_flag;
+  __shared__ uint32_t armed_count;  // k-blocks whose stage barrier the weight producer has armed
   __shared__ float ep_xch[16 * kSkBN];  // fused epilogues: partner exchange of the rotary embedding
   __shared__ float ep_red[4 * 16];      //                  per-warp partial sums of the per-head norm
   volatile uint32_t* abort_flag = &abort_word;
@@ -257,6 +258,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       mbar_init(tempty_bar + i, 4);
     }
     abort_word = 0;
+    armed_count = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmX);
@@ -270,36 +272,61 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
   if (warp == 0) {
     if (elect_one()) {
-      // The weights do not depend on the previous kernel, the activations do: the first ring of weight tiles is
-      // requested before griddep_wait(), the matching activation tiles right after it.
-      uint32_t stage = 0, phase = 0;
+      // Weight producer. The weights do not depend on the previous kernel, so this thread never waits for it: it
+      // arms each stage's barrier for the whole stage (weights + activations), requests the weight tiles and
+      // publishes how many k-blocks are armed. The activation tiles are requested by the thread below.
+      uint32_t stage = 0, phase = 0, armed = 0;
       int u = u_begin;
       Segment sg;
-      bool ok = true, waited = false;
-      int ndef = 0;
-      int def_kb[kSkMaxStages];
-      auto flush_deferred = [&]() {
-        griddep_wait();
-        stamp(2);  // the previous kernel has completed: activations may be loaded
-        fence_proxy_async();
-        waited = true;
-        for (int j = 0; j < ndef; ++j)
-          tma_load_2d(smem + j * p.stage_bytes + kW * kSkWBytes, &tmX, full_bar + j, def_kb[j] * kSkBK, 0);
-      };
+      bool ok = true;
       while (ok && next_segment(p, u, u_end, sg)) {
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
-          if (!waited && ndef == p.stages) flush_deferred();
           if (!mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, timeout_ns)) { ok = false; break; }
           uint8_t* s = smem + stage * p.stage_bytes;
           mbar_expect_tx(full_bar + stage, p.stage_bytes);
           tma_load_2d(s, &tmW, full_bar + stage, kb * kSkBK, sg.tile * kSkBN);
           if (kDual) tma_load_2d(s + kSkWBytes, &tmW, full_bar + stage, kb * kSkBK, p.up_row0 + sg.tile * kSkBN);
-          if (waited) tma_load_2d(s + kW * kSkWBytes, &tmX, full_bar + stage, kb * kSkBK, 0);
-          else def_kb[ndef++] = kb;
+          ++armed;
+          asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(&armed_count)), "r"(armed) : "memory");
           if (++stage == static_cast<uint32_t>(p.stages)) { stage = 0; phase ^= 1; }
         }
       }
-      if (!waited) flush_deferred();
+    }
+    __syncwarp();
+  } else if (warp == 3) {
+    if (elect_one()) {
+      // Activation producer. The activations are the previous kernel's output: wait for it once, then request the
+      // tile of every k-block as soon as the weight producer has armed its stage. Because the two producers are
+      // separate threads, a CTA that starts late (the previous kernel is already complete) gets its activations at
+      // once instead of after the whole first ring of weight requests, and a CTA that starts early keeps prefetching
+      // weights for as long as the previous kernel runs.
+      griddep_wait();
+      stamp(2);  // the previous kernel has completed: activations may be loaded
+      fence_proxy_async();
+      uint32_t stage = 0, done = 0;
+      int u = u_begin;
+      Segment sg;
+      bool ok = true;
+      while (ok && next_segment(p, u, u_end, sg)) {
+        for (int kb = sg.kb0; kb < sg.kb1 && ok; ++kb) {
+          uint64_t t0 = 0;
+          uint32_t spins = 0;
+          while (true) {
+            uint32_t seen;
+            asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(seen) : "r"(smem_u32(&armed_count)) : "memory");
+            if (seen > done) break;
+            if ((++spins & 255u) == 0u) {
+              const uint64_t now = globaltimer_ns();
+              if (t0 == 0) t0 = now;
+              if (*abort_flag != 0u || now - t0 > timeout_ns) { *abort_flag = 1u; ok = false; break; }
+            }
+          }
+          if (!ok) break;
+          tma_load_2d(smem + stage * p.stage_bytes + kW * kSkWBytes, &tmX, full_bar + stage, kb * kSkBK, 0);
+          ++done;
+          if (++stage == static_cast<uint32_t>(p.stages)) stage = 0;
+        }
+      }
     }
     __syncwarp();
   } else if (warp == 1) {

@@ -18,7 +18,7 @@
 
 using namespace b200;
 
-__global__ void reduce_scatter_kernel(const SymmCtx ctx, float* partial, float* out, int n, uint32_t* flags, uint32_t epoch,
+__global__ void __launch_bounds__(512) reduce_scatter_kernel(const SymmCtx ctx, float* partial, float* out, int n, uint32_t* flags, uint32_t epoch,
                                       int use_multimem, uint32_t* ok_out) {
   const bool ok = barrier_all_block(ctx, flags, epoch);
   if (threadIdx.x == 0) *ok_out = ok ? 1u : 0u;
@@ -53,7 +53,7 @@ extern "C" __attribute__((visibility("default"))) int tutorial_reduce_scatter(co
   memcpy(&ctx, symm_ctx, sizeof(ctx));
   if (n % 4 != 0) return -1;
   if (use_multimem && ctx.mc_base == 0) return -2;  // no NVLS mapping on this heap
-  reduce_scatter_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+  reduce_scatter_kernel<<<1, 512, 0, static_cast<cudaStream_t>(stream)>>>(
       ctx, static_cast<float*>(partial), static_cast<float*>(out), n, static_cast<uint32_t*>(flags), epoch, use_multimem,
       static_cast<uint32_t*>(ok_out));
   return static_cast<int>(cudaGetLastError());
