@@ -4,7 +4,7 @@
 #   bash launch.sh [--nproc N] [--port P] script.py [script args]       e.g.  bash launch.sh --nproc 8 bench.py --gpus 8
 #   bash launch.sh --nproc 2 -m triton_distributed_b200.benchmark.bench_comm_gemm
 #
-# N defaults to the number of visible GPUs. Environment passed through: B200DIST_* (see DESIGN.md), NCCL_*.
+# N defaults to the number of visible GPUs. Environment passed through unchanged: the B200DIST_* toggles and NCCL_*.
 set -euo pipefail
 nproc=""
 port="${MASTER_PORT:-29500}"
