@@ -132,11 +132,27 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const Fp8Groupe
   // Roles by warpgroup, each starting with its register budget: the promotion warps hold 128 fp32 accumulators per
   // thread, everybody else gives registers back.
   if (warp < 4) {
-    if (kMode == kFAG) asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");  // the communication warps keep 8 vectors in flight
+    if (kMode == kFAG) asm volatile("setmaxnreg.dec.sync.aligned.u32 120;");  // the communication warps keep 16 vectors in flight
     else asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
     // ------------------------------------------------------------------ W producer (TMA)
-    if (elect_one()) {
+    const bool w_producer = elect_one();
+    if (!w_producer && lane == 31 && kMode == kFAG) {
+      // AG: ONE thread per CTA watches the per-source completion flags in global memory, in the order the shards are
+      // pulled, and republishes them in shared memory for the 128 gather threads. (With every gather thread polling the
+      // flags itself, ~19 K threads hammered one L2 line and starved the communication warps of this very GPU: the
+      // local copy and the pull ran at a fifth of their speed.)
+      for (int step = 1; step < ctx.world; ++step) {
+        int src = ctx.rank + step;
+        if (src >= ctx.world) src -= ctx.world;
+        if (!wait_flag<WaitCmp::EQ, false>(ctx, p.rank_flag + src, epoch, src, __LINE__)) {
+          *abort_flag = 1u;
+          break;
+        }
+        asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(ready_cache + src)), "r"(epoch) : "memory");
+      }
+    }
+    if (w_producer) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
@@ -184,6 +200,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const Fp8Groupe
     const size_t row_bytes = static_cast<size_t>(p.lda);
     uint8_t* buf = p.ag_buf[par];
     constexpr int kRows = 8;
+    constexpr int kInFlight = 16;  // 16-byte loads in flight per thread: 64 threads x 148 CTAs keep ~2.4 MB on the wire
     const int nch = (p.Tr + kRows - 1) / kRows;
     for (int g = blockIdx.x; g < nch * ctx.world; g += gridDim.x) {
       const int step = g / nch, c = g - step * nch;
@@ -204,13 +221,13 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const Fp8Groupe
         from = symm_at(ctx, buf + off, src);
       }
       const size_t nvec = nrows * row_bytes / 16;
-      for (size_t i = ct; i < nvec; i += 64 * 8) {
-        uint4 v[8];
+      for (size_t i = ct; i < nvec; i += 64 * kInFlight) {
+        uint4 v[kInFlight];
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
+        for (int u = 0; u < kInFlight; ++u)
           if (i + u * 64 < nvec) v[u] = ld_v4_relaxed_sys(reinterpret_cast<const uint4*>(from) + i + u * 64);
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
+        for (int u = 0; u < kInFlight; ++u)
           if (i + u * 64 < nvec) st_v4(reinterpret_cast<uint4*>(buf + off) + i + u * 64, v[u]);
       }
       f8_comm_bar();
@@ -345,11 +362,13 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const Fp8Groupe
           const int src = src_row / p.Tr;
           local_row = src == ctx.rank;  // read in place: no copy, no flag
           if (!local_row && src != last_src) {
-            uint32_t seen;  // a shard that any thread of this CTA has seen complete is not polled in global memory again
-            asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(seen) : "r"(smem_u32(ready_cache + src)) : "memory");
-            if (seen != epoch) {
-              ok = wait_flag<WaitCmp::EQ, false>(ctx, p.rank_flag + src, epoch, src, __LINE__);
-              if (ok) asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(ready_cache + src)), "r"(epoch) : "memory");
+            // the shard's completion is republished in shared memory by the CTA's flag watcher (warp 0)
+            uint32_t seen, spins = 0;
+            while (true) {
+              asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(seen) : "r"(smem_u32(ready_cache + src)) : "memory");
+              if (seen == epoch) break;
+              __nanosleep(100);
+              if ((++spins & 63u) == 0u && *abort_flag != 0u) { ok = false; break; }
             }
             last_src = src;
           }

@@ -135,7 +135,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
 
   if (warp == 0) {
     // ------------------------------------------------------------------ W producer (TMA)
-    if (elect_one()) {
+    const bool w_producer = elect_one();
+    if (!w_producer && lane == 31 && kMode == kGAG) {
+      // AG: ONE thread per CTA watches the per-source completion flags in global memory, in the order the shards are
+      // pulled, and republishes them in shared memory for the 128 gather threads. (With every gather thread polling the
+      // flags itself, ~19 K threads hammered one L2 line and starved the communication warps of this very GPU: the
+      // local copy and the pull ran at a fifth of their speed.)
+      for (int step = 1; step < ctx.world; ++step) {
+        int src = ctx.rank + step;
+        if (src >= ctx.world) src -= ctx.world;
+        if (!wait_flag<WaitCmp::EQ, false>(ctx, p.rank_flag + src, epoch, src, __LINE__)) {
+          *abort_flag = 1u;
+          break;
+        }
+        asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(ready_cache + src)), "r"(epoch) : "memory");
+      }
+    }
+    if (w_producer) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
@@ -185,6 +201,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
       const size_t row_bytes = static_cast<size_t>(p.K) * 2;
       uint8_t* buf = static_cast<uint8_t*>(p.ag_buf[par]);
       constexpr int kRows = 8;
+      constexpr int kInFlight = 16;  // 16-byte loads in flight per thread: 64 threads x 148 CTAs keep ~2.4 MB on the wire
       const int nch = (p.Tr + kRows - 1) / kRows;
       for (int g = blockIdx.x; g < nch * ctx.world; g += gridDim.x) {
         const int step = g / nch, c = g - step * nch;
@@ -206,14 +223,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
           from = symm_at(ctx, buf + off, src);
         }
         const size_t nvec = nrows * row_bytes / 16;
-        // eight 16-byte loads in flight per lane: ~1.2 MB per GPU, what a 2 us NVLink round trip needs at link speed
-        for (size_t i = ct; i < nvec; i += 64 * 8) {
-          uint4 v[8];
+        for (size_t i = ct; i < nvec; i += 64 * kInFlight) {
+          uint4 v[kInFlight];
 #pragma unroll
-          for (int u = 0; u < 8; ++u)
+          for (int u = 0; u < kInFlight; ++u)
             if (i + u * 64 < nvec) v[u] = ld_v4_relaxed_sys(reinterpret_cast<const uint4*>(from) + i + u * 64);
 #pragma unroll
-          for (int u = 0; u < 8; ++u)
+          for (int u = 0; u < kInFlight; ++u)
             if (i + u * 64 < nvec) st_v4(reinterpret_cast<uint4*>(buf + off) + i + u * 64, v[u]);
         }
         gcomm_bar();
@@ -310,12 +326,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
           // local rows start at once (the copy into the symmetric buffer is for the peers only)
           local_row = src == ctx.rank;
           if (!local_row && src != last_src) {
-            // a shard that any thread of this CTA has seen complete is not polled in global memory again
-            uint32_t seen;
-            asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(seen) : "r"(smem_u32(ready_cache + src)) : "memory");
-            if (seen != epoch) {
-              ok = wait_flag<WaitCmp::EQ, false>(ctx, p.rank_flag + src, epoch, src, __LINE__);
-              if (ok) asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(ready_cache + src)), "r"(epoch) : "memory");
+            // the shard's completion is republished in shared memory by the CTA's flag watcher (warp 0)
+            uint32_t seen, spins = 0;
+            while (true) {
+              asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(seen) : "r"(smem_u32(ready_cache + src)) : "memory");
+              if (seen == epoch) break;
+              __nanosleep(100);
+              if ((++spins & 63u) == 0u && *abort_flag != 0u) { ok = false; break; }
             }
             last_src = src;
           }
