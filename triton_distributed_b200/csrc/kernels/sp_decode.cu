@@ -219,7 +219,7 @@ B200_API int b200_sp_decode_combine_bulk(const void* symm_ctx, const float* o_pa
   p.flags = flags; p.sync = sync; p.out = out; p.out_lse = out_lse; p.bf16 = dtype == kBF16;
   int per_sm = 0;
   B200_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sp_decode_combine_bulk_kernel, kSpD, 0));
-  per_sm = per_sm > 8 ? 8 : per_sm;
+  per_sm = per_sm > 2 ? 2 : per_sm;  // every CTA waits on the same flags: a few hundred CTAs keep the polling off that L2 line's back
   B200_REQUIRE(per_sm >= 1, "sp decode bulk kernel does not fit an SM");
   const int cap = per_sm * sm_count();
   const int grid = BH < cap ? BH : cap;
