@@ -290,3 +290,81 @@ def test_ag_pull_gather_without_parity_is_caught():
     with pytest.raises(Violation):
         for seed in range(300):
             _ag_pull_model(3, calls=6, rng=random.Random(seed), use_parity=False)
+
+
+# ---------------------------------------------------------------------------------------------- decode GEMM stage ring
+def _two_producer_ring_model(stages, kblocks, rng, publish_after_arming=True):
+    """The stage ring of the decode GEMM (`csrc/kernels/gemm_skinny_sm100.cu`): a weight producer arms the barrier of a
+    stage for the whole stage and requests the weight tile, then publishes how many k-blocks are armed; an activation
+    producer (which first waits for the previous kernel) requests the activation tile of k-block i once `armed > i`; the
+    MMA thread consumes a stage when both tiles have landed and then frees it. Checked: an activation tile never lands in
+    a stage whose barrier is not armed for that k-block (it would complete the transaction count of the wrong phase or
+    overwrite a tile that is still being multiplied), and every k-block is multiplied with its own two tiles."""
+    armed_for = [None] * stages      # k-block the stage's barrier is armed for (None = free)
+    w_in = [None] * stages           # k-block whose weight tile sits in the stage
+    x_in = [None] * stages           # k-block whose activation tile sits in the stage
+    state = {"armed": 0, "dependency": False, "consumed": 0}
+
+    def weights():
+        for i in range(kblocks):
+            s = i % stages
+            while armed_for[s] is not None:      # wait on the stage's empty barrier
+                yield False
+            if publish_after_arming:
+                armed_for[s] = i                 # expect_tx: the barrier now counts the bytes of both tiles
+                yield True
+                state["armed"] = i + 1           # published right after the weight tile was requested
+                yield True
+                w_in[s] = i                      # the weight tile lands (any time after the request)
+            else:                                # broken variant: the count is published before the barrier is armed
+                state["armed"] = i + 1
+                yield True
+                armed_for[s] = i
+                yield True
+                w_in[s] = i
+            yield True
+
+    def activations():
+        while not state["dependency"]:           # griddepcontrol.wait
+            yield False
+        for i in range(kblocks):
+            s = i % stages
+            while state["armed"] <= i:
+                yield False
+            if armed_for[s] != i:
+                raise Violation(f"activation tile of k-block {i} requested into a stage armed for {armed_for[s]}")
+            x_in[s] = i
+            yield True
+
+    def mma():
+        for i in range(kblocks):
+            s = i % stages
+            while not (armed_for[s] == i and w_in[s] == i and x_in[s] == i):   # full barrier: both tiles of this phase
+                yield False
+            yield True                                                          # the MMAs read the stage
+            if w_in[s] != i or x_in[s] != i:
+                raise Violation(f"stage {s} changed under the MMA of k-block {i}")
+            armed_for[s] = None                                                 # tcgen05.commit on the empty barrier
+            state["consumed"] += 1
+            yield True
+
+    def previous_kernel():
+        for _ in range(rng.randrange(0, 3 * stages)):
+            yield True
+        state["dependency"] = True
+        yield True
+
+    _run([weights(), activations(), mma(), previous_kernel()], rng)
+    assert state["consumed"] == kblocks
+
+
+@pytest.mark.parametrize("stages,kblocks", [(1, 5), (3, 7), (6, 6), (13, 40)])
+def test_decode_gemm_two_producer_ring_is_safe_under_random_schedules(stages, kblocks):
+    for seed in range(300):
+        _two_producer_ring_model(stages, kblocks, random.Random(seed))
+
+
+def test_decode_gemm_ring_publishing_before_arming_is_caught():
+    with pytest.raises(Violation):
+        for seed in range(300):
+            _two_producer_ring_model(2, 12, random.Random(seed), publish_after_arming=False)
