@@ -135,6 +135,8 @@ def test_allreduce_method_names_and_auto_choice():
     assert get_auto_allreduce_method(8 << 10, has_multicast=True, world=8) is AllReduceMethod.OneShot
     assert get_auto_allreduce_method(8 << 20, has_multicast=True, world=8) is AllReduceMethod.TwoShot_Multimem
     assert get_auto_allreduce_method(8 << 20, has_multicast=True, world=2) is AllReduceMethod.OneShot   # same bytes as two-shot
+    assert get_auto_allreduce_method(2 << 20, has_multicast=True, world=4) is AllReduceMethod.OneShot
+    assert get_auto_allreduce_method(8 << 20, has_multicast=True, world=4) is AllReduceMethod.TwoShot_Multimem
     assert get_auto_allreduce_method(32 << 20, has_multicast=True, world=2) is AllReduceMethod.TwoShot
     assert get_auto_allreduce_method(8 << 10, has_multicast=False, world=8) is AllReduceMethod.OneShot
     assert get_auto_allreduce_method(8 << 20, has_multicast=False, world=8) is AllReduceMethod.TwoShot

@@ -89,16 +89,16 @@ def create_allreduce_ctx(workspace_nbytes: int, rank: int, world_size: int, loca
 
 
 def get_auto_allreduce_method(nbytes: int, has_multicast: bool | None = None, world: int | None = None) -> AllReduceMethod:
-    """Small messages are latency-bound: the one-shot push (one meeting point) wins up to 1 MB at eight ranks and up to
-    8 MB at two, where it moves no more data than a two-shot. Beyond that the two-shot forms are bandwidth-bound, with
-    the reduction in the switch when the heap has an NVLS mapping and more than two ranks share it. (Measured at 2 and
-    8 GPUs; the NVLS one-shot never beat the plain one-shot on this machine.)"""
+    """Small messages are latency-bound: the one-shot push (one meeting point) wins up to 1 MB at eight ranks, 2 MB at
+    four and 8 MB at two, where it moves no more data than a two-shot. Beyond that the two-shot forms are
+    bandwidth-bound, with the reduction in the switch when the heap has an NVLS mapping and more than two ranks share
+    it. (Measured at 2, 4 and 8 GPUs; the NVLS one-shot never beat the plain one-shot on this machine.)"""
     heap = get_heap() if (has_multicast is None or world is None) else None
     if has_multicast is None:
         has_multicast = heap.has_multicast
     if world is None:
         world = heap.world
-    if nbytes <= (8 << 20 if world <= 2 else 1 << 20):
+    if nbytes <= (8 << 20 if world <= 2 else 2 << 20 if world <= 4 else 1 << 20):
         return AllReduceMethod.OneShot
     return AllReduceMethod.TwoShot_Multimem if (has_multicast and world > 2) else AllReduceMethod.TwoShot
 
