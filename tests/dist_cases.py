@@ -316,10 +316,14 @@ def moe_tp_ag_group_gemm_and_reduce_rs():
             torch.testing.assert_close(up.float(), ref.ag_group_gemm_ref(a, w1, ids, group).float(), rtol=2e-2, atol=2e-2,
                                        msg=lambda s_: f"ag_group_gemm Tr={Tr} it={it}: {s_}")
             x = (up * (0.5 + rank)).contiguous()
-            down = moe_reduce_rs(x, w2, ids, wt, rctx)
-            torch.cuda.synchronize()
-            torch.testing.assert_close(down.float(), ref.moe_reduce_rs_ref(x, w2, ids, wt, group).float(), rtol=5e-2,
-                                       atol=5e-2 * world, msg=lambda s_: f"moe_reduce_rs Tr={Tr} it={it}: {s_}")
+            want_down = ref.moe_reduce_rs_ref(x, w2, ids, wt, group).float()
+            for nvls in ([False, True] if get_heap().has_multicast else [False]):  # slots at the owner / sum in the switch
+                rctx.nvls = nvls
+                down = moe_reduce_rs(x, w2, ids, wt, rctx)
+                torch.cuda.synchronize()
+                torch.testing.assert_close(down.float(), want_down, rtol=5e-2, atol=5e-2 * world,
+                                           msg=lambda s_: f"moe_reduce_rs Tr={Tr} nvls={nvls} it={it}: {s_}")
+            rctx.nvls = False
         ctx.finalize()
         if K % 128 == 0 and N % 128 == 0:
             # block-scaled fp8 forms of both fusions against the bf16 oracles fed with the dequantised operands

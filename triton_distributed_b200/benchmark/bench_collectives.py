@@ -215,6 +215,10 @@ def bench_tp_moe(args, group, rows):
 
     row = {"op": "moe_reduce_rs", "world": world, "tokens": T, "experts": E, "topk": topk, "N": H, "K": il}
     row["ours_us"] = _time(lambda: moe_reduce_rs(act, w2, ids, wt, rctx), args.iters, args.warmup, group)
+    if rctx.heap.has_multicast and world > 1:   # the other reduction mode of the same kernel, for the record
+        rctx.nvls = not rctx.nvls
+        row["nvls_us" if rctx.nvls else "slots_us"] = _time(lambda: moe_reduce_rs(act, w2, ids, wt, rctx), args.iters, args.warmup, group)
+        rctx.nvls = not rctx.nvls
     row["grouped_nccl_us"] = _time(base_down, args.iters, args.warmup, group)
     row["speedup"] = row["grouped_nccl_us"] / row["ours_us"]
     rows.append(row)

@@ -7,7 +7,8 @@
 //   2. for every owner rank, starting with the rank after this one, sums the k copies of each of the owner's tokens
 //      and stores the row into slot [this rank] of the owner's symmetric buffer, then adds the delivered rows to the
 //      owner's counter for this source with a release,
-//   3. waits until every source has delivered this rank's Tr rows and sums the `world` slots into rs_out [Tr, N].
+//   3. waits until every source has delivered this rank's Tr rows and sums the `world` slots into rs_out [Tr, N]
+//      (with `nvls` the rows stay at their producers and the owner sums them with multimem.ld_reduce through the switch).
 // It is called by all threads of all CTAs of a cooperative launch and returns false if a wait ran out (the status
 // block then holds the record). Role in the reference: the scatter / top-k reduce / reduce-scatter consumers of
 // python/triton_dist/kernels/nvidia/moe_reduce_rs.py:379-601, 816-926.
@@ -24,6 +25,8 @@ struct MoeRsArgs {
   const uint32_t* rs_base;  // local u32[world]: counter values before this call
   void* rs_out;           // [Tr, N]
   uint32_t* barrier_ctr;  // local u32 used by the grid barrier
+  int nvls;               // 1: the summed rows stay in this rank's own slots [owner][row]; the owner adds the `world`
+                          // copies with multimem.ld_reduce (the switch does the additions, fp32 accumulation)
 };
 
 __device__ __forceinline__ uint4 moe_rs_pack8(const float (&acc)[8], bool bf16) {
@@ -53,8 +56,13 @@ __device__ __forceinline__ bool moe_rs_phases(const SymmCtx& ctx, const MoeRsArg
     for (int lrow = blockIdx.x; lrow < a.Tr; lrow += gridDim.x) {
       ++my_rows;
       const int t = owner * a.Tr + lrow;
-      uint8_t* dst = static_cast<uint8_t*>(a.slots) + (static_cast<size_t>(ctx.rank) * a.Tr_cap + lrow) * a.N * 2;
-      uint8_t* rdst = symm_at(ctx, dst, owner);
+      uint8_t* rdst;
+      if (a.nvls) {  // keep the row here, at the offset of the owner's segment: the owner reads it through the switch
+        rdst = static_cast<uint8_t*>(a.slots) + (static_cast<size_t>(owner) * a.Tr_cap + lrow) * a.N * 2;
+      } else {
+        uint8_t* dst = static_cast<uint8_t*>(a.slots) + (static_cast<size_t>(ctx.rank) * a.Tr_cap + lrow) * a.N * 2;
+        rdst = symm_at(ctx, dst, owner);
+      }
       for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         const uint8_t* src = out + (static_cast<size_t>(t) * a.topk * a.ldo + v * 8) * 2;
@@ -83,6 +91,14 @@ __device__ __forceinline__ bool moe_rs_phases(const SymmCtx& ctx, const MoeRsArg
   if (!__syncthreads_and(ok)) return false;
   const uint8_t* slots = static_cast<const uint8_t*>(a.slots);
   for (int lrow = blockIdx.x; lrow < a.Tr; lrow += gridDim.x) {
+    if (a.nvls) {
+      const uint8_t* mine = slots + (static_cast<size_t>(ctx.rank) * a.Tr_cap + lrow) * a.N * 2;
+      for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+        const uint4 x = bf16 ? multimem_ld_reduce_bf16x8(mc_ptr(ctx, mine + v * 16)) : multimem_ld_reduce_f16x8(mc_ptr(ctx, mine + v * 16));
+        st_v4(static_cast<uint8_t*>(a.rs_out) + (static_cast<size_t>(lrow) * a.N + v * 8) * 2, x);
+      }
+      continue;
+    }
     for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       uint4 x[kMaxRanks];

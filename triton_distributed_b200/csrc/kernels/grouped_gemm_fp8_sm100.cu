@@ -65,6 +65,7 @@ struct Fp8GroupedParams {
   uint32_t* rs_cnt;           // symmetric u32[world]
   uint32_t* rs_base;          // local u32[world]
   void* rs_out;               // [Tr, N]
+  int rs_nvls;                // RS: reduce in the switch (see b200/moe_rs_phases.cuh)
 };
 
 enum Fp8GroupedMode : int { kFPlain = 0, kFAG = 1, kFRS = 2 };
@@ -405,7 +406,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const Fp8Groupe
   if (kMode == kFRS && !failed) {
     MoeRsArgs rs;
     rs.gemm_out = p.out; rs.ldo = p.ldo; rs.N = p.N; rs.topk = p.topk; rs.Tr = p.Tr; rs.Tr_cap = p.Tr_cap; rs.bf16 = p.bf16;
-    rs.slots = p.slots[par]; rs.rs_cnt = p.rs_cnt; rs.rs_base = p.rs_base; rs.rs_out = p.rs_out; rs.barrier_ctr = p.sync + 3;
+    rs.slots = p.slots[par]; rs.rs_cnt = p.rs_cnt; rs.rs_base = p.rs_base; rs.rs_out = p.rs_out; rs.barrier_ctr = p.sync + 3; rs.nvls = p.rs_nvls;
     failed = !moe_rs_phases(ctx, rs, epoch);
   }
 
@@ -532,10 +533,11 @@ B200_API int b200_grouped_gemm_fp8_rs(const void* symm_ctx, const void* A8, int 
                                       const int32_t* sorted_ids, const int32_t* tile_expert, const int32_t* tile_order,
                                       const int32_t* totals, int max_tiles, const float* row_scale, void* gemm_out,
                                       void* slots0, void* slots1, int Tr_cap, uint32_t* rs_cnt, uint32_t* rs_base,
-                                      uint32_t* sync, void* rs_out, int out_dtype, void* stream) {
+                                      uint32_t* sync, void* rs_out, int out_dtype, int nvls, void* stream) {
   SymmCtx ctx;
   memcpy(&ctx, symm_ctx, sizeof(ctx));
   B200_REQUIRE(Tr <= Tr_cap, "tokens per rank (%d) exceed the context capacity (%d)", Tr, Tr_cap);
+  B200_REQUIRE(!nvls || ctx.mc_base != 0, "the in-switch reduction needs an NVLS multicast mapping");
   Fp8GroupedParams p;
   CUtensorMap tw;
   const int n_pairs = Tr * ctx.world * topk;
@@ -544,5 +546,6 @@ B200_API int b200_grouped_gemm_fp8_rs(const void* symm_ctx, const void* A8, int 
   if (rc != kOk) return rc;
   p.sync = sync; p.Tr = Tr; p.topk = topk; p.Tr_cap = Tr_cap;
   p.slots[0] = slots0; p.slots[1] = slots1; p.rs_cnt = rs_cnt; p.rs_base = rs_base; p.rs_out = rs_out;
+  p.rs_nvls = nvls ? 1 : 0;
   return fp8_launch<kFRS>(tw, p, ctx, sm_count(), nullptr, static_cast<cudaStream_t>(stream));
 }

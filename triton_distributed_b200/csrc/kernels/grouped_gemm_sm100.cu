@@ -67,6 +67,7 @@ struct GroupedParams {
   uint32_t* rs_cnt;           // symmetric u32[world]: rows received per source
   uint32_t* rs_base;          // local u32[world]
   void* rs_out;               // [Tr, N]
+  int rs_nvls;                // RS: reduce in the switch (see b200/moe_rs_phases.cuh)
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int bytes) {
@@ -369,7 +370,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GroupedParams
     // all tiles of this rank are in p.out ([n_pairs, N], routing weight applied)
     MoeRsArgs rs;
     rs.gemm_out = p.out; rs.ldo = p.ldo; rs.N = p.N; rs.topk = p.topk; rs.Tr = p.Tr; rs.Tr_cap = p.Tr_cap; rs.bf16 = p.bf16;
-    rs.slots = p.slots[par]; rs.rs_cnt = p.rs_cnt; rs.rs_base = p.rs_base; rs.rs_out = p.rs_out; rs.barrier_ctr = p.sync + 3;
+    rs.slots = p.slots[par]; rs.rs_cnt = p.rs_cnt; rs.rs_base = p.rs_base; rs.rs_out = p.rs_out; rs.barrier_ctr = p.sync + 3; rs.nvls = p.rs_nvls;
     failed = !moe_rs_phases(ctx, rs, epoch);
   }
 
@@ -501,15 +502,17 @@ B200_API int b200_ag_grouped_gemm(const void* symm_ctx, const void* a_local, voi
 }
 
 // Grouped GEMM + topk-reduce + reduce-scatter: A [n_pairs, K_local] (row per pair), W [E, N, K_local],
-// row_scale [n_pairs] routing weights, gemm_out [n_pairs, N] local scratch, rs_out [Tr, N].
+// row_scale [n_pairs] routing weights, gemm_out [n_pairs, N] local scratch, rs_out [Tr, N]. nvls != 0: the final sum over
+// the ranks runs inside the switch (multimem.ld_reduce) instead of over per-source slots at the owner.
 B200_API int b200_grouped_gemm_rs(const void* symm_ctx, const void* A, int lda, const void* W, int E, int N, int K, int Tr,
                                   int topk, const int32_t* sorted_ids, const int32_t* tile_expert, const int32_t* tile_order,
                                   const int32_t* totals, int max_tiles, const float* row_scale, void* gemm_out, void* slots0,
                                   void* slots1, int Tr_cap, uint32_t* rs_cnt, uint32_t* rs_base, uint32_t* sync, void* rs_out,
-                                  int dtype, void* stream) {
+                                  int dtype, int nvls, void* stream) {
   SymmCtx ctx;
   memcpy(&ctx, symm_ctx, sizeof(ctx));
   B200_REQUIRE(Tr <= Tr_cap, "tokens per rank (%d) exceed the context capacity (%d)", Tr, Tr_cap);
+  B200_REQUIRE(!nvls || ctx.mc_base != 0, "the in-switch reduction needs an NVLS multicast mapping");
   GroupedParams p;
   CUtensorMap tw;
   const int n_pairs = Tr * ctx.world * topk;
@@ -518,5 +521,6 @@ B200_API int b200_grouped_gemm_rs(const void* symm_ctx, const void* A, int lda, 
   if (rc != kOk) return rc;
   p.A = A; p.lda = lda; p.sync = sync; p.Tr = Tr; p.topk = topk; p.Tr_cap = Tr_cap;
   p.slots[0] = slots0; p.slots[1] = slots1; p.rs_cnt = rs_cnt; p.rs_base = rs_base; p.rs_out = rs_out;
+  p.rs_nvls = nvls ? 1 : 0;
   return launch_grouped<kGRS>(tw, p, ctx, sm_count(), static_cast<cudaStream_t>(stream));
 }

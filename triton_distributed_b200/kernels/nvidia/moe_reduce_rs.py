@@ -11,6 +11,7 @@ point maps onto the same kernel: on one NVSwitch node there is no second topolog
 from __future__ import annotations
 
 import dataclasses
+import os
 
 import torch
 import torch.distributed as dist
@@ -53,6 +54,7 @@ class MoEReduceRSContext:
     plans: dict
     full_topk_ids: torch.Tensor | None = None
     full_topk_weight: torch.Tensor | None = None
+    nvls: bool = False   # final sum over the ranks inside the switch (multimem.ld_reduce); needs the multicast mapping
 
     def plan_for(self, ntokens: int) -> MoeSortPlan:
         if ntokens not in self.plans:
@@ -77,6 +79,7 @@ def create_moe_rs_context(pg, local_world_size: int, max_token_num: int, hidden_
     ctx = MoEReduceRSContext(heap.rank, world, max_token_num, hidden_dim, num_experts, topk, output_dtype, heap, slots, rs_cnt,
                              torch.zeros(16, dtype=torch.int32, device="cuda"), torch.zeros(4, dtype=torch.int32, device="cuda"),
                              torch.empty((max_token_num * topk, hidden_dim), dtype=output_dtype, device="cuda"), {})
+    ctx.nvls = heap.has_multicast and world > 1 and os.environ.get("B200DIST_MOE_RS_NVLS", "0") == "1"
     if router_logits is not None:
         ctx.full_topk_ids, ctx.full_topk_weight = select_experts(pg, world, topk, input_dtype, device, router_logits)
     heap.barrier_all()
@@ -101,7 +104,7 @@ def moe_reduce_rs(x: torch.Tensor, w: torch.Tensor, topk_ids: torch.Tensor, topk
     _lib.call("b200_grouped_gemm_rs", ctx.heap.ctx, ptr(x), x.stride(0), ptr(w), E, N, K, Tr, ctx.topk, ptr(plan.sorted_ids),
               ptr(plan.tile_expert), None, ptr(plan.totals), plan.max_tiles, ptr(scale), ptr(ctx.gemm_out), ptr(ctx.slots[0]),
               ptr(ctx.slots[1]), ctx.max_token_num // ctx.world_size, ptr(ctx.rs_cnt), ptr(ctx.rs_base), ptr(ctx.sync),
-              ptr(out), dtype_code(x.dtype), stream_ptr())
+              ptr(out), dtype_code(x.dtype), 1 if ctx.nvls else 0, stream_ptr())
     ops._count()
     return out
 
@@ -158,6 +161,6 @@ def moe_reduce_rs_fp8(x8: torch.Tensor, x_scale: torch.Tensor, w8: torch.Tensor,
               ptr(w8.contiguous()), ptr(w_scale.contiguous()), E, N, K, Tr, ctx.topk, ptr(plan.sorted_ids), ptr(plan.tile_expert),
               None, ptr(plan.totals), plan.max_tiles, ptr(scale), ptr(ctx.gemm_out), ptr(ctx.slots[0]), ptr(ctx.slots[1]),
               ctx.max_token_num // ctx.world_size, ptr(ctx.rs_cnt), ptr(ctx.rs_base), ptr(ctx.sync), ptr(out),
-              dtype_code(out.dtype), stream_ptr())
+              dtype_code(out.dtype), 1 if ctx.nvls else 0, stream_ptr())
     ops._count()
     return out
