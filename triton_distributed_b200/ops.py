@@ -186,7 +186,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) ->
 
 def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float, residual: torch.Tensor | None = None,
             out: torch.Tensor | None = None) -> torch.Tensor:
-    """RMSNorm over the last dim. With `residual`, computes ``residual += x`` in place first and normalises the sum."""
+    """RMSNorm over the last dim. With `residual`, computes ``residual += x`` in place first and normalises the sum.
+
+    ``gamma`` is treated as a weight: the kernel fetches it before it waits for the kernel launched just before it
+    (programmatic dependent launch), so it must not be an output of that kernel. The same holds for the gains of
+    ``qk_norm_rope`` and of the fused all-reduce + RMSNorm."""
     _lib.require_cuda()
     hidden = x.shape[-1]
     x2 = x.reshape(-1, hidden)
