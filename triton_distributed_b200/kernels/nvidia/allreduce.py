@@ -82,7 +82,7 @@ def create_allreduce_ctx(workspace_nbytes: int, rank: int, world_size: int, loca
     if _AR_LL and world_size > 1:
         # dedicated packet buffers (data and flag share a word, so they must never hold anything else)
         ctx.ll_ws = [heap.create_tensor((world_size * _LL_MAX_BYTES * 2,), torch.uint8, align=1024) for _ in range(2)]
-        ctx.ll_sync = torch.zeros(4, dtype=torch.int32, device="cuda")
+        ctx.ll_sync = torch.zeros(256, dtype=torch.int32, device="cuda")  # one call counter per CTA
     heap.barrier_all()
     torch.cuda.synchronize()
     return ctx
