@@ -278,36 +278,53 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const Fp8Groupe
       float acc[kFN];
 #pragma unroll
       for (int j = 0; j < kFN; ++j) acc[j] = 0.f;
-      // AG: a gathered row's scales may be read only after the tile's first partial is complete (by then the gather
-      // warps have seen the row's shard land); they are read past L1
-      float s_next = (kMode != kFAG && valid) ? sa_row[0] * sw_row[0] : 0.f;
-      for (int kb = 0; kb < p.num_kb; ++kb, ++pcount) {
-        const uint32_t pb = pcount & 1, pphase = (pcount >> 1) & 1;
-        float s = s_next;
-        if (!(kMode == kFAG && kb == 0) && kb + 1 < p.num_kb)
-          s_next = valid ? (kMode == kFAG ? __ldcg(sa_row + kb + 1) : sa_row[kb + 1]) * sw_row[kb + 1] : 0.f;  // in flight during the wait
-        if (!mbar_wait(pfull_bar + pb, pphase, abort_flag, timeout_ns)) { ok = false; break; }
-        if (kMode == kFAG && kb == 0) {
-          s = valid ? __ldcg(sa_row) * sw_row[0] : 0.f;
-          if (1 < p.num_kb) s_next = valid ? __ldcg(sa_row + 1) * sw_row[1] : 0.f;
-        }
-        tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(w4 * 32) << 16) + pb * kFN;
+      // The scale of k-block kb is sa[row, kb] * sw[e, n, kb]: two global loads per k-block. They are requested four
+      // k-blocks ahead and kept as raw values (no arithmetic on them until their k-block), so their latency never sits
+      // between two promotions; with a look-ahead of one the loop ran at one L2 round trip per k-block, about six times
+      // the time of the k-block's MMAs. AG: a gathered row's scales may be read only after the tile's first partial is
+      // complete (by then the gather warps have seen the row's shard land); they are read past L1.
+      auto ld_sa = [&](int kb) -> float { return valid ? (kMode == kFAG ? __ldcg(sa_row + kb) : sa_row[kb]) : 0.f; };
+      float sa_r[4], sw_r[4];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t r0[32], r1[32];
-          tmem_ld_32x32(taddr + h * 64, r0);
-          tmem_ld_32x32(taddr + h * 64 + 32, r1);
-          tmem_ld_wait();
+      for (int j = 0; j < 4; ++j) {
+        sw_r[j] = j < p.num_kb ? sw_row[j] : 0.f;
+        sa_r[j] = (kMode != kFAG && j < p.num_kb) ? ld_sa(j) : 0.f;
+      }
+      for (int kb0 = 0; kb0 < p.num_kb && ok; kb0 += 4) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            acc[h * 64 + j] = fmaf(s, __uint_as_float(r0[j]), acc[h * 64 + j]);
-            acc[h * 64 + 32 + j] = fmaf(s, __uint_as_float(r1[j]), acc[h * 64 + 32 + j]);
+        for (int j = 0; j < 4; ++j) {
+          const int kb = kb0 + j;
+          if (kb >= p.num_kb || !ok) break;  // uniform over the CTA's promotion warps
+          const uint32_t pb = pcount & 1, pphase = (pcount >> 1) & 1;
+          ++pcount;
+          if (!mbar_wait(pfull_bar + pb, pphase, abort_flag, timeout_ns)) { ok = false; break; }
+          if (kMode == kFAG && kb == 0) {
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) sa_r[jj] = jj < p.num_kb ? ld_sa(jj) : 0.f;
           }
+          const float s = sa_r[j] * sw_r[j];
+          if (kb + 4 < p.num_kb) {  // refill this slot for the k-block four ahead
+            sa_r[j] = ld_sa(kb + 4);
+            sw_r[j] = sw_row[kb + 4];
+          }
+          tc_fence_after_sync();
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(w4 * 32) << 16) + pb * kFN;
+          // 16 columns in registers while the next 16 are on their way from TMEM (two small buffers in turn: the 128
+          // accumulators leave no room for more)
+          uint32_t r0[16], r1[16];
+          tmem_ld_32x16(taddr, r0);
+#pragma unroll
+          for (int h = 0; h < 8; ++h) {
+            tmem_ld_wait();
+            if (h + 1 < 8) tmem_ld_32x16(taddr + (h + 1) * 16, (h & 1) ? r0 : r1);
+            uint32_t* r = (h & 1) ? r1 : r0;
+#pragma unroll
+            for (int q = 0; q < 16; ++q) acc[h * 16 + q] = fmaf(s, __uint_as_float(r[q]), acc[h * 16 + q]);
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(pempty_bar + pb);
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(pempty_bar + pb);
       }
       if (!ok) break;
       // ---- write the tile: convert, stage through swizzled shared memory, store 128-byte row segments
