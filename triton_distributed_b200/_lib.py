@@ -18,7 +18,8 @@ from pathlib import Path
 import torch
 
 _PKG = Path(__file__).resolve().parent
-LIB_PATH = _PKG / "lib" / "libb200dist.so"
+_DEBUG = os.environ.get("B200DIST_DEBUG_LIB", "0") == "1"   # the checking build (python -m ...build --debug)
+LIB_PATH = _PKG / "lib" / ("libb200dist_debug.so" if _DEBUG else "libb200dist.so")
 
 _lock = threading.Lock()
 _lib: ctypes.CDLL | None = None
@@ -47,7 +48,7 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
                 raise RuntimeError(
                     f"native library {LIB_PATH} is missing; run `python -m triton_distributed_b200.build`")
             from . import build as _build
-            _build.build()
+            _build.build(debug=_DEBUG)
         lib = ctypes.CDLL(str(LIB_PATH))
         lib.b200_last_error.restype = ctypes.c_char_p
         for name in ("b200_heap_base", "b200_heap_mc_base", "b200_heap_bytes", "b200_heap_live_bytes"):

@@ -7,7 +7,11 @@ Compilation is incremental (source / header mtimes) and parallel.
 Role in the reference: CMake + setup.py building ``libtriton_distributed.so`` and the Triton
 backend (``CMakeLists.txt:15-26``, ``csrc/lib/CMakeLists.txt:47``, ``python/setup.py``).
 
-Usage: ``python -m triton_distributed_b200.build [--force] [--verbose]``
+Usage: ``python -m triton_distributed_b200.build [--force] [--verbose] [--debug]``
+
+``--debug`` builds a second library, ``lib/libb200dist_debug.so``, with ``-DB200_DEBUG_CHECKS``: bounds-checked symmetric
+address translation and pseudo-random delays in front of every notify / wait / barrier (see ``b200/primitives.cuh``).
+``B200DIST_DEBUG_LIB=1`` makes the package load it instead of the regular library.
 """
 from __future__ import annotations
 
@@ -24,6 +28,7 @@ CSRC = PKG / "csrc"
 BUILD = PKG.parent / "build" / "b200dist"
 LIB_DIR = PKG / "lib"
 LIB_PATH = LIB_DIR / "libb200dist.so"
+DEBUG_LIB_PATH = LIB_DIR / "libb200dist_debug.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -53,8 +58,8 @@ def _headers_mtime() -> float:
     return max((h.stat().st_mtime for h in (CSRC / "include").rglob("*") if h.is_file()), default=0.0)
 
 
-def _compile(src: Path, obj: Path, verbose: bool, ptxas_v: bool) -> tuple[Path, str]:
-    cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+def _compile(src: Path, obj: Path, verbose: bool, ptxas_v: bool, debug: bool = False) -> tuple[Path, str]:
+    cmd = [_nvcc(), *NVCC_FLAGS, *(["-DB200_DEBUG_CHECKS"] if debug else []), "-c", str(src), "-o", str(obj)]
     if ptxas_v:
         cmd += ["-Xptxas", "-v"]
     proc = subprocess.run(cmd, capture_output=True, text=True)
@@ -63,31 +68,33 @@ def _compile(src: Path, obj: Path, verbose: bool, ptxas_v: bool) -> tuple[Path, 
     return src, proc.stderr if (verbose or ptxas_v) else ""
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_v: bool = False, jobs: int | None = None) -> Path:
-    """Compile what is out of date and link the shared library. Returns its path."""
+def build(force: bool = False, verbose: bool = False, ptxas_v: bool = False, jobs: int | None = None,
+          debug: bool = False) -> Path:
+    """Compile what is out of date and link the shared library (the checking build with ``debug``). Returns its path."""
     BUILD.mkdir(parents=True, exist_ok=True)
     LIB_DIR.mkdir(parents=True, exist_ok=True)
     hdr_time = max(_headers_mtime(), Path(__file__).stat().st_mtime)
+    lib_path = DEBUG_LIB_PATH if debug else LIB_PATH
     todo, objs = [], []
     for src in sources():
-        obj = BUILD / (src.parent.name + "_" + src.stem + ".o")
+        obj = BUILD / (src.parent.name + "_" + src.stem + (".dbg.o" if debug else ".o"))
         objs.append(obj)
         if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_time):
             todo.append((src, obj))
     if todo:
         with concurrent.futures.ThreadPoolExecutor(max_workers=jobs or min(8, os.cpu_count() or 4)) as ex:
-            futs = [ex.submit(_compile, s, o, verbose, ptxas_v) for s, o in todo]
+            futs = [ex.submit(_compile, s, o, verbose, ptxas_v, debug) for s, o in todo]
             for f in concurrent.futures.as_completed(futs):
                 src, log = f.result()
                 if verbose or ptxas_v:
                     print(f"[build] {src.name}\n{log}", file=sys.stderr)
-    if todo or not LIB_PATH.exists():
+    if todo or not lib_path.exists():
         cmd = [_nvcc(), "-shared", "-cudart", "static", "-gencode", "arch=compute_100a,code=sm_100a",
-               "-o", str(LIB_PATH), *map(str, objs), "-lpthread", "-ldl", "-lrt"]
+               "-o", str(lib_path), *map(str, objs), "-lpthread", "-ldl", "-lrt"]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
-    return LIB_PATH
+    return lib_path
 
 
 def compile_extension(source: str | Path, out_dir: str | Path | None = None, extra_flags: list[str] | None = None) -> Path:
@@ -113,8 +120,9 @@ def main() -> None:
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--ptxas-v", action="store_true", help="print registers / spills / shared memory per kernel")
+    ap.add_argument("--debug", action="store_true", help="build lib/libb200dist_debug.so with B200_DEBUG_CHECKS")
     args = ap.parse_args()
-    print(build(force=args.force, verbose=args.verbose, ptxas_v=args.ptxas_v))
+    print(build(force=args.force, verbose=args.verbose, ptxas_v=args.ptxas_v, debug=args.debug))
 
 
 if __name__ == "__main__":

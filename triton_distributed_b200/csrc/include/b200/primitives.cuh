@@ -55,10 +55,39 @@ struct SymmCtx {
 __device__ __forceinline__ int rank(const SymmCtx& c) { return c.rank; }
 __device__ __forceinline__ int num_ranks(const SymmCtx& c) { return c.world; }
 
+// Checking build (`python -m triton_distributed_b200.build --debug` -> lib/libb200dist_debug.so, loaded when
+// B200DIST_DEBUG_LIB=1): compiled with B200_DEBUG_CHECKS, every translation of a symmetric address verifies that the
+// pointer lies inside this rank's heap and that the peer exists. A violation is recorded in the status block
+// (bad argument: who = peer, expected = low word of the heap size, seen = low word of the offset) and the translation
+// falls back to the local address, so the access stays inside this GPU's own memory instead of faulting a peer.
+// notify / signal / wait / barrier entry points also sleep for a pseudo-random time of up to ~2 us first, which
+// widens the windows in which a missing fence, an early flag or a reused buffer would show up in the multi-rank cases.
+__device__ __forceinline__ void report_status(const SymmCtx& c, uint32_t code, uint32_t who, uint32_t expected,
+                                              uint32_t seen, uint32_t line);
+#ifdef B200_DEBUG_CHECKS
+__device__ __forceinline__ bool debug_symm_ok(const SymmCtx& c, uint64_t off, int peer, uint32_t line) {
+  if (off < c.heap_bytes && peer >= 0 && peer < c.world) return true;
+  report_status(c, kStatusBadArgument, static_cast<uint32_t>(peer), static_cast<uint32_t>(c.heap_bytes),
+                static_cast<uint32_t>(off), line);
+  return false;
+}
+__device__ __forceinline__ void debug_jitter() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  const uint32_t h = (static_cast<uint32_t>(t) ^ (threadIdx.x * 2654435761u) ^ (blockIdx.x * 40503u)) * 2246822519u;
+  __nanosleep((h >> 21) & 2047u);
+}
+#else
+__device__ __forceinline__ void debug_jitter() {}
+#endif
+
 // Translate a pointer into this rank's heap to the same offset of `peer`'s heap.
 template <typename T>
 __device__ __forceinline__ T* symm_at(const SymmCtx& c, T* local_ptr, int peer) {
   uint64_t off = reinterpret_cast<uint64_t>(local_ptr) - c.heap_base[c.rank];
+#ifdef B200_DEBUG_CHECKS
+  if (!debug_symm_ok(c, off, peer, __LINE__)) return local_ptr;
+#endif
   return reinterpret_cast<T*>(c.heap_base[peer] + off);
 }
 
@@ -66,6 +95,9 @@ __device__ __forceinline__ T* symm_at(const SymmCtx& c, T* local_ptr, int peer) 
 template <typename T>
 __device__ __forceinline__ T* mc_ptr(const SymmCtx& c, T* local_ptr) {
   uint64_t off = reinterpret_cast<uint64_t>(local_ptr) - c.heap_base[c.rank];
+#ifdef B200_DEBUG_CHECKS
+  if (c.mc_base == 0 || !debug_symm_ok(c, off, c.rank, __LINE__)) return local_ptr;
+#endif
   return reinterpret_cast<T*>(c.mc_base + off);
 }
 
@@ -239,6 +271,7 @@ enum class WaitCmp { EQ, GE };
 template <WaitCmp CMP = WaitCmp::GE, bool SYS = true>
 __device__ __forceinline__ bool wait_flag(const SymmCtx& c, const uint32_t* flag, uint32_t value,
                                           uint32_t who = 0, uint32_t line = 0) {
+  debug_jitter();
   uint64_t t0 = 0;
   uint32_t spins = 0;
   while (true) {
@@ -282,6 +315,7 @@ enum class SigOp { SET, ADD };
 // (e.g. behind __syncthreads()); releases them at system scope and updates `peer`'s copy of the flag.
 template <SigOp OP = SigOp::SET>
 __device__ __forceinline__ void notify(const SymmCtx& c, uint32_t* local_flag, int peer, uint32_t value) {
+  debug_jitter();
   uint32_t* dst = symm_at(c, local_flag, peer);
   if (OP == SigOp::SET) {
     st_release_sys(dst, value);
@@ -369,6 +403,7 @@ __device__ __forceinline__ void putmem_signal_block(const SymmCtx& c, void* dst_
 // `epoch` the value of this round (strictly increasing from call to call, same on every rank).
 // Thread k < world publishes epoch into flags[rank] on peer k, then waits for flags[k] locally.
 __device__ __forceinline__ bool barrier_all_block(const SymmCtx& c, uint32_t* flags, uint32_t epoch) {
+  debug_jitter();
   __syncthreads();
   int t = flat_tid();
   bool ok = true;

@@ -263,6 +263,15 @@ B200_API int b200_test_wait(const void* symm_ctx, const void* flags, int n, uint
   B200_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }
+// 1 when this library was compiled with B200_DEBUG_CHECKS (the checking build), else 0.
+B200_API int b200_debug_checks() {
+#ifdef B200_DEBUG_CHECKS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 B200_API int b200_test_notify_add(const void* symm_ctx, void* counter, int root, uint32_t expected, void* ok_out,
                                   void* stream) {
   LOAD_CTX(ctx);
