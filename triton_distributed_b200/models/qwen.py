@@ -24,10 +24,9 @@ from .. import ops
 from ..kernels.allreduce import AllReduceMethod
 from ..kernels.nvidia import (all_reduce_rmsnorm, create_ag_gemm_context, create_allreduce_ctx,
                               create_fast_allgather_context, create_gemm_rs_context, fast_allgather)
-from ..layers.nvidia import TP_MLP, TP_Attn, TP_MoE, _set_cos_sin_cache, golden, layer_norm
+from ..layers.nvidia import TP_MLP, TP_Attn, _set_cos_sin_cache, golden, layer_norm
 from .config import ArchConfig, ModelConfig
 from .kv_cache import KV_Cache
-from .utils import logger
 from .weights import RandomSource, SafetensorsSource, WeightSource
 
 

@@ -16,7 +16,7 @@ import os
 import torch
 
 from . import _lib
-from ._lib import c_float, c_int, dtype_code, ptr, stream_ptr
+from ._lib import c_float, dtype_code, ptr, stream_ptr
 
 # number of native kernel launches issued through this module (bench.py reports it)
 launch_count = 0

@@ -14,13 +14,10 @@ from __future__ import annotations
 import contextlib
 import datetime
 import functools
-import gzip
 import json
 import os
 import random
-import shutil
 import tarfile
-import time
 from pathlib import Path
 from typing import Callable, Sequence
 
