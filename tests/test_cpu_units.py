@@ -325,3 +325,18 @@ def test_bench_withholds_its_result_when_a_wait_expired(capsys):
     assert json.loads(capsys.readouterr().out) == {"value": 1.0}
     bench.emit_result({"value": 1.0}, FakeHeap(0), 1)   # only rank 0 prints
     assert capsys.readouterr().out == ""
+
+
+def test_gemm_rs_in_switch_reduction_is_opt_in():
+    from types import SimpleNamespace
+
+    from triton_distributed_b200.kernels.nvidia.gemm_reduce_scatter import GEMMReduceScatterTensorParallelContext
+
+    def ctx(world, multicast, nvls=None):
+        return GEMMReduceScatterTensorParallelContext(
+            rank=0, world_size=world, local_world_size=world, max_M=16384, N=8192, output_dtype=None,
+            heap=SimpleNamespace(has_multicast=multicast), slots=[], rs_cnt=None, rs_base=None, sync=None, rs_blocks=4, nvls=nvls)
+
+    assert not ctx(2, True).use_nvls(8192) and not ctx(8, True).use_nvls(8192)   # default: per-source slots
+    assert ctx(8, True, nvls=True).use_nvls(128) and not ctx(2, True, nvls=False).use_nvls(8192)
+    assert not ctx(8, False, nvls=True).use_nvls(128)                            # no multicast mapping, no in-switch sum

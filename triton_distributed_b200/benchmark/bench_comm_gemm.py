@@ -91,7 +91,8 @@ def bench_pair(group, ms, iters: int, warmup: int, rows: list, hidden: int = 819
             rs_ctx.nvls = nvls
             modes[name] = _time(lambda: gemm_rs(x, w2, rs_ctx, out=out), iters, warmup, group)
         rs_ctx.nvls = default_nvls
-        t_ours = modes["nvls" if default_nvls and "nvls" in modes else "slots"]
+        auto_nvls = rs_ctx.use_nvls(M)
+        t_ours = modes["nvls" if auto_nvls and "nvls" in modes else "slots"]
         t_base = _time(base_rs, iters, warmup, group)
         flops = 2.0 * M * H * k_rs
         nv_bytes = (world - 1) * (M // world) * H * 2
@@ -99,7 +100,7 @@ def bench_pair(group, ms, iters: int, warmup: int, rows: list, hidden: int = 819
         rows.append({"op": "gemm_rs", "world": world, "M": M, "N": H, "K": k_rs, "ours_us": t_ours * 1e3,
                      "nccl_cublas_us": t_base * 1e3, "speedup": t_base / t_ours, "roofline_us": roof * 1e3,
                      "frac_of_roofline": roof / t_ours, "tflops": flops / t_ours / 1e9,
-                     "reduce_mode": "nvls" if default_nvls else "slots",
+                     "reduce_mode": "nvls" if auto_nvls else "slots",
                      "modes_us": {k: v * 1e3 for k, v in modes.items()}})
     utils.get_heap().check_status("bench_comm_gemm")
     ag_ctx.finalize()

@@ -7,7 +7,8 @@ the owner rank's slot over NVLink, bumps the owner's arrival counters with a rel
 kernel finishes with the owner-side fp32 reduction of its rows (``csrc/kernels/gemm_sm100.cu``).
 The sum order is fixed (slot 0..r-1), so results are reproducible run to run.
 
-With an NVLS multicast mapping the reduction can run inside the switch instead (``ctx.nvls``, ``B200DIST_RS_NVLS``):
+With an NVLS multicast mapping the reduction can run inside the switch instead (``ctx.nvls`` / ``B200DIST_RS_NVLS``:
+True / 1 to enable; the default is the slot reduction):
 the epilogue keeps every partial row in this rank's own memory at the owner's offset, and the owner issues one
 ``multimem.ld_reduce`` per 16 bytes that returns the sum over the ranks (fp32 accumulation in the switch), the role of
 the multimem reduce-scatter in ``kernels/nvidia/moe_reduce_rs.py:1128-1152`` of the reference. The owner then receives
@@ -24,9 +25,6 @@ from ... import _lib, ops
 from ..._lib import dtype_code, ptr, stream_ptr
 from ...runtime.heap import SymmHeap, get_heap
 
-
-
-_RS_NVLS_DEFAULT = "0"
 
 
 @dataclasses.dataclass
@@ -49,7 +47,15 @@ class GEMMReduceScatterTensorParallelContext:
     stages: int = 4
     group_m: int = 8
     max_ctas: int = 0
-    nvls: bool = False            # reduce in the switch (needs the heap's multicast mapping)
+    nvls: bool | None = None      # reduce in the switch (needs the heap's multicast mapping); None / False = slots
+
+    def use_nvls(self, M: int) -> bool:
+        """Whether a call with M rows sums in the switch: only when asked to (``nvls=True`` or ``B200DIST_RS_NVLS=1``).
+        Measured on the Llama-3-70B down-projection (N = 8192): at two ranks the in-switch reduction wins from a few
+        thousand rows (M = 8192: 1452 us against 1684 us with slots; M = 2048: 397 against 375 us), at four ranks the
+        slots win (714 against 740 us). An automatic switch at two ranks and M >= 4096 made the Qwen3-32B prefill
+        (N = 5120) 4 % slower, so there is none."""
+        return bool(self.nvls) and self.heap.has_multicast
 
     def finalize(self) -> None:
         self.heap.sync_and_check(type(self).__name__)
@@ -75,7 +81,7 @@ def create_gemm_rs_context(max_M: int, N: int, rank: int, world_size: int, local
         heap=heap, slots=slots, rs_cnt=rs_cnt,
         rs_base=torch.zeros(world_size * rs_blocks, dtype=torch.int32, device="cuda"),
         sync=torch.zeros(4, dtype=torch.int32, device="cuda"), rs_blocks=rs_blocks, group_m=GROUP_M,
-        nvls=heap.has_multicast and world_size > 1 and os.environ.get("B200DIST_RS_NVLS", _RS_NVLS_DEFAULT) == "1")
+        nvls={"1": True, "0": False}.get(os.environ.get("B200DIST_RS_NVLS", ""), None))
     heap.barrier_all()
     torch.cuda.synchronize()
     return ctx
@@ -103,6 +109,6 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, ctx: GEMMReduceScatterTensorParall
         raise ValueError("out must be a contiguous [M / world, N] tensor of the context's dtype")
     _lib.call("b200_gemm_rs", ctx.heap.ctx, ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0),
               dtype_code(a.dtype), ptr(ctx.slots[0]), ptr(ctx.slots[1]), ptr(ctx.rs_cnt), ptr(ctx.rs_base), ptr(ctx.sync),
-              ctx.max_M // ctx.world_size, ctx.rs_blocks, ctx.group_m, ctx.max_ctas, 1 if ctx.nvls else 0, stream_ptr())
+              ctx.max_M // ctx.world_size, ctx.rs_blocks, ctx.group_m, ctx.max_ctas, 1 if ctx.use_nvls(M) else 0, stream_ptr())
     ops._count()
     return out
