@@ -340,3 +340,16 @@ def test_gemm_rs_in_switch_reduction_is_opt_in():
     assert not ctx(2, True).use_nvls(8192) and not ctx(8, True).use_nvls(8192)   # default: per-source slots
     assert ctx(8, True, nvls=True).use_nvls(128) and not ctx(2, True, nvls=False).use_nvls(8192)
     assert not ctx(8, False, nvls=True).use_nvls(128)                            # no multicast mapping, no in-switch sum
+
+
+def test_ag_moe_tile_reordering_only_when_it_pays():
+    """Arrival-ordered tiles re-stream every expert's weights once per arrival stage; the wrapper reorders only when
+    those bytes cost clearly less HBM time than the gather takes on the links."""
+    from types import SimpleNamespace
+
+    from triton_distributed_b200.kernels.nvidia.allgather_group_gemm import _reorder_pays
+
+    ctx8 = SimpleNamespace(num_ranks=8, topk=8)
+    assert not _reorder_pays(SimpleNamespace(num_ranks=1, topk=8), 8192, 128, 384, 4096, 2)   # one rank: nothing to overlap
+    assert not _reorder_pays(ctx8, 8192, 128, 384, 4096, 2)     # 403 MB of weights x 3 extra passes >> 58 MB gather
+    assert _reorder_pays(ctx8, 65536, 8, 128, 8192, 2)          # few small experts, many tokens: the gather dominates
