@@ -368,3 +368,26 @@ def test_decode_gemm_ring_publishing_before_arming_is_caught():
     with pytest.raises(Violation):
         for seed in range(300):
             _two_producer_ring_model(2, 12, random.Random(seed), publish_after_arming=False)
+
+
+# ---------------------------------------------------------------------------------------------- per-CTA call counters
+def test_per_cta_call_counters_stay_equal_for_any_sequence_of_grid_sizes():
+    """The packet all-reduce (`csrc/kernels/allreduce_ll.cu`) keeps one copy of its call counter per CTA: CTA b reads
+    copy b on entry, uses `copy + 1` as the packet flag and stores it back when it leaves; CTA 0 also advances the copies
+    of the CTAs that the launch does not have. Every rank must derive the same flag for the same call whatever the grid
+    sizes of the calls so far, i.e. all copies must be equal after every launch."""
+    rng = random.Random(7)
+    max_ctas = 256
+    copies = [0] * max_ctas
+    for call in range(1, 400):
+        grid = rng.choice([1, 2, 8, 8, 8, 37, 148, 256])
+        order = list(range(grid))
+        rng.shuffle(order)                      # CTAs enter and leave in any order
+        flags = {b: copies[b] + 1 for b in order}
+        assert set(flags.values()) == {call}    # every CTA of the launch uses the same flag, and it is the call's number
+        for b in order:
+            copies[b] = flags[b]
+            if b == 0:
+                for j in range(grid, max_ctas):
+                    copies[j] = flags[0]
+        assert copies == [call] * max_ctas
