@@ -218,7 +218,9 @@ def test_scatter_gather_index_helpers_and_public_names():
                  "fused_sp_ag_attn_intra_node", "fused_sp_ag_attn_inter_node", "create_allreduce_ctx", "all_reduce",
                  "get_auto_allreduce_method", "BarrierAllContext", "wait_eq", "set_signal", "create_reduce_scater_2d_ctx",
                  "reduce_scatter_2d_op", "ring_reduce", "calc_gather_scatter_index_triton", "reduce_topk_tma",
-                 "estimate_gemm_sol_time_ms", "get_tensorcore_tflops", "estimate_all_gather_time_ms", "grouped_gemm_fp8"]:
+                 "estimate_gemm_sol_time_ms", "get_tensorcore_tflops", "estimate_all_gather_time_ms", "grouped_gemm_fp8",
+                 "create_ag_group_gemm_fp8_context", "ag_group_gemm_fp8", "moe_reduce_rs_fp8", "moe_reduce_rs",
+                 "quantize_fp8_rows", "quantize_fp8_weight_blocks"]:
         assert hasattr(K, name), name
 
 
